@@ -1,0 +1,161 @@
+/*
+ * vortx_b200 — C ABI of the B200 (sm_100a) matmul path for vortx.
+ *
+ * This is the boundary a vortx build binds instead of khal for GEMM, GEMV and the
+ * device-buffer plumbing around them.  Plain pointers and sizes only; every function
+ * returns a vx_status and never throws or aborts.  A context owns one CUDA stream and
+ * all work it is given is ordered on that stream and asynchronous until
+ * vx_synchronize / vx_download.  A context is not thread-safe; distinct contexts (one
+ * per GPU) may be driven from distinct threads.
+ *
+ * Each declaration names the reference interface it stands in for, by file:line in
+ * the vortx source tree (v0.3.0).
+ */
+#ifndef VORTX_B200_H
+#define VORTX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define VX_API
+#else
+#define VX_API __attribute__((visibility("default")))
+#endif
+
+typedef int32_t vx_status;
+enum {
+    VX_OK = 0,
+    VX_ERR_INVALID_ARGUMENT = 1, /* null pointer, zero/odd size, unknown enum value          */
+    VX_ERR_SHAPE = 2,            /* the shape checks of src/linalg/gemm.rs:70-104 failed      */
+    VX_ERR_OUT_OF_BOUNDS = 3,    /* a layout addresses elements beyond the stated capacity    */
+    VX_ERR_CUDA = 4,             /* a CUDA runtime / driver call failed (see vx_last_error)   */
+    VX_ERR_OUT_OF_MEMORY = 5,    /* cudaMalloc failed                                         */
+    VX_ERR_UNSUPPORTED = 6,      /* the requested kernel cannot take these operands           */
+    VX_ERR_DEVICE_TIMEOUT = 7,   /* a bounded device-side wait gave up; results are invalid   */
+    VX_ERR_NO_DEVICE = 8         /* no usable sm_100 device / driver                          */
+};
+
+/* Thread-local text of the last failure on this thread ("" if none). */
+VX_API const char* vx_last_error(void);
+VX_API const char* vx_version(void);
+
+/* ------------------------------------------------------------------ context ---- */
+/* Replaces khal's GpuBackend::Cuda(Cuda::new(ordinal)) — src/linalg/gemm.rs:353.   */
+typedef struct vx_context vx_context;
+
+VX_API vx_status vx_context_create(int32_t device, vx_context** out);
+/* Same, but work is ordered on a stream the caller owns (a cudaStream_t). */
+VX_API vx_status vx_context_create_on_stream(int32_t device, void* cuda_stream, vx_context** out);
+VX_API vx_status vx_context_destroy(vx_context* ctx);
+/* backend.synchronize() — src/linalg/gemm.rs:421, examples/gemm_bench.rs:77. */
+VX_API vx_status vx_synchronize(vx_context* ctx);
+VX_API vx_status vx_context_device(const vx_context* ctx, int32_t* device);
+VX_API vx_status vx_context_stream(const vx_context* ctx, void** cuda_stream);
+/* Number of kernels this context has launched since creation (copies excluded). */
+VX_API vx_status vx_context_launch_count(const vx_context* ctx, uint64_t* count);
+
+/* ------------------------------------------------------------------- memory ---- */
+/* backend.uninit_buffer(len, usage) — src/tensor/tensor_impl.rs:69.  cudaMalloc. */
+VX_API vx_status vx_alloc(vx_context* ctx, size_t bytes, void** device_ptr);
+VX_API vx_status vx_free(vx_context* ctx, void* device_ptr);
+/* backend.init_buffer(data, usage) / write_buffer(buf, offset, data) —
+ * src/tensor/tensor_impl.rs:105, :715; src/shapes.rs:581, :603.  Stream-ordered H2D. */
+VX_API vx_status vx_upload(vx_context* ctx, void* device_dst, const void* host_src, size_t bytes);
+/* backend.slow_read_buffer(buf, host) — src/linalg/gemm.rs:423-426.  Blocks until done. */
+VX_API vx_status vx_download(vx_context* ctx, void* host_dst, const void* device_src, size_t bytes);
+/* encoder.copy_buffer_to_buffer(src, src_off, dst, dst_off, len) —
+ * src/tensor/tensor_impl.rs:207-213.  Offsets are applied by the caller. */
+VX_API vx_status vx_copy(vx_context* ctx, void* device_dst, const void* device_src, size_t bytes);
+VX_API vx_status vx_memset(vx_context* ctx, void* device_dst, int value, size_t bytes);
+/* Page-locked host staging memory for uploads/downloads that should overlap. */
+VX_API vx_status vx_host_alloc(size_t bytes, void** host_ptr);
+VX_API vx_status vx_host_free(void* host_ptr);
+
+/* -------------------------------------------------------------------- shapes ---- */
+/* vortx-shaders/src/linalg/shape.rs:9-29 — the kernel-side shape, eight u32 in
+ * elements: sizes n,c,h,w (h = rows, w = columns) then the four strides. */
+typedef struct {
+    uint32_t n, c, h, w;
+    uint32_t n_stride, c_stride, h_stride, w_stride;
+} vx_shape;
+
+/* vortx-shaders/src/linalg/shape.rs:112-123 — passed by value, as push constants were
+ * meant to be; there is no uniform-buffer cache (src/shapes.rs:541-640 goes away). */
+typedef struct {
+    vx_shape out, lhs, rhs;
+} vx_shapes3;
+
+/* --------------------------------------------------------------------- GEMM ---- */
+typedef enum {
+    VX_GEMM_AUTO = 0,       /* Gemm::dispatch's rule — src/linalg/gemm.rs:111-118: the exact SIMT
+                               kernel; tiled when M >= 32 || N >= 32, else one thread per element */
+    VX_GEMM_NAIVE = 1,      /* gemm_naive — vortx-shaders/src/linalg/gemm.rs:197-237              */
+    VX_GEMM_SIMT_EXACT = 2, /* gemm_tiled — vortx-shaders/src/linalg/gemm.rs:41-194, bit for bit   */
+    VX_GEMM_TF32 = 3        /* tcgen05 tensor-core kernel, TF32 inputs, f32 accumulate; operands
+                               that TMA cannot address fall back to SIMT_EXACT                     */
+} vx_gemm_mode;
+
+/* The `.call(pass, grid, shapes.., out, lhs, rhs)` level — src/linalg/gemm.rs:131-151,
+ * :217-226, :276-285.  out = lhs * rhs for every (n, c) matrix pair; out is overwritten.
+ * Pointers are device pointers already advanced by the view offset
+ * (src/tensor/tensor_ref.rs:101-103).  cap_* are the element counts reachable from each
+ * pointer; a shape that reaches beyond them is refused with VX_ERR_OUT_OF_BOUNDS (pass 0
+ * to skip the check).  No shape-compatibility check is made at this level, as
+ * dispatch_naive / dispatch_tiled make none. */
+VX_API vx_status vx_gemm_f32(vx_context* ctx, vx_gemm_mode mode, float* out, const float* lhs,
+                             const float* rhs, const vx_shapes3* shapes, uint64_t cap_out,
+                             uint64_t cap_lhs, uint64_t cap_rhs);
+/* Which kernel the last vx_gemm_f32 on this context ran: 1 naive, 2 SIMT tiled (vector
+ * loads), 3 tcgen05 TF32, 4 SIMT tiled (generic strides). */
+VX_API vx_status vx_gemm_last_kernel(const vx_context* ctx, int32_t* kernel);
+
+/* ------------------------------------------------- block-quantised weights ---- */
+/* No reference counterpart: vortx has no quantised type.  Entry points follow the
+ * shape of its matrix-times-[K,1] use of Gemm::dispatch (src/linalg/gemm.rs:46, :373-387).
+ *
+ * Host block streams (what a caller holds): rows*cols/32 blocks, row after row.
+ *   Q8_0 block, 34 B: f16 d | int8 q[32]                 w[i]    = d * q[i]
+ *   Q4_0 block, 18 B: f16 d | u8 qs[16]                  w[i]    = d * ((qs[i] & 15) - 8)
+ *                                                        w[i+16] = d * ((qs[i] >> 4) - 8)
+ * Device form (vx_qweights): the same bytes split into a plane of quants (16-byte
+ * aligned rows) and a plane of scales, so every load is a full aligned vector. */
+typedef enum { VX_Q8_0 = 0, VX_Q4_0 = 1 } vx_qtype;
+typedef struct vx_qweights vx_qweights;
+
+VX_API size_t vx_qblock_bytes(vx_qtype t);
+/* Host quantisers.  cols % 32 == 0.  blocks receives rows*cols/32 * vx_qblock_bytes(t). */
+VX_API vx_status vx_quantize(vx_qtype t, const float* w, size_t rows, size_t cols, void* blocks);
+VX_API vx_status vx_dequantize_host(vx_qtype t, const void* blocks, size_t rows, size_t cols,
+                                    float* w);
+/* Upload a host block stream; rows x cols logical weights. */
+VX_API vx_status vx_qweights_upload(vx_context* ctx, vx_qtype t, const void* blocks, size_t rows,
+                                    size_t cols, vx_qweights** out);
+VX_API vx_status vx_qweights_free(vx_context* ctx, vx_qweights* w);
+VX_API vx_status vx_qweights_info(const vx_qweights* w, int32_t* qtype, size_t* rows, size_t* cols,
+                                  size_t* device_bytes);
+/* Device dequantisation into a row-major f32 matrix (rows*cols floats). */
+VX_API vx_status vx_dequantize(vx_context* ctx, const vx_qweights* w, float* device_out);
+/* y[v*y_stride + r] = sum_c W[r, c] * x[v*x_stride + c], v < batch, f32 accumulation.
+ * x and y are device pointers; strides in elements between batch vectors. */
+VX_API vx_status vx_gemv_q(vx_context* ctx, const vx_qweights* w, const float* x, size_t x_stride,
+                           float* y, size_t y_stride, size_t batch);
+/* Same, for a contiguous slab of rows [row0, row0+nrows): y receives nrows values per vector. */
+VX_API vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t row0, size_t nrows,
+                                const float* x, size_t x_stride, float* y, size_t y_stride,
+                                size_t batch);
+
+/* ----------------------------------------------------------------- tuning ---- */
+/* Integer knobs for experiments ("gemv.variant", "gemv.rows_per_warp", "gemm.tf32.stages"...).
+ * Unknown keys return VX_ERR_INVALID_ARGUMENT.  Defaults are the shipped configuration. */
+VX_API vx_status vx_set_option(vx_context* ctx, const char* key, int64_t value);
+VX_API vx_status vx_get_option(const vx_context* ctx, const char* key, int64_t* value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VORTX_B200_H */

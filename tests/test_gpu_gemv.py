@@ -1,0 +1,120 @@
+"""GPU parity of the Q8_0 / Q4_0 GEMV and dequantisation against the CPU oracle, through the C ABI.
+
+Bars: dequantised weights bit-exact; GEMV outputs within max relative error 1e-4, where the
+relative error of an output vector is max_i |y_i - t_i| / max_i |t_i| against the f64
+oracle t, and additionally every element within 2e-6 of its own conditioning sum |w||x|.
+"""
+import numpy as np
+import pytest
+
+import vortx_b200 as vb
+from vortx_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-4
+COND_TOL = 2e-6
+
+
+def _check(got, y64, absdot):
+    rel = np.abs(got - y64).max() / np.abs(y64).max()
+    cond = (np.abs(got - y64) / np.maximum(absdot, 1e-30)).max()
+    assert rel <= REL_TOL, rel
+    assert cond <= COND_TOL, cond
+    return rel
+
+
+def _run(backend, qt, blocks, rows, cols, x, **kw):
+    w = vb.QuantizedMatrix(backend, qt, blocks, rows, cols)
+    batch = x.shape[0]
+    xd = backend.init_buffer(x.ravel())
+    yd = backend.init_buffer(np.full(batch * rows, np.nan, np.float32))
+    vb.Gemv().dispatch(backend, None, yd, w, xd, batch=batch, **kw)
+    y = np.empty(batch * rows, np.float32)
+    backend.slow_read_buffer(yd, y)
+    w.free()
+    return y.reshape(batch, rows)
+
+
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("rows,cols", [(1, 32), (3, 64), (17, 96), (64, 256), (100, 1056), (513, 4096)])
+def test_dequant_bit_exact(backend, oracle, qt, rows, cols):
+    w = synth.normal_matrix(rows, cols, seed=rows + cols)
+    blocks = oracle.quantize(qt, w)
+    assert np.array_equal(blocks, vb.quantize(qt, w))  # product quantiser == oracle quantiser
+    want = oracle.dequantize(qt, blocks, rows, cols)
+    qm = vb.QuantizedMatrix(backend, qt, blocks, rows, cols)
+    out = backend.uninit_buffer(rows * cols)
+    qm.dequantize(out)
+    got = np.empty(rows * cols, np.float32)
+    backend.slow_read_buffer(out, got)
+    assert np.array_equal(got.view(np.uint32), want.ravel().view(np.uint32))
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("rows,cols,batch", [(1, 32, 1), (7, 96, 1), (33, 1056, 2), (257, 2048, 1),
+                                             (64, 256, 4), (130, 512, 8), (96, 4096, 3)])
+def test_gemv_small(backend, oracle, qt, rows, cols, batch, variant):
+    backend.set_option("gemv.variant", variant)
+    w = synth.normal_matrix(rows, cols, seed=11 * rows + cols)
+    x = synth.normal_vectors(batch, cols, seed=rows)
+    blocks = oracle.quantize(qt, w)
+    y64, absdot = oracle.gemv_f64(qt, blocks, rows, cols, x)
+    for rpw in (1, 2, 4):
+        backend.set_option("gemv.rows_per_warp", rpw)
+        got = _run(backend, qt, blocks, rows, cols, x)
+        _check(got, y64, absdot)
+    backend.set_option("gemv.rows_per_warp", 2)
+    backend.set_option("gemv.variant", 1)
+    # the f32 oracle itself sits within the same bar
+    _check(oracle.gemv(qt, blocks, rows, cols, x), y64, absdot)
+
+
+def test_gemv_q8_0_config1(backend, oracle):
+    """BASELINE config 1: Q8_0, W 4096x4096 ~ N(0, 0.02), x ~ N(0,1), seeds 0 and 1."""
+    rows = cols = 4096
+    w = synth.normal_matrix(rows, cols, seed=0)
+    x = synth.normal_vectors(1, cols, seed=1)
+    blocks = vb.quantize(vb.Q8_0, w)
+    y64, absdot = oracle.gemv_f64(vb.Q8_0, blocks, rows, cols, x)
+    _check(_run(backend, vb.Q8_0, blocks, rows, cols, x), y64, absdot)
+
+
+@pytest.mark.parametrize("batch", [1, 4, 8])
+def test_gemv_q4_0_config2(backend, oracle, batch):
+    """BASELINE config 2: Q4_0, W 8192x8192, batch 1/4/8."""
+    rows = cols = 8192
+    w = synth.normal_matrix(rows, cols, seed=0)
+    x = synth.normal_vectors(batch, cols, seed=1)
+    blocks = vb.quantize(vb.Q4_0, w)
+    y64, absdot = oracle.gemv_f64(vb.Q4_0, blocks, rows, cols, x)
+    _check(_run(backend, vb.Q4_0, blocks, rows, cols, x), y64, absdot)
+
+
+def test_gemv_row_slab_matches_full(backend, oracle):
+    """Row-sharded call (rows [r0, r0+n)) equals the matching slice of the full product."""
+    rows, cols = 448, 1024
+    w = synth.normal_matrix(rows, cols, seed=9)
+    x = synth.normal_vectors(1, cols, seed=10)
+    blocks = vb.quantize(vb.Q4_0, w)
+    full = _run(backend, vb.Q4_0, blocks, rows, cols, x)
+    part = _run(backend, vb.Q4_0, blocks, rows, cols, x, row0=112, nrows=224)
+    assert np.array_equal(part[0].view(np.uint32), full[0, 112:336].view(np.uint32))
+
+
+def test_gemv_linearity_full_size(backend):
+    """Size-independent property at the 28672x8192 shape: W(a x1 + b x2) = a W x1 + b W x2 (to rounding)."""
+    rows, cols = 28672, 8192
+    rng = np.random.Generator(np.random.Philox(42))
+    # random block stream directly (any bytes are valid Q4_0 once the scale is a sane f16)
+    nblocks = rows * cols // 32
+    blocks = rng.integers(0, 256, size=(nblocks, 18), dtype=np.uint8)
+    scales = (rng.random(nblocks, dtype=np.float32) * 0.01 + 0.001).astype(np.float16).view(np.uint16)
+    blocks[:, 0] = scales & 0xFF
+    blocks[:, 1] = scales >> 8
+    x1, x2 = synth.normal_vectors(2, cols, seed=7)
+    xs = np.stack([x1, x2, 2.0 * x1 - 0.5 * x2]).astype(np.float32)
+    y = _run(backend, vb.Q4_0, blocks.ravel(), rows, cols, xs)
+    lin = 2.0 * y[0].astype(np.float64) - 0.5 * y[1].astype(np.float64)
+    assert np.abs(y[2] - lin).max() / np.abs(lin).max() < 1e-5

@@ -1,0 +1,169 @@
+"""ctypes binding of libvortx_b200.so (the C ABI declared in include/vortx_b200*.h).
+
+The library is the product; there is no Python or CPU fallback.  If the shared object is
+missing, `load()` raises with the build command instead of degrading.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libvortx_b200.so"
+
+VX_OK = 0
+VX_ERR_INVALID_ARGUMENT = 1
+VX_ERR_SHAPE = 2
+VX_ERR_OUT_OF_BOUNDS = 3
+VX_ERR_CUDA = 4
+VX_ERR_OUT_OF_MEMORY = 5
+VX_ERR_UNSUPPORTED = 6
+VX_ERR_DEVICE_TIMEOUT = 7
+VX_ERR_NO_DEVICE = 8
+
+VX_GEMM_AUTO, VX_GEMM_NAIVE, VX_GEMM_SIMT_EXACT, VX_GEMM_TF32 = 0, 1, 2, 3
+VX_DISPATCH, VX_DISPATCH_NAIVE, VX_DISPATCH_TILED, VX_DISPATCH_TF32 = 0, 1, 2, 3
+VX_Q8_0, VX_Q4_0 = 0, 1
+
+
+class VxShape(C.Structure):
+    """vortx-shaders/src/linalg/shape.rs:9-29."""
+
+    _fields_ = [(n, C.c_uint32) for n in
+                ("n", "c", "h", "w", "n_stride", "c_stride", "h_stride", "w_stride")]
+
+    def astuple(self):
+        return tuple(getattr(self, f) for f, _ in self._fields_)
+
+
+class VxShapes3(C.Structure):
+    _fields_ = [("out", VxShape), ("lhs", VxShape), ("rhs", VxShape)]
+
+
+class VxLayout(C.Structure):
+    """src/shapes.rs:49-60."""
+
+    _fields_ = [("size", C.c_uint32 * 4), ("stride", C.c_uint32 * 4),
+                ("rank", C.c_uint32), ("offset", C.c_uint32)]
+
+
+class VortxError(RuntimeError):
+    """A non-zero vx_status; `.status` holds the code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"vortx_b200 status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+class ShapeMismatch(VortxError, AssertionError):
+    """VX_ERR_SHAPE — where the reference's assert_eq! would panic (src/linalg/gemm.rs:70-104)."""
+
+
+class LayoutError(VortxError, ValueError):
+    """VX_ERR_INVALID_ARGUMENT from the layout algebra — where the reference panics."""
+
+
+_P = C.c_void_p
+_LP = C.POINTER(VxLayout)
+_U32P = C.POINTER(C.c_uint32)
+
+# name -> (restype, argtypes).  Everything declared in include/vortx_b200.h and
+# include/vortx_b200_host.h is listed here; tests check the two stay in step.
+SIGNATURES = {
+    "vx_last_error": (C.c_char_p, []),
+    "vx_version": (C.c_char_p, []),
+    "vx_context_create": (C.c_int32, [C.c_int32, C.POINTER(_P)]),
+    "vx_context_create_on_stream": (C.c_int32, [C.c_int32, _P, C.POINTER(_P)]),
+    "vx_context_destroy": (C.c_int32, [_P]),
+    "vx_synchronize": (C.c_int32, [_P]),
+    "vx_context_device": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
+    "vx_context_stream": (C.c_int32, [_P, C.POINTER(_P)]),
+    "vx_context_launch_count": (C.c_int32, [_P, C.POINTER(C.c_uint64)]),
+    "vx_alloc": (C.c_int32, [_P, C.c_size_t, C.POINTER(_P)]),
+    "vx_free": (C.c_int32, [_P, _P]),
+    "vx_upload": (C.c_int32, [_P, _P, _P, C.c_size_t]),
+    "vx_download": (C.c_int32, [_P, _P, _P, C.c_size_t]),
+    "vx_copy": (C.c_int32, [_P, _P, _P, C.c_size_t]),
+    "vx_memset": (C.c_int32, [_P, _P, C.c_int, C.c_size_t]),
+    "vx_host_alloc": (C.c_int32, [C.c_size_t, C.POINTER(_P)]),
+    "vx_host_free": (C.c_int32, [_P]),
+    "vx_gemm_f32": (C.c_int32, [_P, C.c_int, _P, _P, _P, C.POINTER(VxShapes3),
+                                C.c_uint64, C.c_uint64, C.c_uint64]),
+    "vx_gemm_last_kernel": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
+    "vx_qblock_bytes": (C.c_size_t, [C.c_int]),
+    "vx_quantize": (C.c_int32, [C.c_int, _P, C.c_size_t, C.c_size_t, _P]),
+    "vx_dequantize_host": (C.c_int32, [C.c_int, _P, C.c_size_t, C.c_size_t, _P]),
+    "vx_qweights_upload": (C.c_int32, [_P, C.c_int, _P, C.c_size_t, C.c_size_t, C.POINTER(_P)]),
+    "vx_qweights_free": (C.c_int32, [_P, _P]),
+    "vx_qweights_info": (C.c_int32, [_P, C.POINTER(C.c_int32), C.POINTER(C.c_size_t),
+                                     C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "vx_dequantize": (C.c_int32, [_P, _P, _P]),
+    "vx_gemv_q": (C.c_int32, [_P, _P, _P, C.c_size_t, _P, C.c_size_t, C.c_size_t]),
+    "vx_gemv_q_rows": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t, _P, C.c_size_t, _P,
+                                   C.c_size_t, C.c_size_t]),
+    "vx_set_option": (C.c_int32, [_P, C.c_char_p, C.c_int64]),
+    "vx_get_option": (C.c_int32, [_P, C.c_char_p, C.POINTER(C.c_int64)]),
+    # host mirror
+    "vx_layout_contiguous": (C.c_int32, [_U32P, C.c_uint32, _LP]),
+    "vx_layout_to_shape": (C.c_int32, [_LP, C.POINTER(VxShape)]),
+    "vx_layout_canonicalize": (C.c_int32, [_LP, _LP]),
+    "vx_layout_unsqueeze_to_rank": (C.c_int32, [_LP, C.c_uint32, _LP]),
+    "vx_layout_unsqueeze": (C.c_int32, [_LP, C.c_uint32, _LP]),
+    "vx_layout_squeeze_axis": (C.c_int32, [_LP, C.c_uint32, _LP]),
+    "vx_layout_squeeze": (C.c_int32, [_LP, _LP]),
+    "vx_layout_index": (C.c_int32, [_LP, C.c_uint32, _LP]),
+    "vx_layout_transpose": (C.c_int32, [_LP, C.c_uint32, C.c_uint32, _LP]),
+    "vx_layout_transpose_last_dims": (C.c_int32, [_LP, _LP]),
+    "vx_layout_permute": (C.c_int32, [_LP, _U32P, _LP]),
+    "vx_layout_permute_ggml": (C.c_int32, [_LP, _U32P, _LP]),
+    "vx_layout_is_contiguous": (C.c_int32, [_LP]),
+    "vx_layout_broadcast": (C.c_int32, [_LP, _LP, _LP, _LP]),
+    "vx_layout_broadcast_assign": (C.c_int32, [_LP, _LP, _LP, _LP]),
+    "vx_layout_view": (C.c_int32, [_LP, C.c_uint32, _U32P, C.c_uint32, _U32P,
+                                   C.POINTER(C.c_uint8), C.c_uint32, _LP]),
+    "vx_layout_reshape": (C.c_int32, [_LP, _U32P, C.c_uint32, _LP]),
+    "vx_layout_narrow": (C.c_int32, [_LP, C.c_uint32, C.c_uint32, C.c_uint32, _LP]),
+    "vx_layout_matrix": (C.c_int32, [_LP, C.c_uint32, _LP]),
+    "vx_layout_columns": (C.c_int32, [_LP, C.c_uint32, C.c_uint32, _LP]),
+    "vx_layout_rows": (C.c_int32, [_LP, C.c_uint32, C.c_uint32, _LP]),
+    "vx_layout_f32_to_vec4": (C.c_int32, [_LP, _LP]),
+    "vx_layout_len": (C.c_uint64, [_LP]),
+    "vx_layout_span": (C.c_uint64, [_LP]),
+    "vx_gemm_dispatch": (C.c_int32, [_P, C.c_int, _P, _LP, C.c_uint64, _P, _LP, C.c_uint64,
+                                     _P, _LP, C.c_uint64]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the shared library once and types every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built. "
+            "Run `python -m vortx_b200.build` (needs nvcc); there is no fallback path.")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().vx_last_error().decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    """Raises the exception that corresponds to a non-zero status."""
+    if status == VX_OK:
+        return
+    msg = last_error()
+    if status == VX_ERR_SHAPE:
+        raise ShapeMismatch(status, msg)
+    raise VortxError(status, msg)

@@ -1,0 +1,249 @@
+// Context, stream-ordered memory and error plumbing of libvortx_b200.
+#include <cstring>
+#include <new>
+
+#include "vx_internal.h"
+
+namespace vx {
+
+static thread_local std::string g_last_error;
+
+vx_status fail(vx_status code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+void clear_error() { g_last_error.clear(); }
+
+int64_t option(const vx_context* ctx, const char* key, int64_t fallback) {
+    auto it = ctx->options.find(key);
+    return it == ctx->options.end() ? fallback : it->second;
+}
+
+static const char* const kKnownOptions[] = {
+    "gemv.variant",       // 0 = shipped kernel; other values select experimental variants
+    "gemv.rows_per_warp", // rows a warp carries at once
+    "gemv.block_threads", // CTA size of the GEMV kernels
+    "gemv.ctas_per_sm",   // persistent grid = SMs x this
+    "gemm.simt.force_generic",  // 1: always take the generic-stride SIMT kernel
+    "gemm.tf32.stages",   // TMA pipeline depth
+    "gemm.tf32.raster",   // tile rasterisation group height
+    "bounds_check",       // 1 (default): refuse layouts that reach beyond the stated capacity
+};
+
+static bool known_option(const char* key) {
+    for (const char* k : kKnownOptions)
+        if (std::strcmp(k, key) == 0) return true;
+    return false;
+}
+
+}  // namespace vx
+
+using vx::fail;
+
+extern "C" {
+
+const char* vx_last_error(void) { return vx::g_last_error.c_str(); }
+const char* vx_version(void) { return "vortx_b200 0.1 (sm_100a)"; }
+
+static vx_status create_context(int32_t device, void* stream, bool adopt, vx_context** out) {
+    VX_REQUIRE(out, VX_ERR_INVALID_ARGUMENT, "vx_context_create: out is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        (void)cudaGetLastError();
+        return fail(VX_ERR_NO_DEVICE, "no CUDA device available: %s",
+                    e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    }
+    VX_REQUIRE(device >= 0 && device < count, VX_ERR_INVALID_ARGUMENT,
+               "device ordinal %d out of range (0..%d)", device, count - 1);
+    vx::DeviceGuard guard(device);
+    cudaDeviceProp prop;
+    VX_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        return fail(VX_ERR_NO_DEVICE,
+                    "device %d is compute capability %d.%d; this library holds sm_100a code only",
+                    device, prop.major, prop.minor);
+    }
+    vx_context* ctx = new (std::nothrow) vx_context();
+    VX_REQUIRE(ctx, VX_ERR_OUT_OF_MEMORY, "host allocation failed");
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    ctx->cc_minor = prop.minor;
+    ctx->l2_bytes = (size_t)prop.l2CacheSize;
+    if (adopt) {
+        ctx->stream = (cudaStream_t)stream;
+        ctx->owns_stream = false;
+    } else {
+        cudaError_t se = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+        if (se != cudaSuccess) {
+            delete ctx;
+            return fail(VX_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(se));
+        }
+        ctx->owns_stream = true;
+    }
+    cudaError_t a1 = cudaMalloc(&ctx->d_status, sizeof(vx::DeviceStatus));
+    cudaError_t a2 = cudaMallocHost(&ctx->h_status, sizeof(vx::DeviceStatus));
+    if (a1 != cudaSuccess || a2 != cudaSuccess) {
+        if (ctx->d_status) cudaFree(ctx->d_status);
+        if (ctx->h_status) cudaFreeHost(ctx->h_status);
+        if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        (void)cudaGetLastError();
+        return fail(VX_ERR_OUT_OF_MEMORY, "could not allocate the context status word");
+    }
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(vx::DeviceStatus), ctx->stream);
+    std::memset(ctx->h_status, 0, sizeof(vx::DeviceStatus));
+    ctx->options["bounds_check"] = 1;
+    *out = ctx;
+    return VX_OK;
+}
+
+vx_status vx_context_create(int32_t device, vx_context** out) {
+    return create_context(device, nullptr, false, out);
+}
+
+vx_status vx_context_create_on_stream(int32_t device, void* cuda_stream, vx_context** out) {
+    return create_context(device, cuda_stream, true, out);
+}
+
+vx_status vx_context_destroy(vx_context* ctx) {
+    if (!ctx) return VX_OK;
+    vx::DeviceGuard guard(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    (void)cudaGetLastError();
+    delete ctx;
+    return VX_OK;
+}
+
+vx_status vx_synchronize(vx_context* ctx) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_synchronize: null context");
+    vx::DeviceGuard guard(ctx->device);
+    // Bring the device status word back with the stream, then look at it.
+    VX_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(vx::DeviceStatus),
+                            cudaMemcpyDeviceToHost, ctx->stream));
+    VX_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->h_status->code != 0) {
+        const uint32_t code = ctx->h_status->code, detail = ctx->h_status->detail;
+        cudaMemsetAsync(ctx->d_status, 0, sizeof(vx::DeviceStatus), ctx->stream);
+        cudaStreamSynchronize(ctx->stream);
+        return fail(VX_ERR_DEVICE_TIMEOUT,
+                    "a bounded device-side wait gave up (stage code %u, block %u); results of the "
+                    "affected kernel are invalid",
+                    code, detail);
+    }
+    return VX_OK;
+}
+
+vx_status vx_context_device(const vx_context* ctx, int32_t* device) {
+    VX_REQUIRE(ctx && device, VX_ERR_INVALID_ARGUMENT, "vx_context_device: null argument");
+    *device = ctx->device;
+    return VX_OK;
+}
+
+vx_status vx_context_stream(const vx_context* ctx, void** cuda_stream) {
+    VX_REQUIRE(ctx && cuda_stream, VX_ERR_INVALID_ARGUMENT, "vx_context_stream: null argument");
+    *cuda_stream = (void*)ctx->stream;
+    return VX_OK;
+}
+
+vx_status vx_context_launch_count(const vx_context* ctx, uint64_t* count) {
+    VX_REQUIRE(ctx && count, VX_ERR_INVALID_ARGUMENT, "vx_context_launch_count: null argument");
+    *count = ctx->launches;
+    return VX_OK;
+}
+
+vx_status vx_alloc(vx_context* ctx, size_t bytes, void** device_ptr) {
+    VX_REQUIRE(ctx && device_ptr, VX_ERR_INVALID_ARGUMENT, "vx_alloc: null argument");
+    *device_ptr = nullptr;
+    vx::DeviceGuard guard(ctx->device);
+    // A zero-length tensor (Tensor::with_capacity(0), an emptied vector) still needs a handle.
+    VX_CUDA(cudaMalloc(device_ptr, bytes ? bytes : 16));
+    return VX_OK;
+}
+
+vx_status vx_free(vx_context* ctx, void* device_ptr) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_free: null context");
+    if (!device_ptr) return VX_OK;
+    vx::DeviceGuard guard(ctx->device);
+    // Work queued on the stream may still use the buffer.
+    VX_CUDA(cudaStreamSynchronize(ctx->stream));
+    VX_CUDA(cudaFree(device_ptr));
+    return VX_OK;
+}
+
+vx_status vx_upload(vx_context* ctx, void* dst, const void* src, size_t bytes) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_upload: null context");
+    if (bytes == 0) return VX_OK;
+    VX_REQUIRE(dst && src, VX_ERR_INVALID_ARGUMENT, "vx_upload: null pointer");
+    vx::DeviceGuard guard(ctx->device);
+    VX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return VX_OK;
+}
+
+vx_status vx_download(vx_context* ctx, void* dst, const void* src, size_t bytes) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_download: null context");
+    if (bytes != 0) {
+        VX_REQUIRE(dst && src, VX_ERR_INVALID_ARGUMENT, "vx_download: null pointer");
+        vx::DeviceGuard guard(ctx->device);
+        VX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return vx_synchronize(ctx);
+}
+
+vx_status vx_copy(vx_context* ctx, void* dst, const void* src, size_t bytes) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_copy: null context");
+    if (bytes == 0) return VX_OK;
+    VX_REQUIRE(dst && src, VX_ERR_INVALID_ARGUMENT, "vx_copy: null pointer");
+    vx::DeviceGuard guard(ctx->device);
+    VX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return VX_OK;
+}
+
+vx_status vx_memset(vx_context* ctx, void* dst, int value, size_t bytes) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_memset: null context");
+    if (bytes == 0) return VX_OK;
+    VX_REQUIRE(dst, VX_ERR_INVALID_ARGUMENT, "vx_memset: null pointer");
+    vx::DeviceGuard guard(ctx->device);
+    VX_CUDA(cudaMemsetAsync(dst, value, bytes, ctx->stream));
+    return VX_OK;
+}
+
+vx_status vx_host_alloc(size_t bytes, void** host_ptr) {
+    VX_REQUIRE(host_ptr, VX_ERR_INVALID_ARGUMENT, "vx_host_alloc: null argument");
+    *host_ptr = nullptr;
+    VX_CUDA(cudaMallocHost(host_ptr, bytes ? bytes : 16));
+    return VX_OK;
+}
+
+vx_status vx_host_free(void* host_ptr) {
+    if (!host_ptr) return VX_OK;
+    VX_CUDA(cudaFreeHost(host_ptr));
+    return VX_OK;
+}
+
+vx_status vx_set_option(vx_context* ctx, const char* key, int64_t value) {
+    VX_REQUIRE(ctx && key, VX_ERR_INVALID_ARGUMENT, "vx_set_option: null argument");
+    VX_REQUIRE(vx::known_option(key), VX_ERR_INVALID_ARGUMENT, "unknown option '%s'", key);
+    ctx->options[key] = value;
+    return VX_OK;
+}
+
+vx_status vx_get_option(const vx_context* ctx, const char* key, int64_t* value) {
+    VX_REQUIRE(ctx && key && value, VX_ERR_INVALID_ARGUMENT, "vx_get_option: null argument");
+    VX_REQUIRE(vx::known_option(key), VX_ERR_INVALID_ARGUMENT, "unknown option '%s'", key);
+    *value = vx::option(ctx, key, 0);
+    return VX_OK;
+}
+
+}  // extern "C"

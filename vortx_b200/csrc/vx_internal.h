@@ -1,0 +1,103 @@
+// Internal declarations shared by the translation units of libvortx_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+
+#include "../../include/vortx_b200.h"
+#include "../../include/vortx_b200_host.h"
+
+namespace vx {
+
+// Records the message for vx_last_error() and returns `code`, so call sites can
+// `return fail(VX_ERR_..., "...")`.
+vx_status fail(vx_status code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+void clear_error();
+
+#define VX_CUDA(expr)                                                                      \
+    do {                                                                                   \
+        cudaError_t vx_e_ = (expr);                                                        \
+        if (vx_e_ != cudaSuccess) {                                                        \
+            (void)cudaGetLastError();                                                      \
+            return ::vx::fail(vx_e_ == cudaErrorMemoryAllocation ? VX_ERR_OUT_OF_MEMORY    \
+                                                                 : VX_ERR_CUDA,            \
+                              "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(vx_e_),   \
+                              __FILE__, __LINE__);                                         \
+        }                                                                                  \
+    } while (0)
+
+#define VX_REQUIRE(cond, code, ...)                      \
+    do {                                                 \
+        if (!(cond)) return ::vx::fail(code, __VA_ARGS__); \
+    } while (0)
+
+// Sets the context's device for the lifetime of the guard and restores the previous one.
+struct DeviceGuard {
+    int prev = -1;
+    bool changed = false;
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != device) {
+            changed = cudaSetDevice(device) == cudaSuccess;
+        }
+    }
+    ~DeviceGuard() {
+        if (changed) cudaSetDevice(prev);
+    }
+};
+
+// Status word the bounded device-side waits report into (tcgen05 GEMM pipeline).
+struct DeviceStatus {
+    uint32_t code;    // 0 ok; otherwise which wait gave up
+    uint32_t detail;  // block index that reported
+};
+
+}  // namespace vx
+
+struct vx_context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    size_t l2_bytes = 0;
+    uint64_t launches = 0;
+    int last_gemm_kernel = 0;
+    vx::DeviceStatus* d_status = nullptr;  // device
+    vx::DeviceStatus* h_status = nullptr;  // pinned host mirror
+    std::map<std::string, int64_t> options;
+};
+
+struct vx_qweights {
+    vx_qtype type;
+    size_t rows = 0, cols = 0;
+    size_t blocks_per_row = 0;
+    size_t quant_row_bytes = 0;   // bytes of quants per row (16 B per Q4_0 block, 32 B per Q8_0 block)
+    uint8_t* d_base = nullptr;    // one allocation: quants plane, then scales plane
+    uint8_t* d_quants = nullptr;  // rows * quant_row_bytes
+    uint16_t* d_scales = nullptr; // rows * blocks_per_row f16
+    size_t device_bytes = 0;
+    int device = 0;
+};
+
+namespace vx {
+
+int64_t option(const vx_context* ctx, const char* key, int64_t fallback);
+
+// SIMT kernels (vx_gemm_simt.cu)
+vx_status launch_gemm_naive(vx_context* ctx, float* out, const float* lhs, const float* rhs,
+                            const vx_shapes3& s);
+// Returns the kernel id it used in *kernel (2 vector, 4 generic).
+vx_status launch_gemm_simt_exact(vx_context* ctx, float* out, const float* lhs, const float* rhs,
+                                 const vx_shapes3& s, int* kernel);
+
+// tcgen05 kernel (vx_gemm_tf32.cu).  *eligible = false when the operands cannot be
+// described to TMA (strides, alignment, batch); nothing is launched then.
+vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const float* rhs,
+                           const vx_shapes3& s, bool* eligible);
+
+}  // namespace vx

@@ -1,0 +1,173 @@
+"""Gemm and the quantised GEMV — vortx's src/linalg/gemm.rs entry points over the CUDA kernels.
+
+`Gemm.dispatch / dispatch_naive / dispatch_tiled` keep the reference's argument order
+(backend, shapes, pass, out, lhs, rhs).  A shape mismatch raises ShapeMismatch (an
+AssertionError) where the reference's assert_eq! panics.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+
+from . import _lib
+from .backend import Backend, GpuBuffer, GpuPass
+from .shapes import TensorLayoutBuffers
+
+
+class MatrixMode:
+    """src/linalg/gemm.rs:11-32 (unused by dispatch, kept for call sites)."""
+
+    Normal = 0
+    Transposed = 1
+
+
+N = MatrixMode.Normal
+T = MatrixMode.Transposed
+
+_KERNEL_NAMES = {0: "none", 1: "naive", 2: "simt_tiled_vec", 3: "tcgen05_tf32", 4: "simt_tiled_generic"}
+
+
+class Gemm:
+    """src/linalg/gemm.rs:34-41.  `from_backend` mirrors khal's Shader derive."""
+
+    def __init__(self, backend: Optional[Backend] = None):
+        self.backend = backend
+
+    @classmethod
+    def from_backend(cls, backend: Backend) -> "Gemm":
+        return cls(backend)
+
+    def _go(self, kind: int, backend: Backend, out, lhs, rhs) -> None:
+        o = out.as_tensor_mut()
+        l = lhs.as_tensor_ref()
+        r = rhs.as_tensor_ref()
+        ob, lb, rb = o.raw_buffer(), l.raw_buffer(), r.raw_buffer()
+        for b in (ob, lb, rb):
+            if b.dtype != np.float32:
+                raise TypeError("Gemm takes f32 tensors")
+        st = _lib.load().vx_gemm_dispatch(
+            backend._ctx, kind,
+            ob.ptr, C.byref(o.layout()._c), ob.len(),
+            lb.ptr, C.byref(l.layout()._c), lb.len(),
+            rb.ptr, C.byref(r.layout()._c), rb.len())
+        _lib.check(st)
+
+    def dispatch(self, backend: Backend, shapes: TensorLayoutBuffers, pass_: GpuPass, out, lhs, rhs) -> None:
+        """src/linalg/gemm.rs:47-187"""
+        self._go(_lib.VX_DISPATCH, backend, out, lhs, rhs)
+
+    def dispatch_naive(self, backend, shapes, pass_, out, lhs, rhs) -> None:
+        """src/linalg/gemm.rs:190-246"""
+        self._go(_lib.VX_DISPATCH_NAIVE, backend, out, lhs, rhs)
+
+    def dispatch_tiled(self, backend, shapes, pass_, out, lhs, rhs) -> None:
+        """src/linalg/gemm.rs:249-305"""
+        self._go(_lib.VX_DISPATCH_TILED, backend, out, lhs, rhs)
+
+    def dispatch_tf32(self, backend, shapes, pass_, out, lhs, rhs) -> None:
+        """Same checks as dispatch, then the tcgen05 TF32 kernel (no reference counterpart)."""
+        self._go(_lib.VX_DISPATCH_TF32, backend, out, lhs, rhs)
+
+    @staticmethod
+    def last_kernel(backend: Backend) -> str:
+        k = C.c_int32()
+        _lib.check(_lib.load().vx_gemm_last_kernel(backend._ctx, C.byref(k)))
+        return _KERNEL_NAMES.get(k.value, str(k.value))
+
+
+# --------------------------------------------------------------------- quantised --------
+
+Q8_0 = _lib.VX_Q8_0
+Q4_0 = _lib.VX_Q4_0
+
+
+def quantize(qtype: int, w: np.ndarray) -> np.ndarray:
+    """Host quantiser: f32 [rows, cols] -> block stream (uint8)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    rows, cols = w.shape
+    lib = _lib.load()
+    out = np.empty(rows * (cols // 32) * lib.vx_qblock_bytes(qtype), dtype=np.uint8)
+    _lib.check(lib.vx_quantize(qtype, w.ctypes.data, rows, cols, out.ctypes.data))
+    return out
+
+
+def dequantize_host(qtype: int, blocks: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    out = np.empty((rows, cols), dtype=np.float32)
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    _lib.check(_lib.load().vx_dequantize_host(qtype, blocks.ctypes.data, rows, cols, out.ctypes.data))
+    return out
+
+
+class QuantizedMatrix:
+    """Device-resident Q8_0 / Q4_0 weights (vx_qweights)."""
+
+    def __init__(self, backend: Backend, qtype: int, blocks: np.ndarray, rows: int, cols: int):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        lib = _lib.load()
+        expect = rows * (cols // 32) * lib.vx_qblock_bytes(qtype)
+        if blocks.size != expect:
+            raise ValueError(f"block stream has {blocks.size} bytes, expected {expect}")
+        h = C.c_void_p()
+        _lib.check(lib.vx_qweights_upload(backend._ctx, qtype, blocks.ctypes.data, rows, cols, C.byref(h)))
+        self.backend, self.qtype, self.rows, self.cols = backend, qtype, rows, cols
+        self._h = h
+
+    @classmethod
+    def from_f32(cls, backend: Backend, qtype: int, w: np.ndarray) -> "QuantizedMatrix":
+        return cls(backend, qtype, quantize(qtype, w), w.shape[0], w.shape[1])
+
+    def stream_bytes(self) -> int:
+        return self.rows * (self.cols // 32) * _lib.load().vx_qblock_bytes(self.qtype)
+
+    def free(self) -> None:
+        if self._h and self.backend._ctx:
+            _lib.check(_lib.load().vx_qweights_free(self.backend._ctx, self._h))
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def dequantize(self, out: GpuBuffer) -> None:
+        if out.len() < self.rows * self.cols:
+            raise ValueError("dequantize destination too small")
+        _lib.check(_lib.load().vx_dequantize(self.backend._ctx, self._h, out.ptr))
+
+
+class Gemv:
+    """y = W x for block-quantised W; x and y are device vectors (batch of them, contiguous by default)."""
+
+    @classmethod
+    def from_backend(cls, backend: Backend) -> "Gemv":
+        return cls()
+
+    def dispatch(self, backend: Backend, pass_: Optional[GpuPass], y, w: QuantizedMatrix, x, batch: int = 1,
+                 x_stride: Optional[int] = None, y_stride: Optional[int] = None,
+                 row0: int = 0, nrows: Optional[int] = None) -> None:
+        nrows = w.rows - row0 if nrows is None else nrows
+        xs = w.cols if x_stride is None else x_stride
+        ys = nrows if y_stride is None else y_stride
+        xp, xl = _ptr_len(x)
+        yp, yl = _ptr_len(y)
+        if xl is not None and batch and (batch - 1) * xs + w.cols > xl:
+            raise IndexError("x is shorter than batch * cols")
+        if yl is not None and batch and (batch - 1) * ys + nrows > yl:
+            raise IndexError("y is shorter than batch * rows")
+        _lib.check(_lib.load().vx_gemv_q_rows(backend._ctx, w._h, row0, nrows, xp, xs, yp, ys, batch))
+
+
+def _ptr_len(t):
+    """Device pointer (with view offset) and remaining length of a Tensor / view / buffer / raw int."""
+    if isinstance(t, int):
+        return t, None
+    if isinstance(t, GpuBuffer):
+        return t.ptr, t.len()
+    if hasattr(t, "as_tensor_ref"):
+        v = t.as_tensor_ref()
+        sl = v.buffer()
+        return sl.ptr, sl.len()
+    raise TypeError(f"cannot take a device pointer from {type(t)!r}")
