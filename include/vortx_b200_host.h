@@ -31,9 +31,10 @@ VX_API vx_status vx_layout_contiguous(const uint32_t* size, uint32_t rank, vx_la
 VX_API vx_status vx_layout_to_shape(const vx_layout* l, vx_shape* out);
 /* src/shapes.rs:145-155 — pads to rank 4 with ones on the left; the offset is dropped. */
 VX_API vx_status vx_layout_canonicalize(const vx_layout* l, vx_layout* out);
-/* src/shapes.rs:115-141 */
+/* src/shapes.rs:115-141 — VX_ERR_UNSUPPORTED where the reference returns None. */
 VX_API vx_status vx_layout_unsqueeze_to_rank(const vx_layout* l, uint32_t rank, vx_layout* out);
-/* src/shapes.rs:161-175 */
+/* src/shapes.rs:161-175 — VX_ERR_UNSUPPORTED where the reference returns None (rank already 4,
+ * axis > rank); axis 3 makes the reference index stride[4] and panic: VX_ERR_INVALID_ARGUMENT. */
 VX_API vx_status vx_layout_unsqueeze(const vx_layout* l, uint32_t axis, vx_layout* out);
 /* src/shapes.rs:177-200 */
 VX_API vx_status vx_layout_squeeze_axis(const vx_layout* l, uint32_t axis, vx_layout* out);

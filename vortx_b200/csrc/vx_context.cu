@@ -26,7 +26,10 @@ int64_t option(const vx_context* ctx, const char* key, int64_t fallback) {
 }
 
 static const char* const kKnownOptions[] = {
-    "gemv.variant",       // 0 = shipped kernel; other values select experimental variants
+    "gemv.variant",       // 2 (default) = TMA streaming kernel; 0 / 1 = register-staged kernels
+    "gemv.stages",        // ring depth of the streaming kernel (0 = as many as fit)
+    "gemv.tile_rows",     // rows per TMA tile of the streaming kernel: 8 (default) or 4
+    "gemv.pdl",           // 1 (default): launch the streaming kernel with programmatic dependent launch
     "gemv.rows_per_warp", // rows a warp carries at once
     "gemv.block_threads", // CTA size of the GEMV kernels
     "gemv.ctas_per_sm",   // persistent grid = SMs x this
@@ -129,10 +132,15 @@ vx_status vx_context_destroy(vx_context* ctx) {
 vx_status vx_synchronize(vx_context* ctx) {
     VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_synchronize: null context");
     vx::DeviceGuard guard(ctx->device);
-    // Bring the device status word back with the stream, then look at it.
+    if (!ctx->status_dirty) {
+        VX_CUDA(cudaStreamSynchronize(ctx->stream));
+        return VX_OK;
+    }
+    // A kernel with bounded device-side waits ran: bring its status word back with the stream.
     VX_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(vx::DeviceStatus),
                             cudaMemcpyDeviceToHost, ctx->stream));
     VX_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->status_dirty = false;
     if (ctx->h_status->code != 0) {
         const uint32_t code = ctx->h_status->code, detail = ctx->h_status->detail;
         cudaMemsetAsync(ctx->d_status, 0, sizeof(vx::DeviceStatus), ctx->stream);

@@ -1,0 +1,430 @@
+// Streaming GEMV for block-quantised weights: TMA-fed, x-stationary, integer dot products.
+//
+// Shape of the kernel (8 consumer warps + 1 producer warp + 1 epilogue warp per CTA):
+//   * The producer thread streams tiles of TR consecutive rows (their quants, and their f16
+//     scales) from HBM into a ring of shared-memory stages with untiled TMA bulk copies,
+//     completion counted on one mbarrier per stage.  Bytes in flight are set by the ring,
+//     not by registers or occupancy.
+//   * Every consumer thread owns the same 16-byte chunk position(s) of every row (32 Q4_0
+//     weights or 16 Q8_0 weights) and keeps the matching slice of x in registers for the whole
+//     kernel, so x is read from memory once per CTA and never touches shared memory.
+//   * x is held as fixed point: per chunk, x_i = sx * X_i with |X_i| < 2^23, and X_i split into
+//     three byte planes (signed high, unsigned middle and low).  A chunk-row product is then
+//     6 (Q4_0: 24, Q8_0: 12) dp4a on the raw quants — exact integer arithmetic — followed by
+//     one f32 multiply-add with d * sx.  The rounding of x to 24 bits relative to the chunk
+//     maximum is of the order of one f32 ulp, and the block sums are exact, so the result is at
+//     least as accurate as an f32-accumulated product.  The "- 8" of Q4_0 is folded into the
+//     initial value of the integer accumulators (-8 * sum of the digits).
+//   * Per tile, the TR partial sums per thread are combined with a transposed shuffle
+//     reduction (values halve as lanes pair up); each warp then drops its partials into a small
+//     shared-memory buffer and signals an mbarrier.  A tenth warp adds the warps' partials and
+//     writes y, so the consumer warps never meet at a CTA barrier.
+// No scratch memory in global memory, no split along K, every weight byte read once.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "vx_internal.h"
+#include "vx_sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kConsumers = 256;
+constexpr int kThreads = kConsumers + 64;  // + producer warp + epilogue warp
+constexpr int kWarps = kConsumers / 32;
+constexpr int kRedBufs = 4;                // partial-sum buffers between consumers and the epilogue warp
+
+struct StreamParams {
+    const uint8_t* quants;
+    const uint8_t* scales;  // f16 plane, addressed in bytes
+    uint32_t nchunks;       // 16-byte chunks per row
+    uint32_t nb;            // blocks per row
+    uint64_t row0;
+    uint32_t nrows;
+    const float* x;
+    float* y;
+    uint32_t tpr;           // threads per row group (multiple of 32)
+    uint32_t stages;
+    uint32_t stage_bytes;
+    uint32_t q_stage_bytes;  // TR * row bytes: where the scales start inside a stage
+    uint32_t x_vec;          // x is 16-byte aligned
+    vx::DeviceStatus* status;
+};
+
+__device__ __forceinline__ void report(vx::DeviceStatus* st, uint32_t code) {
+    if (atomicCAS(&st->code, 0u, code) == 0u) st->detail = blockIdx.x;
+}
+
+template <int NR>
+__device__ __forceinline__ float transposed_reduce(float (&v)[NR], uint32_t lane) {
+    // After the call lane l holds the full warp sum of v[row(l)], where row(l) is read off the
+    // lane's high bits: NR = 8 -> bits 4,3,2; NR = 4 -> bits 4,3; NR = 2 -> bit 4; NR = 1 -> none.
+    int off = 16;
+#pragma unroll
+    for (int n = NR; n > 1; n >>= 1, off >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float send = upper ? v[i] : v[i + n / 2];
+            const float keep = upper ? v[i + n / 2] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+    float r = v[0];
+    for (; off > 0; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+    return r;
+}
+
+// QT: 0 = Q8_0 (16 weights per 16-byte chunk), 1 = Q4_0 (32 weights per chunk).
+// CPT: chunk positions per thread.  RP: row groups working side by side.  TR: rows per tile.
+template <int QT, int CPT, int RP, int TR>
+__global__ void __launch_bounds__(kThreads, 1)
+gemv_stream_kernel(const StreamParams p) {
+    constexpr int W = QT == 1 ? 32 : 16;
+    constexpr int DR = W / 4;   // registers per digit plane per chunk
+    constexpr int NR = TR / RP; // rows per thread per tile
+    static_assert(TR % RP == 0 && NR >= 1 && NR <= 8, "bad tile split");
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    float* red = reinterpret_cast<float*>(smem + (size_t)p.stages * p.stage_bytes);  // [kRedBufs][TR][kWarps]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + kRedBufs * TR * kWarps);
+    // full[S], empty[S], red_full[kRedBufs], red_empty[kRedBufs]
+    const uint32_t bar0 = smem_addr(bars);
+    auto full = [&](uint32_t s) { return bar0 + 8u * s; };
+    auto empty = [&](uint32_t s) { return bar0 + 8u * (p.stages + s); };
+    auto red_full = [&](uint32_t b) { return bar0 + 8u * (2 * p.stages + b); };
+    auto red_empty = [&](uint32_t b) { return bar0 + 8u * (2 * p.stages + kRedBufs + b); };
+
+    const uint32_t tid = threadIdx.x;
+    // Programmatic dependent launch: let the next kernel in the stream start its own prologue
+    // as soon as this grid's CTAs are all under way.  Nothing here depends on that kernel.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), kWarps);
+        }
+        for (uint32_t b = 0; b < kRedBufs; ++b) {
+            mbar_init(red_full(b), kWarps);
+            mbar_init(red_empty(b), 1);
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const uint32_t tiles = (p.nrows + TR - 1) / TR;
+    const uint32_t row_bytes = p.nchunks * 16;
+
+    const uint32_t wpr = p.tpr >> 5;  // warps per row group
+
+    if (tid >= kConsumers + 32) {
+        // ---------------------------------------------------------------- epilogue ----
+        const uint32_t lane = tid & 31;
+        // y may still be read by the previous kernel in the stream: write it only once that
+        // kernel has completed.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        uint32_t k = 0;
+        for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
+            const uint32_t b = k % kRedBufs;
+            if (!mbar_wait(red_full(b), (k / kRedBufs) & 1)) report(p.status, 14);
+            const float* slot = red + (size_t)b * TR * kWarps;
+            const uint32_t row = t * TR + lane;
+            if (lane < (uint32_t)TR && row < p.nrows) {
+                float sum = 0.0f;
+                for (uint32_t wv = 0; wv < wpr; ++wv) sum += slot[lane * kWarps + wv];
+                p.y[row] = sum;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(red_empty(b));
+        }
+        return;
+    }
+    if (tid >= kConsumers) {
+        // ---------------------------------------------------------------- producer ----
+        if (tid == kConsumers) {
+            const uint64_t policy = policy_evict_first();
+            uint32_t k = 0;
+            for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
+                const uint32_t s = k % p.stages, use = k / p.stages;
+                if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1)) report(p.status, 11);
+                const uint32_t tr = min((uint32_t)TR, p.nrows - t * TR);
+                const uint64_t first = p.row0 + (uint64_t)t * TR;
+                const uint32_t qbytes = tr * row_bytes;
+                const uint64_t soff = first * p.nb * 2;
+                const uint64_t salign = soff & ~(uint64_t)15;
+                const uint32_t sbytes = (uint32_t)(((soff - salign) + (uint64_t)tr * p.nb * 2 + 15) & ~(uint64_t)15);
+                const uint32_t dst = smem_addr(smem + (size_t)s * p.stage_bytes);
+                mbar_arrive_expect_tx(full(s), qbytes + sbytes);
+                bulk_g2s_hint(dst, p.quants + first * row_bytes, qbytes, full(s), policy);
+                bulk_g2s_hint(dst + p.q_stage_bytes, p.scales + salign, sbytes, full(s), policy);
+            }
+            // Do not leave while copies into this CTA's shared memory are still in flight:
+            // wait until the consumers have released the last use of every stage.
+            for (uint32_t s = 0; s < p.stages && s < k; ++s) {
+                const uint32_t last_k = ((k - 1 - s) / p.stages) * p.stages + s;  // last tile index on stage s
+                if (!mbar_wait(empty(s), (last_k / p.stages) & 1)) report(p.status, 12);
+            }
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers ----
+    const uint32_t lane = tid & 31, warp = tid >> 5;
+    const uint32_t rp = warp / wpr;           // this warp's row group
+    const bool active = rp < (uint32_t)RP;
+    const uint32_t tc = tid - rp * p.tpr;     // position inside the group
+
+    // x may be the output of the previous kernel in the stream: wait for it (the producer
+    // warp is already streaming weights, which no kernel writes).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // x -> three byte planes per chunk, kept in registers.
+    uint32_t DA[CPT][DR], DB[CPT][DR], DC[CPT][DR];
+    float sxs[CPT];
+    int initA[CPT], initB[CPT], initC[CPT];
+    uint32_t chunk[CPT];
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) {
+        const uint32_t c = tc + j * p.tpr;
+        const bool valid = active && c < p.nchunks;
+        chunk[j] = valid ? c : 0;
+        float xv[W];
+        if (valid) {
+            const float* src = p.x + (size_t)c * W;
+            if (p.x_vec) {
+#pragma unroll
+                for (int i = 0; i < W / 4; ++i) {
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(src) + i);
+                    xv[4 * i + 0] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < W; ++i) xv[i] = __ldg(src + i);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < W; ++i) xv[i] = 0.0f;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < W; ++i) amax = fmaxf(amax, fabsf(xv[i]));
+        // |x * inv| <= 8388606.5 before rounding, so X stays within 24 signed bits without a clamp.
+        const float inv = amax > 0.0f ? 8388606.0f / amax : 0.0f;
+        sxs[j] = valid ? amax / 8388606.0f : 0.0f;
+        int sa = 0, sb = 0, sc = 0;
+#pragma unroll
+        for (int r = 0; r < DR; ++r) {
+            const uint32_t X0 = (uint32_t)__float2int_rn(xv[4 * r + 0] * inv);
+            const uint32_t X1 = (uint32_t)__float2int_rn(xv[4 * r + 1] * inv);
+            const uint32_t X2 = (uint32_t)__float2int_rn(xv[4 * r + 2] * inv);
+            const uint32_t X3 = (uint32_t)__float2int_rn(xv[4 * r + 3] * inv);
+            // byte n of each X gathered into one register: n = 2 signed high, 1 middle, 0 low
+            DA[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0062), __byte_perm(X2, X3, 0x0062), 0x5410);
+            DB[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0051), __byte_perm(X2, X3, 0x0051), 0x5410);
+            DC[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0040), __byte_perm(X2, X3, 0x0040), 0x5410);
+            sa = dp4a_ss(0x01010101u, DA[j][r], sa);
+            sb = dp4a_su(0x01010101u, DB[j][r], sb);
+            sc = dp4a_su(0x01010101u, DC[j][r], sc);
+        }
+        initA[j] = QT == 1 ? -8 * sa : 0;
+        initB[j] = QT == 1 ? -8 * sb : 0;
+        initC[j] = QT == 1 ? -8 * sc : 0;
+    }
+
+    uint32_t k = 0;
+    for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
+        const uint32_t s = k % p.stages;
+        if (!mbar_wait(full(s), (k / p.stages) & 1)) report(p.status, 13);
+        const uint8_t* sq = smem + (size_t)s * p.stage_bytes;
+        const uint64_t soff = (p.row0 + (uint64_t)t * TR) * p.nb * 2;
+        const uint8_t* ss = sq + p.q_stage_bytes + (uint32_t)(soff & 15);
+
+        float acc[NR];
+#pragma unroll
+        for (int i = 0; i < NR; ++i) acc[i] = 0.0f;
+
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) {
+                const uint32_t c = chunk[j];
+                const uint32_t blk = QT == 1 ? c : (c >> 1);
+                // All shared-memory reads of the tile first, so that the integer chains of the
+                // NR rows can overlap.
+                uint4 q[NR];
+                uint16_t dh[NR];
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    const uint32_t r = rp + i * RP;  // row inside the tile
+                    q[i] = *reinterpret_cast<const uint4*>(sq + ((size_t)r * p.nchunks + c) * 16);
+                    dh[i] = *reinterpret_cast<const uint16_t*>(ss + ((size_t)r * p.nb + blk) * 2);
+                }
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+                    int sa = initA[j], sb = initB[j], sc = initC[j];
+                    if (QT == 1) {
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            const uint32_t lo = w[m] & 0x0F0F0F0Fu, hi = (w[m] >> 4) & 0x0F0F0F0Fu;
+                            sa = dp4a_ss(lo, DA[j][m], sa);
+                            sb = dp4a_su(lo, DB[j][m], sb);
+                            sc = dp4a_su(lo, DC[j][m], sc);
+                            sa = dp4a_ss(hi, DA[j][4 + m], sa);
+                            sb = dp4a_su(hi, DB[j][4 + m], sb);
+                            sc = dp4a_su(hi, DC[j][4 + m], sc);
+                        }
+                    } else {
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            sa = dp4a_ss(w[m], DA[j][m], sa);
+                            sb = dp4a_su(w[m], DB[j][m], sb);
+                            sc = dp4a_su(w[m], DC[j][m], sc);
+                        }
+                    }
+                    // sum q X = 65536 sa + 256 sb + sc; |256 sb + sc| < 2^31 for both formats.
+                    const float tsum = fmaf((float)sa, 65536.0f, (float)(sb * 256 + sc));
+                    const float d = __half2float(__ushort_as_half(dh[i]));
+                    acc[i] = fmaf(d * sxs[j], tsum, acc[i]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty(s));  // this warp has finished reading the stage
+
+        const float total = transposed_reduce<NR>(acc, lane);
+        const uint32_t b = k % kRedBufs;
+        if (k >= kRedBufs && !mbar_wait(red_empty(b), ((k / kRedBufs) - 1) & 1)) report(p.status, 15);
+        float* slot = red + (size_t)b * TR * kWarps;
+        if (active) {
+            // lanes whose low bits are zero hold one row each
+            constexpr uint32_t low_mask = NR == 8 ? 3u : NR == 4 ? 7u : NR == 2 ? 15u : 31u;
+            if ((lane & low_mask) == 0) {
+                const uint32_t i = NR == 8 ? (((lane >> 4) & 1u) * 4 + ((lane >> 3) & 1u) * 2 + ((lane >> 2) & 1u))
+                                 : NR == 4 ? (((lane >> 4) & 1u) * 2 + ((lane >> 3) & 1u))
+                                 : NR == 2 ? ((lane >> 4) & 1u) : 0u;
+                slot[(rp + i * RP) * kWarps + (warp - rp * wpr)] = total;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(red_full(b));
+    }
+}
+
+template <int QT, int CPT, int RP, int TR>
+vx_status launch_one(vx_context* ctx, const StreamParams& p, dim3 grid, size_t smem) {
+    auto kernel = gemv_stream_kernel<QT, CPT, RP, TR>;
+    // Raise the dynamic shared-memory limit once per device and kernel instance.
+    static size_t granted[64] = {};
+    const int dev = ctx->device & 63;
+    if (granted[dev] < smem) {
+        VX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        granted[dev] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 ? 1 : 0;
+    VX_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    return VX_OK;
+}
+
+template <int QT, int TR>
+vx_status launch_qt(vx_context* ctx, int cpt, int rp, const StreamParams& p, dim3 grid, size_t smem) {
+    if (cpt == 1) {
+        switch (rp) {
+            case 1: return launch_one<QT, 1, 1, TR>(ctx, p, grid, smem);
+            case 2: return launch_one<QT, 1, 2, TR>(ctx, p, grid, smem);
+            default: return launch_one<QT, 1, 4, TR>(ctx, p, grid, smem);
+        }
+    }
+    if (cpt == 2) return launch_one<QT, 2, 1, TR>(ctx, p, grid, smem);
+    return launch_one<QT, 4, 1, TR>(ctx, p, grid, smem);
+}
+
+}  // namespace
+
+namespace vx {
+
+// One vector (batch 1).  *eligible = false (nothing launched) when the row is too long for
+// the shared-memory ring or the register-resident x.
+vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
+                             const float* x, float* y, bool* eligible) {
+    const uint32_t TR = option(ctx, "gemv.tile_rows", 8) == 4 ? 4 : 8;
+    *eligible = false;
+    const uint32_t nb = (uint32_t)w->blocks_per_row;
+    const uint32_t nchunks = (uint32_t)(w->quant_row_bytes / 16);
+    if (nchunks > 4 * kConsumers) return VX_OK;
+    const int cpt = nchunks <= kConsumers ? 1 : nchunks <= 2 * kConsumers ? 2 : 4;
+    uint32_t tpr = ((nchunks + cpt - 1) / cpt + 31) / 32 * 32;
+    tpr = std::min<uint32_t>(tpr, kConsumers);
+    int rp = 1;
+    if (cpt == 1) {
+        const uint32_t fit = kConsumers / tpr;  // 1..8
+        rp = fit >= 4 ? 4 : fit >= 2 ? 2 : 1;
+    }
+
+    const uint32_t q_stage = TR * nchunks * 16;
+    const uint32_t s_stage = (TR * nb * 2 + 32 + 15) / 16 * 16;
+    const uint32_t stage_bytes = (q_stage + s_stage + 127) / 128 * 128;
+    const size_t fixed = kRedBufs * TR * kWarps * sizeof(float) + (2 * 16 + 2 * kRedBufs) * sizeof(uint64_t);
+    const uint32_t tiles = (nrows + TR - 1) / TR;
+    // Measured on B200: two CTAs per SM pay off once every CTA slot streams many tiles; short
+    // launches do better with one CTA per SM, which also balances their few tiles better.  The
+    // ring stays at two stages by default so that a CTA takes well under half of the SM's
+    // shared memory: the next kernel of a dependent-launch chain can then become resident and
+    // prefetch its first tiles while this one is still running.
+    int64_t per_sm = option(ctx, "gemv.ctas_per_sm", 0);
+    if (per_sm <= 0) per_sm = tiles >= 16u * (uint32_t)ctx->sm_count ? 2 : 1;
+    per_sm = std::min<int64_t>(per_sm, 4);
+    const size_t budget = (size_t)(200 * 1024) / (size_t)per_sm - fixed;
+    int64_t want_stages = option(ctx, "gemv.stages", 0);
+    if (want_stages <= 0) want_stages = 2;
+    uint32_t stages = (uint32_t)std::min<size_t>(16, budget / stage_bytes);
+    stages = std::min<uint32_t>(stages, (uint32_t)want_stages);
+    if (stages < 2) {
+        // a long row: give one CTA the whole SM
+        per_sm = 1;
+        stages = (uint32_t)std::min<size_t>(2, ((size_t)(227 * 1024) - 1024 - fixed) / stage_bytes);
+        if (stages < 2) return VX_OK;
+    }
+
+    StreamParams p;
+    p.quants = w->d_quants;
+    p.scales = reinterpret_cast<const uint8_t*>(w->d_scales);
+    p.nchunks = nchunks;
+    p.nb = nb;
+    p.row0 = row0;
+    p.nrows = nrows;
+    p.x = x;
+    p.y = y;
+    p.tpr = tpr;
+    p.stages = stages;
+    p.stage_bytes = stage_bytes;
+    p.q_stage_bytes = q_stage;
+    p.x_vec = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 ? 1u : 0u;
+    p.status = ctx->d_status;
+
+    const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * per_sm);
+    dim3 grid(std::min(tiles, slots));
+    const size_t smem = (size_t)stages * stage_bytes + fixed;
+    vx_status st;
+    if (TR == 8)
+        st = w->type == VX_Q4_0 ? launch_qt<1, 8>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 8>(ctx, cpt, rp, p, grid, smem);
+    else
+        st = w->type == VX_Q4_0 ? launch_qt<1, 4>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 4>(ctx, cpt, rp, p, grid, smem);
+    if (st != VX_OK) return st;
+    ctx->launches++;
+    ctx->status_dirty = true;
+    *eligible = true;
+    return VX_OK;
+}
+
+}  // namespace vx

@@ -69,6 +69,7 @@ struct vx_context {
     int last_gemm_kernel = 0;
     vx::DeviceStatus* d_status = nullptr;  // device
     vx::DeviceStatus* h_status = nullptr;  // pinned host mirror
+    bool status_dirty = false;             // a kernel that may write d_status ran since the last check
     std::map<std::string, int64_t> options;
 };
 
@@ -99,5 +100,10 @@ vx_status launch_gemm_simt_exact(vx_context* ctx, float* out, const float* lhs, 
 // described to TMA (strides, alignment, batch); nothing is launched then.
 vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const float* rhs,
                            const vx_shapes3& s, bool* eligible);
+
+// Streaming GEMV (vx_gemv_stream.cu), one vector.  *eligible = false when the row shape does
+// not fit its shared-memory ring or register-resident x; nothing is launched then.
+vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
+                             const float* x, float* y, bool* eligible);
 
 }  // namespace vx

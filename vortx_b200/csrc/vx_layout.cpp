@@ -79,7 +79,8 @@ vx_status vx_layout_canonicalize(const vx_layout* l, vx_layout* out) {
 
 vx_status vx_layout_unsqueeze_to_rank(const vx_layout* l, uint32_t rank, vx_layout* out) {
     VX_REQUIRE(valid(l) && out, VX_ERR_INVALID_ARGUMENT, "vx_layout_unsqueeze_to_rank: bad argument");
-    VX_REQUIRE(rank <= 4 && rank >= l->rank, VX_ERR_INVALID_ARGUMENT,
+    // The reference returns None here, not a panic.
+    VX_REQUIRE(rank <= 4 && rank >= l->rank, VX_ERR_UNSUPPORTED,
                "cannot unsqueeze rank %u to rank %u", l->rank, rank);
     vx_layout r = *l;
     if (l->rank == rank) {
@@ -102,8 +103,11 @@ vx_status vx_layout_unsqueeze_to_rank(const vx_layout* l, uint32_t rank, vx_layo
 
 vx_status vx_layout_unsqueeze(const vx_layout* l, uint32_t axis, vx_layout* out) {
     VX_REQUIRE(valid(l) && out, VX_ERR_INVALID_ARGUMENT, "vx_layout_unsqueeze: bad argument");
-    VX_REQUIRE(l->rank < 4 && axis <= l->rank, VX_ERR_INVALID_ARGUMENT,
+    // The reference returns None here, not a panic.
+    VX_REQUIRE(l->rank < 4 && axis <= l->rank, VX_ERR_UNSUPPORTED,
                "Not enough rank available for unsqueezing (rank %u, axis %u)", l->rank, axis);
+    // Appending an axis to a rank-3 layout reads stride[4] in the reference and panics there.
+    VX_REQUIRE(axis < 3, VX_ERR_INVALID_ARGUMENT, "unsqueeze at axis 3 indexes past the stride array");
     vx_layout r = *l;
     for (int i = 2; i >= (int)axis; --i) {
         r.size[i + 1] = r.size[i];

@@ -354,7 +354,7 @@ vx_status launch_q8(vx_context* ctx, dim3 grid, dim3 block, size_t smem, const v
 template <int B>
 vx_status launch_batch(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
                        const float* x, size_t x_stride, float* y, size_t y_stride) {
-    const int variant = (int)vx::option(ctx, "gemv.variant", 1);
+    const int variant = vx::option(ctx, "gemv.variant", 1) == 0 ? 0 : 1;
     int rpw = (int)vx::option(ctx, "gemv.rows_per_warp", 2);
     if (B >= 4) rpw = 1;  // keep the accumulators in registers
     const int threads = (int)vx::option(ctx, "gemv.block_threads", 256);
@@ -575,6 +575,24 @@ vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t row0, siz
                "batch strides (x %zu, y %zu) shorter than the vectors (%zu, %zu)", x_stride, y_stride,
                w->cols, nrows);
     vx::DeviceGuard guard(ctx->device);
+
+    // Default: the TMA-fed streaming kernel, one launch per vector (weights of the later
+    // vectors come out of L2 when the matrix fits there).  "gemv.variant" 0 / 1 select the
+    // register-staged kernels below, which also take over when a row does not fit the ring.
+    if (vx::option(ctx, "gemv.variant", 2) == 2) {
+        size_t v = 0;
+        for (; v < batch; ++v) {
+            bool eligible = false;
+            vx_status st = vx::launch_gemv_stream(ctx, w, row0, (uint32_t)nrows, x + v * x_stride,
+                                                  y + v * y_stride, &eligible);
+            if (st != VX_OK) return st;
+            if (!eligible) break;
+        }
+        if (v == batch) return VX_OK;
+        x += v * x_stride;
+        y += v * y_stride;
+        batch -= v;
+    }
 
     // Shared memory bounds how many x vectors one launch can stage.
     const size_t per_vec = w->blocks_per_row * (8 * sizeof(float4) + sizeof(float));

@@ -104,17 +104,20 @@ class TensorLayout:
     def canonicalize(self) -> "TensorLayout":
         return self._call("vx_layout_canonicalize")
 
-    def unsqueeze_to_rank(self, rank: int) -> Optional["TensorLayout"]:
+    def _call_optional(self, name: str, *args) -> Optional["TensorLayout"]:
+        """For the reference functions that return Option: None on VX_ERR_UNSUPPORTED."""
         try:
-            return self._call("vx_layout_unsqueeze_to_rank", rank)
-        except LayoutError:
-            return None
+            return self._call(name, *args)
+        except _lib.VortxError as e:
+            if e.status == _lib.VX_ERR_UNSUPPORTED:
+                return None
+            raise
+
+    def unsqueeze_to_rank(self, rank: int) -> Optional["TensorLayout"]:
+        return self._call_optional("vx_layout_unsqueeze_to_rank", rank)
 
     def unsqueeze(self, axis: int) -> Optional["TensorLayout"]:
-        try:
-            return self._call("vx_layout_unsqueeze", axis)
-        except LayoutError:
-            return None
+        return self._call_optional("vx_layout_unsqueeze", axis)
 
     def squeeze_axis(self, axis: int) -> "TensorLayout":
         return self._call("vx_layout_squeeze_axis", axis)
