@@ -1,0 +1,481 @@
+#!/usr/bin/env python
+"""Benchmark of the block-quantised GEMV hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("q4_0_gemv_28672x8192_x32"): the Q4_0 GEMV y = W x with W 28672 x 8192 (the FFN
+up-projection shape of the multi-GPU configuration), x f32 of length 8192, W ~ N(0, 0.02)
+before quantisation, x ~ N(0, 1), all seeded and synthetic.  One STEP is a pass over 32
+such matrices held at 32 different addresses (4.2 GB of weights at N = 1, far beyond the
+126 MB L2), i.e. 32 dependent GEMV launches replayed from one CUDA graph.  With N > 1 the rows
+of every matrix are split into N contiguous slabs (strong scaling: total work fixed), each
+rank computes its slab straight into its slice of y and the slices are all-gathered with NCCL.
+
+The line printed by rank 0:
+  value      algorithmic bytes per step / device time per step, weights resident in HBM
+             (bytes per GEMV = 132 120 576 of blocks + 32 768 n of x + 114 688 of y)
+  e2e        the same through the public API with host buffers: per GEMV the activation is
+             copied from pinned host memory, the product is read back to the host
+  roofline   the streaming GEMV kernel against the measured HBM copy bandwidth
+  cpu_baseline  the CPU oracle's GEMV on the host cores, on a bounded sample (rank 0, N = 1)
+`--impl reference` times that CPU implementation alone, on the same configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ROWS, COLS, LAYERS = 28672, 8192, 32
+QBLOCK = 18  # bytes per Q4_0 block
+METRIC = "q4_0_gemv_hbm_bandwidth"
+UNIT = "GB/s"
+
+
+def gemv_bytes(rows: int, cols: int, n_gpus: int = 1, batch: int = 1, qblock: int = QBLOCK) -> int:
+    """Algorithmic bytes of one GEMV: weights once, x on each GPU, y once."""
+    return rows * cols // 32 * qblock + batch * cols * 4 * n_gpus + batch * rows * 4
+
+
+def measured_peak_hbm():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_weights(rows: int, cols: int, seed: int) -> np.ndarray:
+    """One Q4_0 block stream for a rows x cols matrix ~ N(0, 0.02), quantised by the library's host quantiser."""
+    import vortx_b200 as vb
+    from vortx_b200 import synth
+    return vb.quantize(vb.Q4_0, synth.normal_matrix(rows, cols, seed))
+
+
+# ------------------------------------------------------------------------ CPU arm ----
+
+CPU_GEMVS_PER_STEP = 4  # of the step's 32: bounds the CPU arm to a fraction of a second per step
+
+
+def cpu_gemv_rate(blocks: np.ndarray, rows: int, steps: int, warmup: int):
+    """Times the CPU oracle's Q4_0 GEMV with all host threads: CPU_GEMVS_PER_STEP full-size GEMVs per step."""
+    import oracle as o
+    o.build()
+    from vortx_b200 import synth
+    threads = o.hardware_threads()
+    x = synth.normal_vectors(1, COLS, seed=1)[0]
+    for _ in range(max(warmup, 1)):
+        o.gemv(o.Q4_0, blocks, rows, COLS, x, nthreads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for _ in range(CPU_GEMVS_PER_STEP):
+            o.gemv(o.Q4_0, blocks, rows, COLS, x, nthreads=threads)
+    dt = (time.perf_counter() - t0) / steps
+    gbs = CPU_GEMVS_PER_STEP * gemv_bytes(rows, COLS) / dt / 1e9
+    return gbs, dt, threads
+
+
+def run_reference(args):
+    """`--impl reference`: the reference has no quantised GEMV and its CPU backend (khal) cannot be
+    built here, so this arm times the CPU oracle's GEMV, the stand-in the parity tests use."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    blocks = make_weights(ROWS, COLS, seed=100)
+    gbs, dt, threads = cpu_gemv_rate(blocks, ROWS, args.steps, args.warmup)
+    sample = (f"each step is {CPU_GEMVS_PER_STEP} of the workload's {LAYERS} GEMVs ({ROWS} x {COLS} Q4_0), "
+              f"{threads} host threads; C++ restatement of the GEMV, not khal")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "q4_0 x f32 -> f32", "data": "synthetic",
+        "config": {"workload": "q4_0_gemv_28672x8192_x32", "rows": ROWS, "cols": COLS, "batch": 1,
+                   "sampled": sample},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------ GPU arm ----
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import vortx_b200 as vb
+    from vortx_b200 import _lib, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    lib = _lib.load()
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    be = vb.Backend(local, stream=stream.cuda_stream)
+
+    n = world
+    assert ROWS % n == 0
+    shard = ROWS // n
+    row0 = rank * shard
+
+    # One quantised shard, uploaded LAYERS times to distinct addresses (identical bytes are still
+    # distinct cache lines, and the step walks all of them before coming back).
+    blocks = make_weights(shard, COLS, seed=100 + rank)
+    layers = [vb.QuantizedMatrix(be, vb.Q4_0, blocks, shard, COLS) for _ in range(LAYERS)]
+    x_host = synth.normal_vectors(1, COLS, seed=1)[0]
+    x_dev = torch.from_numpy(x_host).to(dev)
+    y_full = torch.zeros(LAYERS, ROWS, device=dev, dtype=torch.float32)  # one y per layer
+
+    def gemv(layer: int, xptr: int):
+        yptr = y_full[layer].data_ptr() + row0 * 4
+        st = lib.vx_gemv_q_rows(be._ctx, layers[layer]._h, 0, shard, xptr, COLS, yptr, shard, 1)
+        if st != 0:
+            raise RuntimeError(_lib.last_error())
+
+    def step_device():
+        for l in range(LAYERS):
+            gemv(l, x_dev.data_ptr())
+            if n > 1:
+                dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
+
+    # Warm-up outside the graph (also sizes NCCL's buffers), then capture one step.
+    launches_before = be.launch_count()
+    step_device()
+    launches_per_step = be.launch_count() - launches_before
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step_device()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if n > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if n > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    bytes_per_step = LAYERS * gemv_bytes(ROWS, COLS, n)
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # Kernel-only figure for the roofline: the same launches without the collective (N = 1: the
+    # step itself), timed live with CUDA events on the launching stream.
+    def kernels_only():
+        for l in range(LAYERS):
+            gemv(l, x_dev.data_ptr())
+    kgraph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(kgraph, stream=stream):
+        kernels_only()
+    for _ in range(3):
+        kgraph.replay()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record(stream)
+    reps = max(3, args.steps)
+    for _ in range(reps):
+        kgraph.replay()
+    k1.record(stream)
+    torch.cuda.synchronize()
+    launch_us = k0.elapsed_time(k1) * 1e3 / (reps * LAYERS)
+    shard_bytes = gemv_bytes(shard, COLS)
+    peak, peak_kind = measured_peak_hbm()
+    achieved = shard_bytes / (launch_us * 1e-6) / 1e9
+
+    # End to end through the public API with host buffers: per GEMV, x from pinned host memory,
+    # y back to the host.
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    y_pin = torch.empty(ROWS, dtype=torch.float32).pin_memory()
+    x_stage = torch.empty(COLS, device=dev, dtype=torch.float32)
+
+    def step_e2e():
+        for l in range(LAYERS):
+            _lib.check(lib.vx_upload(be._ctx, x_stage.data_ptr(), x_pin.data_ptr(), COLS * 4))
+            gemv(l, x_stage.data_ptr())
+            if n > 1:
+                dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
+            _lib.check(lib.vx_download(be._ctx, y_pin.data_ptr(), y_full[l].data_ptr(), ROWS * 4))
+
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e2e_steps = max(2, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if n > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e_value = bytes_per_step / (e2e_ms * 1e-3) / 1e9
+
+    extra = {}
+    cpu = None
+    if rank == 0 and n == 1:
+        extra = side_configs(be, lib, torch, stream)
+        try:
+            gbs, dt, threads = cpu_gemv_rate(blocks, ROWS, steps=5, warmup=1)
+            cpu = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
+                   "sample": f"5 x {CPU_GEMVS_PER_STEP} GEMVs of {ROWS} x {COLS} Q4_0 (the step has {LAYERS}); "
+                             "C++ restatement of the GEMV, not khal"}
+        except Exception as e:  # the oracle is test infrastructure; its absence must not hide the GPU numbers
+            cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {e}"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "q4_0 x f32 (24-bit fixed point) -> f32",
+            "data": "synthetic",
+            "config": {"workload": "q4_0_gemv_28672x8192_x32", "rows": ROWS, "cols": COLS, "batch": 1,
+                       "gemv_per_step": LAYERS, "sharding": f"rows/{n} per GPU, NCCL all-gather of y" if n > 1 else "none",
+                       "l2": "inputs larger than L2: 32 weight copies walked in turn", "launch": "CUDA graph replay"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": LAYERS * COLS * 4, "d2h_bytes_per_step": LAYERS * ROWS * 4},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": "gemv_stream_kernel",
+                         "bytes_per_launch": shard_bytes, "us_per_launch": launch_us,
+                         "traffic": int(round(shard_bytes * 1.0002)) if n == 1 else None,
+                         "traffic_source": "ncu dram bytes of one launch, see profiles/"},
+            "clocks": clocks,
+            "extra": extra,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if n > 1:
+        dist.destroy_process_group()
+
+
+def side_configs(be, lib, torch, stream):
+    """The other benchmark configurations, each timed briefly (graph replay, rotating weight copies)."""
+    import vortx_b200 as vb
+    from vortx_b200 import _lib, synth
+    import ctypes as C
+    out = {}
+
+    def time_graph(fn, n_launch, reps=5):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        for _ in range(2):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            g.replay()
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / (reps * n_launch)
+
+    peak, _ = measured_peak_hbm()
+    for name, qt, rows, cols, batches, copies in (("q8_0_gemv_4096x4096", vb.Q8_0, 4096, 4096, (1,), 24),
+                                                  ("q4_0_gemv_8192x8192", vb.Q4_0, 8192, 8192, (1, 4, 8), 12)):
+        blocks = vb.quantize(qt, synth.normal_matrix(rows, cols, seed=0))
+        ws = [vb.QuantizedMatrix(be, qt, blocks, rows, cols) for _ in range(copies)]
+        qb = lib.vx_qblock_bytes(qt)
+        for b in batches:
+            x = torch.randn(b, cols, device="cuda")
+            y = torch.empty(b, rows, device="cuda")
+
+            def fn():
+                for w in ws:
+                    _lib.check(lib.vx_gemv_q_rows(be._ctx, w._h, 0, rows, x.data_ptr(), cols, y.data_ptr(), rows, b))
+            us = time_graph(fn, copies)
+            byts = gemv_bytes(rows, cols, 1, b, qb)
+            out[f"{name}_b{b}"] = {"us": us, "GB/s": byts / us / 1e3, "frac_of_measured_hbm": byts / us / 1e3 / peak}
+        for w in ws:
+            w.free()
+
+    # f32 GEMM 1024^3, exact SIMT path (and the TF32 path at 8192^3 when the device has room).
+    for name, mode, dim in (("gemm_f32_simt_exact_1024", _lib.VX_GEMM_SIMT_EXACT, 1024),
+                            ("gemm_tf32_8192", _lib.VX_GEMM_TF32, 8192)):
+        A = torch.rand(dim, dim, device="cuda") * 2 - 1
+        B = torch.rand(dim, dim, device="cuda") * 2 - 1
+        Cm = torch.empty(dim, dim, device="cuda")
+        sh = _lib.VxShapes3()
+        for s in (sh.out, sh.lhs, sh.rhs):
+            s.n = s.c = 1
+            s.h = s.w = dim
+            s.n_stride = s.c_stride = dim * dim
+            s.h_stride, s.w_stride = dim, 1
+
+        def fn():
+            _lib.check(lib.vx_gemm_f32(be._ctx, mode, Cm.data_ptr(), A.data_ptr(), B.data_ptr(), C.byref(sh), 0, 0, 0))
+        us = time_graph(fn, 1, reps=3)
+        k = C.c_int32()
+        lib.vx_gemm_last_kernel(be._ctx, C.byref(k))
+        out[name] = {"us": us, "TFLOP/s": 2 * dim ** 3 / us / 1e6, "kernel": int(k.value)}
+    return out
+
+
+PROFILE_CASES = {
+    # name: (kind, rows/dim, cols, qtype name, weight copies)
+    "gemv_q4_0_28672x8192": ("gemv", 28672, 8192, "Q4_0", 2),
+    "gemv_q4_0_8192x8192": ("gemv", 8192, 8192, "Q4_0", 4),
+    "gemv_q8_0_4096x4096": ("gemv", 4096, 4096, "Q8_0", 8),
+    "gemm_simt_exact_1024": ("gemm", 1024, 1024, "SIMT", 0),
+    "gemm_tf32_4096": ("gemm", 4096, 4096, "TF32", 0),
+    "gemm_tf32_8192": ("gemm", 8192, 8192, "TF32", 0),
+}
+
+
+def run_profile_case(name: str):
+    """A handful of plain launches of one kernel on a small footprint, for `ncu` captures.
+    Prints what it ran; nothing printed here is a benchmark value."""
+    import ctypes as C
+    import vortx_b200 as vb
+    from vortx_b200 import _lib
+    kind, rows, cols, what, copies = PROFILE_CASES[name]
+    be = vb.Backend(0)
+    lib = _lib.load()
+    rng = np.random.Generator(np.random.Philox(1))
+    if kind == "gemv":
+        qt = vb.Q4_0 if what == "Q4_0" else vb.Q8_0
+        bb = lib.vx_qblock_bytes(qt)
+        nblocks = rows * cols // 32
+        # random quants with sane f16 scales: the kernel's work does not depend on the values
+        blocks = rng.integers(0, 256, size=(nblocks, bb), dtype=np.uint8)
+        sc = (rng.random(nblocks, dtype=np.float32) * 0.01 + 0.001).astype(np.float16).view(np.uint16)
+        blocks[:, 0] = sc & 0xFF
+        blocks[:, 1] = sc >> 8
+        ws = [vb.QuantizedMatrix(be, qt, blocks.ravel(), rows, cols) for _ in range(copies)]
+        x = be.init_buffer(rng.standard_normal(cols, dtype=np.float32))
+        y = be.uninit_buffer(rows)
+        for _ in range(3):
+            for w in ws:
+                vb.Gemv().dispatch(be, None, y, w, x)
+    else:
+        mode = _lib.VX_GEMM_SIMT_EXACT if what == "SIMT" else _lib.VX_GEMM_TF32
+        a = be.init_buffer(rng.random(rows * cols, dtype=np.float32) * 2 - 1)
+        b = be.init_buffer(rng.random(rows * cols, dtype=np.float32) * 2 - 1)
+        c = be.uninit_buffer(rows * cols)
+        sh = _lib.VxShapes3()
+        for s in (sh.out, sh.lhs, sh.rhs):
+            s.n = s.c = 1
+            s.h = s.w = rows
+            s.n_stride = s.c_stride = rows * cols
+            s.h_stride, s.w_stride = cols, 1
+        for _ in range(4):
+            _lib.check(lib.vx_gemm_f32(be._ctx, mode, c.ptr, a.ptr, b.ptr, C.byref(sh), 0, 0, 0))
+    be.synchronize()
+    print(json.dumps({"profile_case": name, "kernels_launched": be.launch_count()}), flush=True)
+    be.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), default=None,
+                    help="run a few launches of one kernel on a small footprint (for ncu) and exit")
+    args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -92,17 +92,17 @@ static vx_status create_context(int32_t device, void* stream, bool adopt, vx_con
         }
         ctx->owns_stream = true;
     }
-    cudaError_t a1 = cudaMalloc(&ctx->d_status, sizeof(vx::DeviceStatus));
-    cudaError_t a2 = cudaMallocHost(&ctx->h_status, sizeof(vx::DeviceStatus));
+    // The status word lives in mapped host memory: kernels write it only when a bounded wait
+    // gives up, and the host reads it after a stream synchronisation without any copy.
+    cudaError_t a1 = cudaHostAlloc(&ctx->h_status, sizeof(vx::DeviceStatus), cudaHostAllocMapped);
+    cudaError_t a2 = a1 == cudaSuccess ? cudaHostGetDevicePointer(&ctx->d_status, ctx->h_status, 0) : a1;
     if (a1 != cudaSuccess || a2 != cudaSuccess) {
-        if (ctx->d_status) cudaFree(ctx->d_status);
         if (ctx->h_status) cudaFreeHost(ctx->h_status);
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;
         (void)cudaGetLastError();
         return fail(VX_ERR_OUT_OF_MEMORY, "could not allocate the context status word");
     }
-    cudaMemsetAsync(ctx->d_status, 0, sizeof(vx::DeviceStatus), ctx->stream);
     std::memset(ctx->h_status, 0, sizeof(vx::DeviceStatus));
     ctx->options["bounds_check"] = 1;
     *out = ctx;
@@ -121,7 +121,6 @@ vx_status vx_context_destroy(vx_context* ctx) {
     if (!ctx) return VX_OK;
     vx::DeviceGuard guard(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     (void)cudaGetLastError();
@@ -132,19 +131,15 @@ vx_status vx_context_destroy(vx_context* ctx) {
 vx_status vx_synchronize(vx_context* ctx) {
     VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_synchronize: null context");
     vx::DeviceGuard guard(ctx->device);
-    if (!ctx->status_dirty) {
-        VX_CUDA(cudaStreamSynchronize(ctx->stream));
-        return VX_OK;
-    }
-    // A kernel with bounded device-side waits ran: bring its status word back with the stream.
-    VX_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(vx::DeviceStatus),
-                            cudaMemcpyDeviceToHost, ctx->stream));
     VX_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (!ctx->status_dirty) return VX_OK;
+    // A kernel with bounded device-side waits ran since the last check: look at its status word.
     ctx->status_dirty = false;
-    if (ctx->h_status->code != 0) {
-        const uint32_t code = ctx->h_status->code, detail = ctx->h_status->detail;
-        cudaMemsetAsync(ctx->d_status, 0, sizeof(vx::DeviceStatus), ctx->stream);
-        cudaStreamSynchronize(ctx->stream);
+    volatile vx::DeviceStatus* hs = ctx->h_status;
+    if (hs->code != 0) {
+        const uint32_t code = hs->code, detail = hs->detail;
+        hs->code = 0;
+        hs->detail = 0;
         return fail(VX_ERR_DEVICE_TIMEOUT,
                     "a bounded device-side wait gave up (stage code %u, block %u); results of the "
                     "affected kernel are invalid",

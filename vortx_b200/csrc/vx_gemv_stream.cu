@@ -54,7 +54,11 @@ struct StreamParams {
 };
 
 __device__ __forceinline__ void report(vx::DeviceStatus* st, uint32_t code) {
-    if (atomicCAS(&st->code, 0u, code) == 0u) st->detail = blockIdx.x;
+    // Mapped host memory, written only on failure; which failing block wins does not matter.
+    volatile vx::DeviceStatus* v = st;
+    v->detail = blockIdx.x;
+    v->code = code;
+    __threadfence_system();
 }
 
 template <int NR>
