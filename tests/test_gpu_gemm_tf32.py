@@ -1,0 +1,98 @@
+"""The tcgen05 TF32 GEMM against the exact SIMT kernel and the f64 oracle, through the C ABI.
+
+Bar (stated by the benchmark definition): relative Frobenius error of the TF32 result against
+the SIMT f32 result <= 5e-3.  TF32 keeps 10 explicit mantissa bits per operand, so the observed
+error is near 1e-3 * sqrt(2) / sqrt(3) ~ 5e-4.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import vortx_b200 as vb
+from vortx_b200 import _lib, synth
+
+pytestmark = pytest.mark.gpu
+
+TOL = 5e-3
+
+
+def _gemm(backend, how, A, B, out_rows=None):
+    m, k = A.shape
+    _, n = B.shape
+    a = vb.Tensor.matrix(backend, m, k, A)
+    b = vb.Tensor.matrix(backend, k, n, B)
+    c = vb.Tensor.matrix(backend, m, n, np.full((m, n), np.nan, np.float32))
+    getattr(vb.Gemm(), how)(backend, None, None, c, a, b)
+    backend.synchronize()
+    return c.read(backend), vb.Gemm.last_kernel(backend)
+
+
+def _rel_fro(x, ref):
+    return float(np.linalg.norm(x.astype(np.float64) - ref.astype(np.float64)) / np.linalg.norm(ref.astype(np.float64)))
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 32, 256), (128, 64, 256), (256, 128, 512), (128, 8, 32), (1, 4, 4),
+                                   (200, 100, 264), (129, 36, 260), (1000, 520, 72), (384, 1024, 768)])
+def test_tf32_matches_simt(backend, oracle, m, k, n):
+    A = synth.uniform_matrix(m, k, seed=m + k)
+    B = synth.uniform_matrix(k, n, seed=n + 3)
+    got, kern = _gemm(backend, "dispatch_tf32", A, B)
+    assert kern == "tcgen05_tf32", kern
+    ref, _ = _gemm(backend, "dispatch_tiled", A, B)
+    assert not np.isnan(got).any()
+    assert _rel_fro(got, ref) <= TOL
+    # and against the f64 product, so that an error common to both kernels cannot hide
+    assert _rel_fro(got, oracle.gemm_f64(A, B)) <= TOL
+
+
+def test_tf32_exact_on_tf32_representable_inputs(backend):
+    """Inputs with at most 10 mantissa bits and small integer products: TF32 loses nothing, f32
+    accumulation of exactly representable partial sums is exact, so the result must be exact."""
+    rng = np.random.Generator(np.random.Philox(3))
+    m, k, n = 256, 96, 512
+    A = rng.integers(-8, 9, size=(m, k)).astype(np.float32)
+    B = rng.integers(-8, 9, size=(k, n)).astype(np.float32)
+    got, kern = _gemm(backend, "dispatch_tf32", A, B)
+    assert kern == "tcgen05_tf32"
+    assert np.array_equal(got, (A.astype(np.int64) @ B.astype(np.int64)).astype(np.float32))
+
+
+def test_tf32_falls_back_when_tma_cannot_address(backend):
+    """A transposed lhs view has no unit stride along its rows: the call must still succeed, on the SIMT kernel."""
+    m, k, n = 96, 64, 128
+    At = synth.uniform_matrix(k, m, seed=1)
+    B = synth.uniform_matrix(k, n, seed=2)
+    at = vb.Tensor.matrix(backend, k, m, At)
+    b = vb.Tensor.matrix(backend, k, n, B)
+    c = vb.Tensor.matrix(backend, m, n, np.zeros((m, n), np.float32))
+    vb.Gemm().dispatch_tf32(backend, None, None, c, at.transpose(0, 1), b)
+    assert vb.Gemm.last_kernel(backend) == "simt_tiled_generic"
+    ref = At.T.astype(np.float64) @ B.astype(np.float64)
+    assert np.allclose(c.read(backend), ref, atol=1e-4)
+
+
+def test_tf32_batched_and_strided_rows(backend, oracle):
+    """A 2 x 2 batch, lhs rows padded (pitch 72 for K = 64): TMA takes pitches, not just dense matrices."""
+    nb, cb, m, k, n, pitch = 2, 2, 160, 64, 288, 72
+    Abuf = synth.uniform_matrix(nb * cb * m, pitch, seed=5).reshape(nb, cb, m, pitch)
+    B = synth.uniform_matrix(nb * cb * k, n, seed=6).reshape(nb, cb, k, n)
+    at = vb.Tensor(list(Abuf.shape), 4, backend.init_buffer(Abuf.ravel()))
+    bt = vb.Tensor(list(B.shape), 4, backend.init_buffer(B.ravel()))
+    ct = vb.Tensor([nb, cb, m, n], 4, backend.init_buffer(np.zeros(nb * cb * m * n, np.float32)))
+    vb.Gemm().dispatch_tf32(backend, None, None, ct, at.narrow(3, 0, k), bt)
+    assert vb.Gemm.last_kernel(backend) == "tcgen05_tf32"
+    got = ct.read(backend)
+    ref = np.einsum("bcmk,bckn->bcmn", Abuf[..., :k].astype(np.float64), B.astype(np.float64))
+    assert _rel_fro(got, ref) <= TOL
+
+
+def test_tf32_4096_against_simt(backend):
+    """A larger square case (several waves of tiles, both accumulators, the whole ring)."""
+    dim = 4096
+    A = synth.uniform_matrix(dim, dim, seed=0)
+    B = synth.uniform_matrix(dim, dim, seed=1)
+    got, kern = _gemm(backend, "dispatch_tf32", A, B)
+    assert kern == "tcgen05_tf32"
+    ref, _ = _gemm(backend, "dispatch_tiled", A, B)
+    assert _rel_fro(got, ref) <= TOL

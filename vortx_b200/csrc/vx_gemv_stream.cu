@@ -100,12 +100,15 @@ gemv_stream_kernel(const StreamParams p) {
     auto empty = [&](uint32_t s) { return bar0 + 8u * (p.stages + s); };
     auto red_full = [&](uint32_t b) { return bar0 + 8u * (2 * p.stages + b); };
     auto red_empty = [&](uint32_t b) { return bar0 + 8u * (2 * p.stages + kRedBufs + b); };
+    // Set by the first bounded wait that gives up; see sm100::mbar_wait.
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * 16 + 2 * kRedBufs);
 
     const uint32_t tid = threadIdx.x;
     // Programmatic dependent launch: let the next kernel in the stream start its own prologue
     // as soon as this grid's CTAs are all under way.  Nothing here depends on that kernel.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
+        *abort_flag = 0u;
         for (uint32_t s = 0; s < p.stages; ++s) {
             mbar_init(full(s), 1);
             mbar_init(empty(s), kWarps);
@@ -132,7 +135,7 @@ gemv_stream_kernel(const StreamParams p) {
         uint32_t k = 0;
         for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
             const uint32_t b = k % kRedBufs;
-            if (!mbar_wait(red_full(b), (k / kRedBufs) & 1)) report(p.status, 14);
+            if (!mbar_wait(red_full(b), (k / kRedBufs) & 1, abort_flag)) report(p.status, 14);
             const float* slot = red + (size_t)b * TR * kWarps;
             const uint32_t row = t * TR + lane;
             if (lane < (uint32_t)TR && row < p.nrows) {
@@ -152,7 +155,7 @@ gemv_stream_kernel(const StreamParams p) {
             uint32_t k = 0;
             for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
                 const uint32_t s = k % p.stages, use = k / p.stages;
-                if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1)) report(p.status, 11);
+                if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1, abort_flag)) report(p.status, 11);
                 const uint32_t tr = min((uint32_t)TR, p.nrows - t * TR);
                 const uint64_t first = p.row0 + (uint64_t)t * TR;
                 const uint32_t qbytes = tr * row_bytes;
@@ -168,7 +171,7 @@ gemv_stream_kernel(const StreamParams p) {
             // wait until the consumers have released the last use of every stage.
             for (uint32_t s = 0; s < p.stages && s < k; ++s) {
                 const uint32_t last_k = ((k - 1 - s) / p.stages) * p.stages + s;  // last tile index on stage s
-                if (!mbar_wait(empty(s), (last_k / p.stages) & 1)) report(p.status, 12);
+                if (!mbar_wait(empty(s), (last_k / p.stages) & 1, abort_flag)) report(p.status, 12);
             }
         }
         return;
@@ -240,7 +243,7 @@ gemv_stream_kernel(const StreamParams p) {
     uint32_t k = 0;
     for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
         const uint32_t s = k % p.stages;
-        if (!mbar_wait(full(s), (k / p.stages) & 1)) report(p.status, 13);
+        if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 13);
         const uint8_t* sq = smem + (size_t)s * p.stage_bytes;
         const uint64_t soff = (p.row0 + (uint64_t)t * TR) * p.nb * 2;
         const uint8_t* ss = sq + p.q_stage_bytes + (uint32_t)(soff & 15);
@@ -299,7 +302,7 @@ gemv_stream_kernel(const StreamParams p) {
 
         const float total = transposed_reduce<NR>(acc, lane);
         const uint32_t b = k % kRedBufs;
-        if (k >= kRedBufs && !mbar_wait(red_empty(b), ((k / kRedBufs) - 1) & 1)) report(p.status, 15);
+        if (k >= kRedBufs && !mbar_wait(red_empty(b), ((k / kRedBufs) - 1) & 1, abort_flag)) report(p.status, 15);
         float* slot = red + (size_t)b * TR * kWarps;
         if (active) {
             // lanes whose low bits are zero hold one row each
@@ -378,7 +381,7 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
     const uint32_t q_stage = TR * nchunks * 16;
     const uint32_t s_stage = (TR * nb * 2 + 32 + 15) / 16 * 16;
     const uint32_t stage_bytes = (q_stage + s_stage + 127) / 128 * 128;
-    const size_t fixed = kRedBufs * TR * kWarps * sizeof(float) + (2 * 16 + 2 * kRedBufs) * sizeof(uint64_t);
+    const size_t fixed = kRedBufs * TR * kWarps * sizeof(float) + (2 * 16 + 2 * kRedBufs + 1) * sizeof(uint64_t);
     const uint32_t tiles = (nrows + TR - 1) / TR;
     // Measured on B200: two CTAs per SM pay off once every CTA slot streams many tiles; short
     // launches do better with one CTA per SM, which also balances their few tiles better.  The

@@ -39,13 +39,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Each try_wait may itself suspend for a hardware-defined slice, so this budget is seconds
-// at the very least; a healthy pipeline completes within the first few tries.
-constexpr uint32_t kWaitTries = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitTries; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+// Bounded wait: gives up after about a fifth of a second of SM clocks (a healthy pipeline
+// completes within the first few tries).  `abort_flag` lives in the CTA's shared memory: the
+// first wait that gives up sets it, and every later wait of the CTA then returns at once, so a
+// broken pipeline costs one budget per CTA, not one per wait.
+constexpr long long kWaitCycles = 400ll * 1000 * 1000;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag != 0u) return false;
+        if (clock64() - start > kWaitCycles) {
+            *abort_flag = 1u;
+            return false;
+        }
+    }
 }
 
 // ----------------------------------------------------------- bulk async copy ----
@@ -145,15 +155,22 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // Shared-memory matrix descriptor of tcgen05.mma (64 bits):
 //   [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
-//   [46,48) = 1 (descriptor version for sm_100), [49,52) base offset, [61,64) swizzle (2 = 128 B).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   [46,48) = 1 (descriptor version for sm_100), [49,52) base offset, [61,64) swizzle mode.
+constexpr uint32_t kSwizzle128B = 2;        // 128-byte swizzle, 16-byte atoms (K-major operands)
+constexpr uint32_t kSwizzle128BAtom32B = 1; // 128-byte swizzle, 32-byte atoms: the only mode the
+                                            // tensor core accepts for an MN-major 32-bit operand
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t swizzle_mode) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
+    d |= (uint64_t)swizzle_mode << 61;
     return d;
+}
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return smem_desc(saddr, lbo_bytes, sbo_bytes, kSwizzle128B);
 }
 
 // dp4a with mixed signedness: a holds signed bytes, b unsigned bytes.
