@@ -172,6 +172,13 @@ def run_ours(args):
     import vortx_b200 as vb
     from vortx_b200 import _lib, synth
 
+    t_start = time.perf_counter()
+
+    def note(msg):
+        if os.environ.get("VX_BENCH_VERBOSE"):
+            print(f"[bench {time.perf_counter() - t_start:7.1f}s rank {os.environ.get('RANK', '0')}] {msg}",
+                  file=sys.stderr, flush=True)
+
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -183,6 +190,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    note("process group ready")
     lib = _lib.load()
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
@@ -213,6 +221,7 @@ def run_ours(args):
             if n > 1:
                 dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
 
+    note("weights uploaded")
     # Warm-up outside the graph (also sizes NCCL's buffers), then capture one step.
     launches_before = be.launch_count()
     step_device()
@@ -223,6 +232,7 @@ def run_ours(args):
         step_device()
     torch.cuda.synchronize()
 
+    note("step captured")
     def barrier():
         if n > 1:
             dist.barrier()
@@ -250,6 +260,7 @@ def run_ours(args):
     bytes_per_step = LAYERS * gemv_bytes(ROWS, COLS, n)
     value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
 
+    note("timed region done")
     # Kernel-only figure for the roofline: the same launches without the collective (N = 1: the
     # step itself), timed live with CUDA events on the launching stream.
     def kernels_only():
@@ -273,6 +284,7 @@ def run_ours(args):
     peak, peak_kind = measured_peak_hbm()
     achieved = shard_bytes / (launch_us * 1e-6) / 1e9
 
+    note("kernel-only timing done")
     # End to end through the public API with host buffers: per GEMV, x from pinned host memory,
     # y back to the host.
     x_pin = torch.from_numpy(x_host).pin_memory()
@@ -302,6 +314,7 @@ def run_ours(args):
     e2e_ms = float(t.item())
     e2e_value = bytes_per_step / (e2e_ms * 1e-3) / 1e9
 
+    note("end-to-end timing done")
     extra = {}
     cpu = None
     if rank == 0 and n == 1:

@@ -149,6 +149,27 @@ VX_API vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t ro
                                 const float* x, size_t x_stride, float* y, size_t y_stride,
                                 size_t batch);
 
+/* --------------------------------------------------------------- reductions ---- */
+/* Reduce::launch(backend, shapes, pass, variant, input, output) — src/linalg/reduce.rs:79-207 —
+ * over the kernels of vortx-shaders/src/linalg/reduce.rs:19-367.  Only the w axis of `shape` is
+ * walked (element i is in[i * w_stride]); the result is written to out[0].  f32 min / max start
+ * from +-1e18 as the reference kernels do (reduce.rs:292-295). */
+typedef enum {
+    VX_REDUCE_SUM = 0,   /* ReduceVariant::Sum    — reduce_add_{f32,u32,i32}   */
+    VX_REDUCE_PROD = 1,  /* ReduceVariant::Prod   — reduce_mul_*                */
+    VX_REDUCE_MIN = 2,   /* ReduceVariant::Min    — reduce_min_*                */
+    VX_REDUCE_MAX = 3,   /* ReduceVariant::Max    — reduce_max_*                */
+    VX_REDUCE_SQNORM = 4 /* ReduceVariant::SqNorm — reduce_sq_norm (f32 only)   */
+} vx_reduce_op;
+typedef enum { VX_F32 = 0, VX_U32 = 1, VX_I32 = 2 } vx_dtype;
+typedef enum {
+    VX_REDUCE_ORDERED = 0, /* one 128-thread block in the reference kernel's order: bit-identical  */
+    VX_REDUCE_WIDE = 1     /* many blocks + a fold over per-block partials held in scratch memory
+                              the context owns; f32 sum / product / norm differ by rounding order  */
+} vx_reduce_mode;
+VX_API vx_status vx_reduce(vx_context* ctx, vx_reduce_op op, vx_dtype dtype, vx_reduce_mode mode,
+                           const void* in, const vx_shape* shape, uint64_t cap_in, void* out);
+
 /* ----------------------------------------------------------------- tuning ---- */
 /* Integer knobs for experiments ("gemv.variant", "gemv.rows_per_warp", "gemm.tf32.stages"...).
  * Unknown keys return VX_ERR_INVALID_ARGUMENT.  Defaults are the shipped configuration. */

@@ -121,6 +121,7 @@ vx_status vx_context_destroy(vx_context* ctx) {
     if (!ctx) return VX_OK;
     vx::DeviceGuard guard(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->reduce_scratch) cudaFree(ctx->reduce_scratch);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     (void)cudaGetLastError();

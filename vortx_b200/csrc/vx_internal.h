@@ -70,6 +70,7 @@ struct vx_context {
     vx::DeviceStatus* d_status = nullptr;  // device
     vx::DeviceStatus* h_status = nullptr;  // pinned host mirror
     bool status_dirty = false;             // a kernel that may write d_status ran since the last check
+    void* reduce_scratch = nullptr;        // per-block partials of the wide reduction (device)
     std::map<std::string, int64_t> options;
 };
 

@@ -77,6 +77,48 @@ class Gemm:
         return _KERNEL_NAMES.get(k.value, str(k.value))
 
 
+class ReduceVariant:
+    """src/linalg/reduce.rs:16-30"""
+
+    Min = 2
+    Max = 3
+    Sum = 0
+    Prod = 1
+    SqNorm = 4
+
+
+_DTYPE_CODES = {np.dtype(np.float32): 0, np.dtype(np.uint32): 1, np.dtype(np.int32): 2}
+
+
+class Reduce:
+    """src/linalg/reduce.rs:44-207.  `launch` keeps the reference's argument order; the reference's host
+    type takes f32 tensors only, u32 / i32 tensors are accepted here because their kernels exist
+    (vortx-shaders/src/linalg/reduce.rs:301-308)."""
+
+    ORDERED, WIDE = 0, 1
+
+    def __init__(self, backend: Optional[Backend] = None, mode: int = 0):
+        self.backend = backend
+        self.mode = mode
+
+    @classmethod
+    def from_backend(cls, backend: Backend) -> "Reduce":
+        return cls(backend)
+
+    def launch(self, backend: Backend, shapes, pass_, variant: int, input_, output, mode: Optional[int] = None) -> None:
+        i = input_.as_tensor_ref()
+        o = output.as_tensor_mut()
+        ib, ob = i.raw_buffer(), o.raw_buffer()
+        if ib.dtype != ob.dtype or ib.dtype not in _DTYPE_CODES:
+            raise TypeError("Reduce takes f32, u32 or i32 tensors of one type")
+        shape = i.layout().canonicalize().into_gpu()
+        isz = ib.dtype.itemsize
+        st = _lib.load().vx_reduce(backend._ctx, variant, _DTYPE_CODES[ib.dtype], self.mode if mode is None else mode,
+                                   ib.ptr + i.layout().offset * isz, C.byref(shape), ib.len() - i.layout().offset,
+                                   ob.ptr + o.layout().offset * isz)
+        _lib.check(st)
+
+
 # --------------------------------------------------------------------- quantised --------
 
 Q8_0 = _lib.VX_Q8_0
