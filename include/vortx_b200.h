@@ -170,6 +170,24 @@ typedef enum {
 VX_API vx_status vx_reduce(vx_context* ctx, vx_reduce_op op, vx_dtype dtype, vx_reduce_mode mode,
                            const void* in, const vx_shape* shape, uint64_t cap_in, void* out);
 
+/* No counterpart in the reference.  The VX_REDUCE_WIDE reduction for callers that must not
+ * allocate at the moment of the call — a host that gave the whole device to its own arena at
+ * start-up and forbids driver allocations afterwards, or a latency-critical loop that cannot
+ * afford the device-wide stall a cudaMalloc may cause.  It needs no vx_context (creating one
+ * allocates): work goes to `cuda_stream` (a cudaStream_t) of `device`, and the per-block partials
+ * live in a fixed 4 KB array inside the library's device image instead of allocated scratch.
+ *   - At most 67 108 864 elements (1024 partials x 65 536 elements per block); more is refused
+ *     with VX_ERR_UNSUPPORTED.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     before any stream capture on that device.
+ *   - All calls share the one array: two calls whose kernels can overlap on the GPU (different
+ *     streams, no dependency) race.  Nothing needs clearing between calls.
+ * Results equal those of vx_reduce(.., VX_REDUCE_WIDE, ..): identical for integers and for
+ * min / max; f32 sums, products and norms agree to rounding order (the two split the vector
+ * into different numbers of blocks). */
+VX_API vx_status vx_reduce_static(int32_t device, void* cuda_stream, vx_reduce_op op, vx_dtype dtype,
+                                  const void* in, const vx_shape* shape, void* out);
+
 /* ----------------------------------------------------------------- tuning ---- */
 /* Integer knobs for experiments ("gemv.variant", "gemv.rows_per_warp", "gemm.tf32.stages"...).
  * Unknown keys return VX_ERR_INVALID_ARGUMENT.  Defaults are the shipped configuration. */

@@ -103,6 +103,7 @@ SIGNATURES = {
     "vx_gemv_q_rows": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t, _P, C.c_size_t, _P,
                                    C.c_size_t, C.c_size_t]),
     "vx_reduce": (C.c_int32, [_P, C.c_int, C.c_int, C.c_int, _P, C.POINTER(VxShape), C.c_uint64, _P]),
+    "vx_reduce_static": (C.c_int32, [C.c_int32, _P, C.c_int, C.c_int, _P, C.POINTER(VxShape), _P]),
     "vx_set_option": (C.c_int32, [_P, C.c_char_p, C.c_int64]),
     "vx_get_option": (C.c_int32, [_P, C.c_char_p, C.POINTER(C.c_int64)]),
     # host mirror

@@ -203,3 +203,95 @@ vx_status vx_reduce(vx_context* ctx, vx_reduce_op op, vx_dtype dtype, vx_reduce_
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------- reduction without any allocation ----
+// vx_reduce_static is the WIDE reduction for hosts that must not allocate when they call it: a
+// process that handed the whole device to its own arena at start-up and forbids driver
+// allocations afterwards, or a latency-critical loop in which a cudaMalloc (which can stall the
+// whole device) is not acceptable.  It therefore takes no vx_context either (creating one
+// allocates): just a device ordinal and a stream.
+//
+// Its scratch — one partial per block — is the fixed array below, part of the library's device
+// image: every GPU that loads the library carries these 4 KB until the process exits.  The array
+// name is a host-side handle, not a device address; the address a kernel can use is obtained once
+// per device with cudaGetSymbolAddress (static_partials_for) and cached.
+namespace {
+
+constexpr uint32_t kStaticPartials = 1024;           // blocks, hence partials, per call at most
+constexpr uint32_t kStaticPerBlock = 65536;          // elements one block folds at most
+constexpr uint64_t kStaticMaxElements = (uint64_t)kStaticPartials * kStaticPerBlock;  // 67 108 864
+static __device__ __align__(256) unsigned char g_static_partials[kStaticPartials * 4];
+
+// Device address of g_static_partials on `device`, looked up on the first call for that device
+// (with that device current) and remembered.  No allocation: the symbol already exists.
+vx_status static_partials_for(int device, void** out) {
+    static void* cached[64] = {};
+    VX_REQUIRE(device >= 0 && device < 64, VX_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", device);
+    if (!cached[device]) {
+        void* p = nullptr;
+        VX_CUDA(cudaGetSymbolAddress(&p, g_static_partials));
+        cached[device] = p;
+    }
+    *out = cached[device];
+    return VX_OK;
+}
+
+template <class T, int OP>
+vx_status run_static(cudaStream_t stream, const T* in, uint32_t n, uint32_t stride, T* out, T* partials) {
+    uint32_t blocks = (n + kWideThreads * 8 - 1) / (kWideThreads * 8);
+    blocks = std::max(1u, std::min(blocks, kStaticPartials));
+    // Every partial the second kernel reads is written by the first one of the same call, so
+    // nothing in the shared array has to be cleared between calls.
+    reduce_wide_partials_kernel<T, OP><<<blocks, kWideThreads, 0, stream>>>(in, n, stride, partials);
+    VX_CUDA(cudaGetLastError());
+    reduce_wide_final_kernel<T, OP><<<1, kWideThreads, 0, stream>>>(partials, blocks, out);
+    VX_CUDA(cudaGetLastError());
+    return VX_OK;
+}
+
+template <class T>
+vx_status run_static_op(int op, cudaStream_t stream, const void* in, uint32_t n, uint32_t stride, void* out,
+                        void* partials) {
+    const T* i = static_cast<const T*>(in);
+    T* o = static_cast<T*>(out);
+    T* p = static_cast<T*>(partials);
+    switch (op) {
+        case SUM: return run_static<T, SUM>(stream, i, n, stride, o, p);
+        case PROD: return run_static<T, PROD>(stream, i, n, stride, o, p);
+        case MIN: return run_static<T, MIN>(stream, i, n, stride, o, p);
+        case MAX: return run_static<T, MAX>(stream, i, n, stride, o, p);
+        default: return run_static<T, SQNORM>(stream, i, n, stride, o, p);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+vx_status vx_reduce_static(int32_t device, void* cuda_stream, vx_reduce_op op, vx_dtype dtype, const void* in,
+                           const vx_shape* shape, void* out) {
+    VX_REQUIRE(shape && out, VX_ERR_INVALID_ARGUMENT, "vx_reduce_static: null argument");
+    VX_REQUIRE(op >= VX_REDUCE_SUM && op <= VX_REDUCE_SQNORM, VX_ERR_INVALID_ARGUMENT, "unknown reduction %d", (int)op);
+    VX_REQUIRE(dtype >= VX_F32 && dtype <= VX_I32, VX_ERR_INVALID_ARGUMENT, "unknown element type %d", (int)dtype);
+    VX_REQUIRE(op != VX_REDUCE_SQNORM || dtype == VX_F32, VX_ERR_UNSUPPORTED, "the squared norm exists for f32 only");
+    VX_REQUIRE(in || shape->w == 0, VX_ERR_INVALID_ARGUMENT, "vx_reduce_static: null input");
+    VX_REQUIRE((uint64_t)shape->w <= kStaticMaxElements, VX_ERR_UNSUPPORTED,
+               "vx_reduce_static takes at most %llu elements (its scratch is a fixed %u-entry array); got %u",
+               (unsigned long long)kStaticMaxElements, kStaticPartials, shape->w);
+    int device_count = 0;
+    VX_CUDA(cudaGetDeviceCount(&device_count));
+    VX_REQUIRE(device >= 0 && device < device_count, VX_ERR_INVALID_ARGUMENT,
+               "device ordinal %d out of range (0..%d)", device, device_count - 1);
+    vx::DeviceGuard guard(device);
+    void* partials = nullptr;
+    vx_status st = static_partials_for(device, &partials);
+    if (st != VX_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    switch (dtype) {
+        case VX_F32: return run_static_op<float>((int)op, stream, in, shape->w, shape->w_stride, out, partials);
+        case VX_U32: return run_static_op<uint32_t>((int)op, stream, in, shape->w, shape->w_stride, out, partials);
+        default: return run_static_op<int32_t>((int)op, stream, in, shape->w, shape->w_stride, out, partials);
+    }
+}
+
+}  // extern "C"
