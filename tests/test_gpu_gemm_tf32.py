@@ -32,12 +32,16 @@ def _rel_fro(x, ref):
     return float(np.linalg.norm(x.astype(np.float64) - ref.astype(np.float64)) / np.linalg.norm(ref.astype(np.float64)))
 
 
+@pytest.mark.parametrize("tile_m", [128, 256])
 @pytest.mark.parametrize("m,k,n", [(128, 32, 256), (128, 64, 256), (256, 128, 512), (128, 8, 32), (1, 4, 4),
-                                   (200, 100, 264), (129, 36, 260), (1000, 520, 72), (384, 1024, 768)])
-def test_tf32_matches_simt(backend, oracle, m, k, n):
+                                   (200, 100, 264), (129, 36, 260), (1000, 520, 72), (384, 1024, 768),
+                                   (257, 40, 300), (512, 2048, 512)])
+def test_tf32_matches_simt(backend, oracle, m, k, n, tile_m):
+    backend.set_option("gemm.tf32.tile_m", tile_m)     # both tile shapes on every case
     A = synth.uniform_matrix(m, k, seed=m + k)
     B = synth.uniform_matrix(k, n, seed=n + 3)
     got, kern = _gemm(backend, "dispatch_tf32", A, B)
+    backend.set_option("gemm.tf32.tile_m", 0)
     assert kern == "tcgen05_tf32", kern
     ref, _ = _gemm(backend, "dispatch_tiled", A, B)
     assert not np.isnan(got).any()
@@ -87,12 +91,15 @@ def test_tf32_batched_and_strided_rows(backend, oracle):
     assert _rel_fro(got, ref) <= TOL
 
 
-def test_tf32_4096_against_simt(backend):
+@pytest.mark.parametrize("tile_m", [128, 256])
+def test_tf32_4096_against_simt(backend, tile_m):
     """A larger square case (several waves of tiles, both accumulators, the whole ring)."""
     dim = 4096
     A = synth.uniform_matrix(dim, dim, seed=0)
     B = synth.uniform_matrix(dim, dim, seed=1)
+    backend.set_option("gemm.tf32.tile_m", tile_m)
     got, kern = _gemm(backend, "dispatch_tf32", A, B)
+    backend.set_option("gemm.tf32.tile_m", 0)
     assert kern == "tcgen05_tf32"
     ref, _ = _gemm(backend, "dispatch_tiled", A, B)
     assert _rel_fro(got, ref) <= TOL

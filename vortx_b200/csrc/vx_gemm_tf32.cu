@@ -2,20 +2,27 @@
 //
 // out[M,N] = lhs[M,K] * rhs[K,N], all row-major f32 (vortx's layout: src/tensor/tensor_impl.rs:543-555).
 // Same semantics as gemm_tiled (vortx-shaders/src/linalg/gemm.rs:41-194) — overwrite, no alpha /
-// beta — but the products are formed from the top 19 bits of each operand (TF32) and summed in
-// an order of the hardware's choosing, so results agree with the SIMT kernel to about 1e-3
-// relative, not bit for bit.
+// beta — but the products are formed from TF32 operands and summed in an order of the hardware's
+// choosing, so results agree with the SIMT kernel to about 1e-3 relative, not bit for bit.
 //
 // One persistent CTA per SM, 192 threads:
-//   warp 0   TMA producer: per k-block of 32, one 128 x 32 box of A (K-major, 128-byte swizzle) and
-//            eight 32 x 32 boxes of B (N-major: the natural form of a row-major K x N matrix) into a
-//            4-stage shared-memory ring, completion on one mbarrier per stage.
-//   warp 1   MMA issuer: allocates 512 columns of tensor memory (two 128 x 256 f32 accumulators),
-//            issues tcgen05.mma.kind::tf32 128x256x8 four times per stage from one thread, commits
-//            the stage back to the producer and, after the last k-block, the accumulator to the epilogue.
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its 32 lanes), store rows to global
-//            memory, hand the accumulator back.  The next tile's MMAs run meanwhile in the other
-//            accumulator.
+//   warp 0   TMA producer: per k-block of 32, one box of A (K-major, 128-byte swizzle) and eight
+//            32 x 32 boxes of B (N-major: the natural form of a row-major K x N matrix) into a
+//            shared-memory ring, completion on one mbarrier per stage.
+//   warp 1   MMA issuer: allocates all 512 columns of tensor memory (two 128 x 256 f32
+//            accumulators), issues tcgen05.mma.kind::tf32 128x256x8 from one thread, commits each
+//            stage back to the producer and, after the last k-block, the accumulators to the epilogue.
+//   warps 2-5  epilogue: tcgen05.ld the accumulators (each warp its 32 lanes), store rows to global
+//            memory, hand the accumulators back.
+// Two tile shapes share the code (template parameter HALVES):
+//   HALVES = 1  128 x 256 tiles, the two accumulators alternate between consecutive tiles so that the
+//               epilogue of one tile runs under the MMAs of the next; 4 stages of 48 KB.
+//   HALVES = 2  256 x 256 tiles, the two accumulators are the upper and lower half of one tile and
+//               every stage of B feeds both.  With 4-byte operands the kernel is bound by the bytes
+//               that must reach shared memory per FLOP (measured: 12.5 TB/s from L2 at 128 x 256,
+//               tensor pipe 61 % busy); sharing B across 256 rows cuts that by a third, at the price
+//               of an epilogue that is no longer hidden (about 2 % of a tile at K = 8192).  3 stages
+//               of 64 KB.
 // B needs no transposing pre-pass: the instruction descriptor marks it MN-major.  For a 32-bit
 // MN-major operand the tensor core accepts exactly one shared-memory form, the 128-byte swizzle
 // with 32-byte atoms (measured: the 16-byte-atom form yields zeros), so B's tensor map uses
@@ -33,16 +40,22 @@ namespace {
 
 using namespace sm100;
 
-constexpr int BM = 128, BN = 256, BK = 32;  // tile; BK floats = 128 bytes = one swizzle span
-constexpr int UMMA_K = 8;                   // k per tcgen05.mma for 32-bit inputs
-constexpr int kStages = 4;
-constexpr int kAccStages = 2;
-constexpr uint32_t kABytes = BM * BK * 4;        // 16 KB
-constexpr uint32_t kBAtomBytes = 32 * BK * 4;    // one 32-column atom: 32 k-rows x 128 B = 4 KB
+constexpr int BMMA = 128, BN = 256, BK = 32;  // one MMA's M, N; BK floats = 128 bytes = one swizzle span
+constexpr int UMMA_K = 8;                     // k per tcgen05.mma for 32-bit inputs
+constexpr uint32_t kAHalfBytes = BMMA * BK * 4;        // 16 KB: 128 rows of A
+constexpr uint32_t kBAtomBytes = 32 * BK * 4;          // one 32-column atom: 32 k-rows x 128 B = 4 KB
 constexpr uint32_t kBBytes = (BN / 32) * kBAtomBytes;  // 32 KB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kTmemCols = kAccStages * BN;  // 512
+constexpr uint32_t kTmemCols = 2 * BN;                 // 512: both accumulators
 constexpr int kThreads = 192;
+constexpr int kMaxStages = 4;
+
+template <int HALVES> struct Cfg {
+    static constexpr int BM = BMMA * HALVES;                 // rows of C per tile
+    static constexpr uint32_t kABytes = kAHalfBytes * HALVES;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;  // 48 KB or 64 KB
+    static constexpr int kStages = HALVES == 1 ? 4 : 3;
+    static constexpr int kAccStages = HALVES == 1 ? 2 : 1;   // tiles in flight in tensor memory
+};
 
 struct Tf32Params {
     float* out;
@@ -55,10 +68,10 @@ struct Tf32Params {
 };
 
 struct SharedTail {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
-    uint64_t acc_full[kAccStages];
-    uint64_t acc_empty[kAccStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -84,11 +97,16 @@ __device__ __forceinline__ void tile_coords(const Tf32Params& p, uint32_t t, uin
 // Instruction descriptor of tcgen05.mma.kind::tf32: f32 accumulate (bits 4-5 = 1), A and B TF32
 // (bits 7-9, 10-12 = 2), A K-major (bit 15 = 0), B MN-major (bit 16 = 1), N / 8 at bit 17, M / 16 at bit 24.
 constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) |
-                            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BMMA >> 4) << 24);
 
+template <int HALVES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const Tf32Params p) {
+    using C = Cfg<HALVES>;
+    constexpr int kStages = C::kStages, kAccStages = C::kAccStages;
+    constexpr uint32_t kStageBytes = C::kStageBytes, kABytes = C::kABytes;
+
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // The ring must start on a 1024-byte boundary (128-byte swizzle repeats every 8 rows).
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -137,7 +155,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t dst_a = smem_addr(smem + s * kStageBytes);
                     const uint32_t dst_b = dst_a + kABytes;
                     mbar_arrive_expect_tx(full, kStageBytes);
-                    tma_load_2d(dst_a, &map_a, (int32_t)(kb * BK), (int32_t)(tm * BM), full);
+                    // A: one box of BM rows x 32 floats (the box of map_a is BM rows tall)
+                    tma_load_2d(dst_a, &map_a, (int32_t)(kb * BK), (int32_t)(tm * C::BM), full);
 #pragma unroll
                     for (int a = 0; a < BN / 32; ++a)
                         tma_load_2d(dst_b + a * kBAtomBytes, &map_b, (int32_t)(tn * BN + a * 32), (int32_t)(kb * BK), full);
@@ -158,7 +177,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (ause > 0 && !mbar_wait(smem_addr(&tail->acc_empty[as]), (ause - 1) & 1, abort_flag))
                     report(p.status, 23);
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + as * BN;
+                // HALVES = 1: accumulator `as` (256 columns).  HALVES = 2: both, upper half first.
+                const uint32_t d_tmem = tmem_base + (HALVES == 1 ? as * BN : 0);
                 for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
                     const uint32_t s = it % kStages;
                     if (!mbar_wait(smem_addr(&tail->full[s]), (it / kStages) & 1, abort_flag)) report(p.status, 24);
@@ -167,17 +187,21 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
                     for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                        // A: K-major, rows of 128 B, 8-row groups 1 KB apart; a k-step is 32 B along the row.
-                        const uint64_t da = smem_desc_sw128(a_addr + ks * UMMA_K * 4, 16, 1024);
                         // B: MN-major with 32-byte swizzle atoms: 32-column atoms 4 KB apart (leading
                         // offset), groups of 4 k-rows of 128 B 512 B apart (stride offset); a k-step of 8
                         // rows is 1 KB.
                         const uint64_t db = smem_desc(b_addr + ks * UMMA_K * 128, kBAtomBytes, 512, kSwizzle128BAtom32B);
-                        mma_tf32(d_tmem, da, db, kIdesc, (kb | ks) != 0 ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h) {
+                            // A: K-major, rows of 128 B, 8-row groups 1 KB apart; a k-step is 32 B along the
+                            // row; the lower half of a 256-row tile starts 16 KB further.
+                            const uint64_t da = smem_desc_sw128(a_addr + h * kAHalfBytes + ks * UMMA_K * 4, 16, 1024);
+                            mma_tf32(d_tmem + h * BN, da, db, kIdesc, (kb | ks) != 0 ? 1u : 0u);
+                        }
                     }
                     mma_commit(smem_addr(&tail->empty[s]));  // stage reusable once these MMAs have read it
                 }
-                mma_commit(smem_addr(&tail->acc_full[as]));  // accumulator complete
+                mma_commit(smem_addr(&tail->acc_full[as]));  // accumulator(s) complete
             }
         }
     } else {
@@ -191,27 +215,30 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!mbar_wait(smem_addr(&tail->acc_full[as]), (tile_it / kAccStages) & 1, abort_flag))
                 report(p.status, 25);
             tc_fence_after_sync();
-            const uint32_t row = tm * BM + quad * 32 + lane;
             const uint32_t col0 = tn * BN;
-            float* dst_row = p.out + (size_t)row * p.ldc + col0;
-            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + as * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(taddr + c * 32, v);
-                tmem_ld_wait();
-                if (row < p.m) {
-                    const uint32_t col = col0 + c * 32;
-                    if (p.out_vec && col + 32 <= p.n) {
-                        float4* d4 = reinterpret_cast<float4*>(dst_row + c * 32);
+            for (int h = 0; h < HALVES; ++h) {
+                const uint32_t row = tm * C::BM + h * BMMA + quad * 32 + lane;
+                float* dst_row = p.out + (size_t)row * p.ldc + col0;
+                const uint32_t taddr = tmem_base + ((quad * 32) << 16) + (HALVES == 1 ? as * BN : h * BN);
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + c * 32, v);
+                    tmem_ld_wait();
+                    if (row < p.m) {
+                        const uint32_t col = col0 + c * 32;
+                        if (p.out_vec && col + 32 <= p.n) {
+                            float4* d4 = reinterpret_cast<float4*>(dst_row + c * 32);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            d4[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                    } else {
+                            for (int j = 0; j < 8; ++j)
+                                d4[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                    __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < p.n) dst_row[c * 32 + j] = __uint_as_float(v[j]);
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < p.n) dst_row[c * 32 + j] = __uint_as_float(v[j]);
+                        }
                     }
                 }
             }
@@ -267,6 +294,24 @@ bool make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t oute
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+template <int HALVES>
+vx_status launch_tiles(vx_context* ctx, const CUtensorMap& map_a, const CUtensorMap& map_b, Tf32Params p) {
+    using C = Cfg<HALVES>;
+    const size_t smem = (size_t)C::kStages * C::kStageBytes + sizeof(SharedTail) + 1024;
+    static bool attr_set[64] = {};
+    if (!attr_set[ctx->device & 63]) {
+        VX_CUDA(cudaFuncSetAttribute(gemm_tf32_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[ctx->device & 63] = true;
+    }
+    p.tiles_m = (p.m + C::BM - 1) / C::BM;
+    p.tiles_n = (p.n + BN - 1) / BN;
+    const uint32_t tiles = p.tiles_m * p.tiles_n;
+    dim3 grid(std::min<uint32_t>(tiles, (uint32_t)ctx->sm_count));
+    gemm_tf32_kernel<HALVES><<<grid, kThreads, smem, ctx->stream>>>(map_a, map_b, p);
+    VX_CUDA(cudaGetLastError());
+    return VX_OK;
+}
+
 }  // namespace
 
 namespace vx {
@@ -287,12 +332,13 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
     if (batches > 4096) return VX_OK;
     if (!encode_fn()) return VX_OK;
 
-    const size_t smem = (size_t)kStages * kStageBytes + sizeof(SharedTail) + 1024;
-    static bool attr_set[64] = {};
-    if (!attr_set[ctx->device & 63]) {
-        VX_CUDA(cudaFuncSetAttribute(gemm_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[ctx->device & 63] = true;
-    }
+    // 256-row tiles as soon as they fill the SMs once (measured at 4096^3, 1.7 waves: 709 against
+    // 537 TFLOP/s); below that the finer 128-row tiles spread better.  "gemm.tf32.tile_m" forces one.
+    const uint64_t tiles256 = (uint64_t)((m + 255) / 256) * ((n + BN - 1) / BN);
+    int halves = tiles256 >= (uint64_t)ctx->sm_count ? 2 : 1;
+    const int64_t forced = option(ctx, "gemm.tf32.tile_m", 0);
+    if (forced == 128) halves = 1;
+    if (forced == 256) halves = 2;
 
     for (uint32_t bn = 0; bn < s.out.n; ++bn)
         for (uint32_t bc = 0; bc < s.out.c; ++bc) {
@@ -300,7 +346,7 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
             const float* b = rhs + (size_t)bn * s.rhs.n_stride + (size_t)bc * s.rhs.c_stride;
             float* c = out + (size_t)bn * s.out.n_stride + (size_t)bc * s.out.c_stride;
             CUtensorMap map_a, map_b;
-            if (!make_map(&map_a, a, k, m, s.lhs.h_stride, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+            if (!make_map(&map_a, a, k, m, s.lhs.h_stride, BK, BMMA * halves, CU_TENSOR_MAP_SWIZZLE_128B) ||
                 !make_map(&map_b, b, n, k, s.rhs.h_stride, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) {
                 if (bn == 0 && bc == 0) return VX_OK;  // nothing launched yet: let the caller fall back
                 return fail(VX_ERR_CUDA, "cuTensorMapEncodeTiled refused a batch matrix after the first");
@@ -311,15 +357,12 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
             p.n = n;
             p.k = k;
             p.ldc = s.out.h_stride;
-            p.tiles_m = (m + BM - 1) / BM;
-            p.tiles_n = (n + BN - 1) / BN;
-            p.raster = (uint32_t)std::max<int64_t>(1, option(ctx, "gemm.tf32.raster", 16));
+            p.tiles_m = p.tiles_n = 0;  // set by launch_tiles
+            p.raster = (uint32_t)std::max<int64_t>(1, option(ctx, "gemm.tf32.raster", halves == 2 ? 2 : 8));
             p.out_vec = (aligned16(c) && s.out.h_stride % 4 == 0) ? 1u : 0u;
             p.status = ctx->d_status;
-            const uint32_t tiles = p.tiles_m * p.tiles_n;
-            dim3 grid(std::min<uint32_t>(tiles, (uint32_t)ctx->sm_count));
-            gemm_tf32_kernel<<<grid, kThreads, smem, ctx->stream>>>(map_a, map_b, p);
-            VX_CUDA(cudaGetLastError());
+            vx_status st = halves == 2 ? launch_tiles<2>(ctx, map_a, map_b, p) : launch_tiles<1>(ctx, map_a, map_b, p);
+            if (st != VX_OK) return st;
             ctx->launches++;
             ctx->status_dirty = true;
         }
