@@ -209,17 +209,27 @@ def run_ours(args):
     x_dev = torch.from_numpy(x_host).to(dev)
     y_full = torch.zeros(LAYERS, ROWS, device=dev, dtype=torch.float32)  # one y per layer
 
+    # N > 1: how the slabs of y reach every GPU.  "peer" (default): the GEMV's epilogue stores each row
+    # into every peer's y over NVLink and a one-warp barrier kernel follows; "nccl": all-gather after the kernel.
+    scatter = None
+    if n > 1:
+        from vortx_b200.multi_gpu import PeerScatterGemv
+        scatter = PeerScatterGemv(be, ROWS, COLS, LAYERS)
+
     def gemv(layer: int, xptr: int):
         yptr = y_full[layer].data_ptr() + row0 * 4
         st = lib.vx_gemv_q_rows(be._ctx, layers[layer]._h, 0, shard, xptr, COLS, yptr, shard, 1)
         if st != 0:
             raise RuntimeError(_lib.last_error())
 
-    def step_device():
+    def step_device(exchange=args.exchange):
         for l in range(LAYERS):
-            gemv(l, x_dev.data_ptr())
-            if n > 1:
-                dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
+            if n > 1 and exchange == "peer":
+                scatter.dispatch(layers[l], x_dev.data_ptr(), l)
+            else:
+                gemv(l, x_dev.data_ptr())
+                if n > 1:
+                    dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
 
     note("weights uploaded")
     # Warm-up outside the graph (also sizes NCCL's buffers), then capture one step.
@@ -294,10 +304,15 @@ def run_ours(args):
     def step_e2e():
         for l in range(LAYERS):
             _lib.check(lib.vx_upload(be._ctx, x_stage.data_ptr(), x_pin.data_ptr(), COLS * 4))
-            gemv(l, x_stage.data_ptr())
-            if n > 1:
-                dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
-            _lib.check(lib.vx_download(be._ctx, y_pin.data_ptr(), y_full[l].data_ptr(), ROWS * 4))
+            if n > 1 and args.exchange == "peer":
+                scatter.dispatch(layers[l], x_stage.data_ptr(), l)
+                src = scatter.y_ptr(l)
+            else:
+                gemv(l, x_stage.data_ptr())
+                if n > 1:
+                    dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
+                src = y_full[l].data_ptr()
+            _lib.check(lib.vx_download(be._ctx, y_pin.data_ptr(), src, ROWS * 4))
 
     for _ in range(2):
         step_e2e()
@@ -316,6 +331,28 @@ def run_ours(args):
 
     note("end-to-end timing done")
     extra = {}
+    if n > 1:
+        # the other way of exchanging y, timed the same way, for comparison
+        other = "nccl" if args.exchange == "peer" else "peer"
+        step_device(other)
+        torch.cuda.synchronize()
+        og = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(og, stream=stream):
+            step_device(other)
+        for _ in range(3):
+            og.replay()
+        barrier()
+        o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        o0.record(stream)
+        for _ in range(args.steps):
+            og.replay()
+        o1.record(stream)
+        barrier()
+        t = torch.tensor([o0.elapsed_time(o1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        other_ms = float(t.item()) / args.steps
+        extra[f"exchange_{other}"] = {"ms_per_step": other_ms, "GB/s": bytes_per_step / (other_ms * 1e-3) / 1e9}
+        extra["kernels_only"] = {"us_per_launch": launch_us, "GB/s_per_gpu": achieved}
     cpu = None
     if rank == 0 and n == 1:
         extra = side_configs(be, lib, torch, stream)
@@ -334,7 +371,9 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "q4_0 x f32 (24-bit fixed point) -> f32",
             "data": "synthetic",
             "config": {"workload": "q4_0_gemv_28672x8192_x32", "rows": ROWS, "cols": COLS, "batch": 1,
-                       "gemv_per_step": LAYERS, "sharding": f"rows/{n} per GPU, NCCL all-gather of y" if n > 1 else "none",
+                       "gemv_per_step": LAYERS,
+                       "sharding": (f"rows/{n} per GPU; y exchanged by " + ("peer stores from the kernel epilogue + barrier kernel"
+                                    if args.exchange == "peer" else "NCCL all-gather")) if n > 1 else "none",
                        "l2": "inputs larger than L2: 32 weight copies walked in turn", "launch": "CUDA graph replay"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": LAYERS * COLS * 4, "d2h_bytes_per_step": LAYERS * ROWS * 4},
@@ -342,8 +381,8 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": "gemv_stream_kernel",
                          "bytes_per_launch": shard_bytes, "us_per_launch": launch_us,
-                         "traffic": int(round(shard_bytes * 1.0002)) if n == 1 else None,
-                         "traffic_source": "ncu dram bytes of one launch, see profiles/"},
+                         "traffic": 135_400_000 if n == 1 else None,
+                         "traffic_source": "ncu dram__bytes_read + write of one launch of this shape, profiles/gemv_stream_q4_0_28672x8192.md"},
             "clocks": clocks,
             "extra": extra,
         }
@@ -351,7 +390,12 @@ def run_ours(args):
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     if n > 1:
-        dist.destroy_process_group()
+        # NCCL's communicator teardown was seen to hang on this pool's boxes after all work had
+        # completed; every rank has synchronised and rank 0 has printed, so leave without it.
+        barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def side_configs(be, lib, torch, stream):
@@ -479,6 +523,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: how y is exchanged (peer stores from the kernel, or an NCCL all-gather)")
     ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), default=None,
                     help="run a few launches of one kernel on a small footprint (for ncu) and exit")
     args = ap.parse_args()

@@ -149,6 +149,32 @@ VX_API vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t ro
                                 const float* x, size_t x_stride, float* y, size_t y_stride,
                                 size_t batch);
 
+/* ------------------------------------------------- several GPUs, one process each ---- */
+/* No reference counterpart (vortx knows one device ordinal, src/linalg/gemm.rs:353).
+ * A row-sharded GEMV needs every rank's slab of y on every GPU.  Instead of a collective after
+ * the kernel, vx_gemv_q_rows_scatter stores each finished row into the peers' y buffers as
+ * well (plain stores over NVLink; nothing is loaded from a peer), and vx_peer_barrier tells
+ * every rank when all slabs have landed.  Peer buffers are mapped with CUDA IPC:
+ * export a vx_alloc'd buffer on its owner, pass the 64 bytes to the other processes by any
+ * means, import them there. */
+VX_API vx_status vx_ipc_export(vx_context* ctx, const void* device_ptr, void* handle64);
+VX_API vx_status vx_ipc_import(vx_context* ctx, const void* handle64, void** device_ptr);
+VX_API vx_status vx_ipc_release(vx_context* ctx, void* device_ptr);
+/* y[r] and peer_y[i][r] (r < nrows, i < n_peers <= 7) all receive row row0 + r of W times x.  The
+ * pointers are already advanced to where the slab belongs in each full-length y. */
+VX_API vx_status vx_gemv_q_rows_scatter(vx_context* ctx, const vx_qweights* w, size_t row0, size_t nrows,
+                                        const float* x, float* y, float* const* peer_y, size_t n_peers);
+/* flags[r] (r < world <= 8) is rank r's array of 64 u32, zero-initialised: its own for
+ * r == rank, a mapped peer pointer otherwise.  Stream-ordered: after all earlier work of this
+ * context it announces this rank's next barrier number to every rank, then waits, on the device
+ * and for at most about 0.2 s, until every rank has announced the same number (all ranks must
+ * issue the same sequence of barriers; the count lives on the device, so a replayed CUDA graph
+ * keeps advancing).  A wait that gives up surfaces as VX_ERR_DEVICE_TIMEOUT from the next
+ * vx_synchronize.  One barrier orders "every rank has written" before "any rank reads"; a buffer
+ * that is rewritten later needs its own ordering against the readers (a second barrier or a
+ * second buffer). */
+VX_API vx_status vx_peer_barrier(vx_context* ctx, uint32_t* const* flags, size_t world, size_t rank);
+
 /* --------------------------------------------------------------- reductions ---- */
 /* Reduce::launch(backend, shapes, pass, variant, input, output) — src/linalg/reduce.rs:79-207 —
  * over the kernels of vortx-shaders/src/linalg/reduce.rs:19-367.  Only the w axis of `shape` is
@@ -187,6 +213,26 @@ VX_API vx_status vx_reduce(vx_context* ctx, vx_reduce_op op, vx_dtype dtype, vx_
  * into different numbers of blocks). */
 VX_API vx_status vx_reduce_static(int32_t device, void* cuda_stream, vx_reduce_op op, vx_dtype dtype,
                                   const void* in, const vx_shape* shape, void* out);
+
+/* -------------------------------------------------------- element-wise kernels ---- */
+/* The `.call(pass, num_threads, shape_a, shape_b, a, b)` level of OpAssign — src/linalg/op_assign.rs:53-80
+ * over gpu_add / gpu_sub / gpu_mul / gpu_div / gpu_copy (vortx-shaders/src/linalg/op_assign.rs:29-166)
+ * and gpu_copy_with_offsets (:171-187): for every linear id of shape_a, decomposed over shape_a's
+ * sizes, a[offset_a + it_a(id)] op= b[offset_b + it_b(id)].  shape_b carries zero strides where b
+ * is broadcast. */
+typedef enum { VX_OP_ADD = 0, VX_OP_SUB = 1, VX_OP_MUL = 2, VX_OP_DIV = 3, VX_OP_COPY = 4 } vx_op;
+VX_API vx_status vx_op_assign(vx_context* ctx, vx_op op, float* a, const vx_shape* shape_a, uint64_t cap_a,
+                              const float* b, const vx_shape* shape_b, uint64_t cap_b, uint32_t offset_a,
+                              uint32_t offset_b);
+/* contiguous / contiguous_with_offset — vortx-shaders/src/linalg/contiguous.rs:18-85, called from
+ * src/linalg/contiguous.rs:20-129: dest[i] = src[offset + it(n,c,h,w)] with i walked in row-major
+ * order of shape_src's sizes.  Elements are 4 bytes of any type. */
+VX_API vx_status vx_contiguous(vx_context* ctx, void* dest, uint64_t cap_dest, const void* src,
+                               const vx_shape* shape_src, uint64_t cap_src, uint32_t offset);
+/* repeat — vortx-shaders/src/linalg/repeat.rs:15-43, called from src/linalg/repeat.rs:24-88:
+ * result[it_r(id)] = source[it_s(id mod source sizes)]. */
+VX_API vx_status vx_repeat(vx_context* ctx, float* result, const vx_shape* shape_result, uint64_t cap_result,
+                           const float* source, const vx_shape* shape_source, uint64_t cap_source);
 
 /* ----------------------------------------------------------------- tuning ---- */
 /* Integer knobs for experiments ("gemv.variant", "gemv.rows_per_warp", "gemm.tf32.stages"...).

@@ -98,6 +98,14 @@ VX_API vx_status vx_gemm_dispatch(vx_context* ctx, vx_dispatch_kind kind, float*
                                   const vx_layout* lhs_layout, uint64_t lhs_cap, const float* rhs,
                                   const vx_layout* rhs_layout, uint64_t rhs_cap);
 
+/* OpAssign::launch — src/linalg/op_assign.rs:38-143 — and, with is_repeat != 0, Repeat::launch —
+ * src/linalg/repeat.rs:24-88: broadcast_assign(a, b) (VX_ERR_SHAPE where the reference panics on
+ * incompatible shapes), canonicalise both, apply the view offsets, launch.  a and b are the base
+ * pointers of the underlying buffers, *_cap their lengths in elements. */
+VX_API vx_status vx_op_assign_dispatch(vx_context* ctx, vx_op op, int32_t is_repeat, float* a,
+                                       const vx_layout* layout_a, uint64_t cap_a, const float* b,
+                                       const vx_layout* layout_b, uint64_t cap_b);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,7 +18,7 @@ _SO = _DIR / "libvortx_oracle.so"
 __all__ = [
     "Shape", "build", "lib", "shape_contiguous", "gemm_naive", "gemm_tiled", "gemm_dispatch", "gemm_f64",
     "quantize", "dequantize", "gemv", "gemv_f64", "f32_to_f16", "f16_to_f32", "reduce", "hardware_threads",
-    "Q8_0", "Q4_0", "BLOCK_BYTES",
+    "Q8_0", "Q4_0", "BLOCK_BYTES", "op_assign", "contiguous", "repeat",
 ]
 
 Q8_0, Q4_0 = 0, 1
@@ -78,6 +78,9 @@ def lib():
         L.orc_reduce_u32.argtypes = [P, S, C.c_int]
         L.orc_reduce_i32.restype = C.c_int32
         L.orc_reduce_i32.argtypes = [P, S, C.c_int]
+        L.orc_op_assign.argtypes = [C.c_int, P, S, P, S, C.c_uint32, C.c_uint32]
+        L.orc_contiguous.argtypes = [P, P, S, C.c_uint32]
+        L.orc_repeat.argtypes = [P, S, P, S]
         L.orc_hardware_threads.restype = C.c_int
         _lib = L
     return _lib
@@ -196,3 +199,25 @@ def reduce(v, op: str, stride: int = 1, length=None):
     if v.dtype == np.int32:
         return np.int32(lib().orc_reduce_i32(v.ctypes.data, C.byref(s), code))
     raise TypeError(v.dtype)
+
+
+def op_assign(op: int, a, sa: Shape, b, sb: Shape, off_a: int = 0, off_b: int = 0):
+    """In place on the flat f32 buffer `a`; op: 0 add, 1 sub, 2 mul, 3 div, 4 copy."""
+    assert a.dtype == np.float32 and b.dtype == np.float32 and a.flags["C_CONTIGUOUS"] and b.flags["C_CONTIGUOUS"]
+    lib().orc_op_assign(op, a.ctypes.data, C.byref(sa), b.ctypes.data, C.byref(sb), off_a, off_b)
+    return a
+
+
+def contiguous(src, s: Shape, offset: int = 0):
+    """Row-major gather of the 4-byte elements that `s` addresses in the flat buffer `src`."""
+    src = np.ascontiguousarray(src)
+    assert src.dtype.itemsize == 4
+    out = np.empty(s.n * s.c * s.h * s.w, src.dtype)
+    lib().orc_contiguous(out.ctypes.data, src.ctypes.data, C.byref(s), offset)
+    return out
+
+
+def repeat(result, sr: Shape, source, ss: Shape):
+    assert result.dtype == np.float32 and source.dtype == np.float32
+    lib().orc_repeat(result.ctypes.data, C.byref(sr), source.ctypes.data, C.byref(ss))
+    return result

@@ -476,3 +476,61 @@ int orc_hardware_threads(void) {
 }
 
 }  // extern "C"
+
+// ---- element-wise kernels -----------------------------------------------------------------------
+// vortx-shaders/src/linalg/op_assign.rs:29-187, contiguous.rs:18-85, repeat.rs:15-43, with
+// Shape::decompose (shape.rs:76-86) and it_vec / it_repeating_vec (shape.rs:52-74).
+namespace {
+struct Idx4 { uint32_t n, c, h, w; };
+inline Idx4 decompose(const orc_shape& s, uint32_t i) {
+    const uint32_t chw = s.c * s.h * s.w, hw = s.h * s.w;
+    const uint32_t i3 = chw ? i / chw : 0;
+    const uint32_t r3 = i - i3 * chw;
+    const uint32_t i2 = hw ? r3 / hw : 0;
+    const uint32_t r2 = r3 - i2 * hw;
+    const uint32_t i1 = s.w ? r2 / s.w : 0;
+    return Idx4{i3, i2, i1, r2 - i1 * s.w};
+}
+inline uint32_t it_vec(const orc_shape& s, const Idx4& id) {
+    return id.n * s.n_stride + id.c * s.c_stride + id.h * s.h_stride + id.w * s.w_stride;
+}
+}  // namespace
+
+extern "C" {
+
+void orc_op_assign(int op, float* a, const orc_shape* sa, const float* b, const orc_shape* sb, uint32_t off_a,
+                   uint32_t off_b) {
+    const uint32_t len = sa->n * sa->c * sa->h * sa->w;
+    for (uint32_t i = 0; i < len; ++i) {
+        const Idx4 id = decompose(*sa, i);
+        const uint32_t ia = off_a + it_vec(*sa, id), ib = off_b + it_vec(*sb, id);
+        switch (op) {
+            case 0: a[ia] = a[ia] + b[ib]; break;
+            case 1: a[ia] = a[ia] - b[ib]; break;
+            case 2: a[ia] = a[ia] * b[ib]; break;
+            case 3: a[ia] = a[ia] / b[ib]; break;
+            default: a[ia] = b[ib]; break;
+        }
+    }
+}
+
+void orc_contiguous(uint32_t* dest, const uint32_t* src, const orc_shape* s, uint32_t offset) {
+    const uint32_t len = s->n * s->c * s->h * s->w;
+    for (uint32_t i = 0; i < len; ++i) {
+        // contiguous.rs:66-76 spells the decomposition out with div and mod; same values
+        const uint32_t h_stride = s->w, c_stride = s->h * s->w, n_stride = s->c * s->h * s->w;
+        const uint32_t n = i / n_stride, c = (i % n_stride) / c_stride, h = (i % c_stride) / h_stride, w = i % h_stride;
+        dest[i] = src[offset + it(*s, n, c, h, w)];
+    }
+}
+
+void orc_repeat(float* result, const orc_shape* sr, const float* source, const orc_shape* ss) {
+    const uint32_t len = sr->n * sr->c * sr->h * sr->w;
+    for (uint32_t i = 0; i < len; ++i) {
+        const Idx4 id = decompose(*sr, i);
+        const Idx4 w{id.n % ss->n, id.c % ss->c, id.h % ss->h, id.w % ss->w};
+        result[it_vec(*sr, id)] = source[it_vec(*ss, w)];
+    }
+}
+
+}  // extern "C"

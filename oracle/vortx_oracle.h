@@ -92,6 +92,13 @@ float orc_reduce_f32(const float* v, const orc_shape* s, int op);
 uint32_t orc_reduce_u32(const uint32_t* v, const orc_shape* s, int op);
 int32_t orc_reduce_i32(const int32_t* v, const orc_shape* s, int op);
 
+/* Element-wise kernels: vortx-shaders/src/linalg/op_assign.rs:29-187 (op: 0 add, 1 sub, 2 mul, 3 div,
+ * 4 copy; offsets as in gpu_copy_with_offsets), contiguous.rs:18-85, repeat.rs:15-43. */
+void orc_op_assign(int op, float* a, const orc_shape* sa, const float* b, const orc_shape* sb,
+                   uint32_t off_a, uint32_t off_b);
+void orc_contiguous(uint32_t* dest, const uint32_t* src, const orc_shape* s, uint32_t offset);
+void orc_repeat(float* result, const orc_shape* sr, const float* source, const orc_shape* ss);
+
 int orc_hardware_threads(void);
 
 #ifdef __cplusplus

@@ -1,0 +1,103 @@
+"""Two GPUs, one process each: the row-sharded GEMV whose epilogue stores y into the peer's memory, followed
+by the cross-GPU barrier kernel, against the CPU oracle; and the NCCL all-gather form of the same product.
+
+Skipped on a box with one GPU.  Ranks are child processes; each leaves only after a final host barrier, with
+no kernel in flight."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu_count():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import vortx_b200 as vb
+    from vortx_b200 import synth
+    from vortx_b200.multi_gpu import PeerScatterGemv, ShardedGemv, shard_blocks
+    be = vb.Backend(rank)
+    rows, cols, slots = 1024, 2048, 3
+    results = {}
+    for qt, name in ((vb.Q4_0, "q4"), (vb.Q8_0, "q8")):
+        w = synth.normal_matrix(rows, cols, seed=21)
+        blocks = vb.quantize(qt, w)
+        mine = shard_blocks(blocks, rows, cols, 18 if qt == vb.Q4_0 else 34, world, rank)
+        g = PeerScatterGemv(be, rows, cols, slots)
+        qm = vb.QuantizedMatrix(be, qt, mine, g.nrows, cols)
+        xs = synth.normal_vectors(slots, cols, seed=22)
+        xd = be.init_buffer(xs.ravel())
+        for rep in range(2):                     # twice: the device-side barrier count must keep advancing
+            for s in range(slots):
+                g.dispatch(qm, xd.ptr + s * cols * 4, s)
+        be.synchronize()
+        y = np.empty(slots * rows, np.float32)
+        be.slow_read_buffer(g.y.local, y.view(np.uint8))
+        results[f"{name}_peer"] = y.reshape(slots, rows)
+        dist.barrier()
+        g.close()
+        # NCCL form through torch tensors on the same stream
+        sg = ShardedGemv.for_backend(be, qt, mine, rows, cols)
+        stream = torch.cuda.ExternalStream(be.stream)
+        with torch.cuda.stream(stream):
+            xt = torch.from_numpy(xs[:1]).cuda()
+            yt = torch.zeros(1, rows, device="cuda")
+            sg.dispatch(xt, yt)
+            stream.synchronize()
+        results[f"{name}_nccl"] = yt.cpu().numpy()
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **results)
+    dist.barrier()
+    be.close()
+    os._exit(0)   # skip NCCL teardown, which has hung on these boxes after all work was done
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_peer_scatter_and_nccl_gemv_on_two_gpus(tmp_path, oracle):
+    import torch.multiprocessing as mp
+    import vortx_b200 as vb
+    from vortx_b200 import synth
+    world = 2
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    for p in procs:
+        if p.is_alive():
+            p.kill()          # the exact child started above
+            pytest.fail("a rank did not finish in time")
+        assert p.exitcode == 0
+    rows, cols, slots = 1024, 2048, 3
+    w = synth.normal_matrix(rows, cols, seed=21)
+    xs = synth.normal_vectors(slots, cols, seed=22)
+    for qt, name in ((vb.Q4_0, "q4"), (vb.Q8_0, "q8")):
+        y64, absdot = oracle.gemv_f64(qt, vb.quantize(qt, w), rows, cols, xs)
+        for r in range(world):
+            got = np.load(tmp_path / f"rank{r}.npz")
+            peer, nccl = got[f"{name}_peer"], got[f"{name}_nccl"]
+            assert np.abs(peer - y64).max() / np.abs(y64).max() <= 1e-4
+            assert (np.abs(peer - y64) <= 2e-6 * absdot).all()
+            assert np.array_equal(nccl[0].view(np.uint32), peer[0].view(np.uint32))   # same kernel, same rows

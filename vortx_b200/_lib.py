@@ -102,8 +102,18 @@ SIGNATURES = {
     "vx_gemv_q": (C.c_int32, [_P, _P, _P, C.c_size_t, _P, C.c_size_t, C.c_size_t]),
     "vx_gemv_q_rows": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t, _P, C.c_size_t, _P,
                                    C.c_size_t, C.c_size_t]),
+    "vx_ipc_export": (C.c_int32, [_P, _P, _P]),
+    "vx_ipc_import": (C.c_int32, [_P, _P, C.POINTER(_P)]),
+    "vx_ipc_release": (C.c_int32, [_P, _P]),
+    "vx_gemv_q_rows_scatter": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t, _P, _P, C.POINTER(_P), C.c_size_t]),
+    "vx_peer_barrier": (C.c_int32, [_P, C.POINTER(_P), C.c_size_t, C.c_size_t]),
     "vx_reduce": (C.c_int32, [_P, C.c_int, C.c_int, C.c_int, _P, C.POINTER(VxShape), C.c_uint64, _P]),
     "vx_reduce_static": (C.c_int32, [C.c_int32, _P, C.c_int, C.c_int, _P, C.POINTER(VxShape), _P]),
+    "vx_op_assign": (C.c_int32, [_P, C.c_int, _P, C.POINTER(VxShape), C.c_uint64, _P, C.POINTER(VxShape), C.c_uint64,
+                                 C.c_uint32, C.c_uint32]),
+    "vx_contiguous": (C.c_int32, [_P, _P, C.c_uint64, _P, C.POINTER(VxShape), C.c_uint64, C.c_uint32]),
+    "vx_repeat": (C.c_int32, [_P, _P, C.POINTER(VxShape), C.c_uint64, _P, C.POINTER(VxShape), C.c_uint64]),
+    "vx_op_assign_dispatch": (C.c_int32, [_P, C.c_int, C.c_int32, _P, _LP, C.c_uint64, _P, _LP, C.c_uint64]),
     "vx_set_option": (C.c_int32, [_P, C.c_char_p, C.c_int64]),
     "vx_get_option": (C.c_int32, [_P, C.c_char_p, C.POINTER(C.c_int64)]),
     # host mirror

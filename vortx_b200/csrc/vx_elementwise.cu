@@ -1,0 +1,186 @@
+// Strided element-wise kernels around the matmul path: in-place binary operations with
+// broadcast strides (vortx-shaders/src/linalg/op_assign.rs:29-187), the strided-to-row-major
+// gather (contiguous.rs:18-85) and the wrap-around tiling copy (repeat.rs:15-43).
+//
+// Index arithmetic follows the shaders exactly — a linear id is decomposed over the first
+// shape's sizes (shape.rs:76-86) and re-composed through each operand's strides (shape.rs:52-54),
+// all in wrapping u32 — so results are the very same bits wherever the reference is defined.
+// One grid-stride loop per kernel; adjacent threads take adjacent linear ids, which are adjacent
+// addresses whenever the innermost stride is 1.
+#include "vx_internal.h"
+
+namespace {
+
+using vx::fail;
+
+struct Idx4 {
+    uint32_t n, c, h, w;
+};
+
+// vortx-shaders/src/linalg/shape.rs:76-86 (checked_div(..).unwrap_or(0) for empty dimensions)
+__host__ __device__ __forceinline__ Idx4 decompose(const vx_shape& s, uint32_t i) {
+    const uint32_t chw = s.c * s.h * s.w, hw = s.h * s.w;
+    const uint32_t i3 = chw ? i / chw : 0;
+    const uint32_t r3 = i - i3 * chw;
+    const uint32_t i2 = hw ? r3 / hw : 0;
+    const uint32_t r2 = r3 - i2 * hw;
+    const uint32_t i1 = s.w ? r2 / s.w : 0;
+    return Idx4{i3, i2, i1, r2 - i1 * s.w};
+}
+__host__ __device__ __forceinline__ uint32_t compose(const vx_shape& s, const Idx4& id) {
+    return id.n * s.n_stride + id.c * s.c_stride + id.h * s.h_stride + id.w * s.w_stride;
+}
+__host__ __device__ __forceinline__ uint32_t shape_len(const vx_shape& s) { return s.n * s.c * s.h * s.w; }
+
+template <int OP>
+__device__ __forceinline__ float apply(float a, float b) {
+    if (OP == VX_OP_ADD) return __fadd_rn(a, b);
+    if (OP == VX_OP_SUB) return __fsub_rn(a, b);
+    if (OP == VX_OP_MUL) return __fmul_rn(a, b);
+    if (OP == VX_OP_DIV) return __fdiv_rn(a, b);
+    return b;
+}
+
+template <int OP>
+__global__ void __launch_bounds__(256)
+op_assign_kernel(float* __restrict__ a, const float* __restrict__ b, const vx_shape sa, const vx_shape sb,
+                 uint32_t off_a, uint32_t off_b) {
+    const uint32_t len = shape_len(sa);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < len; i += gridDim.x * blockDim.x) {
+        const Idx4 id = decompose(sa, i);
+        const uint32_t ia = off_a + compose(sa, id), ib = off_b + compose(sb, id);
+        a[ia] = apply<OP>(a[ia], b[ib]);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+contiguous_kernel(uint32_t* __restrict__ dest, const uint32_t* __restrict__ src, const vx_shape s, uint32_t offset) {
+    const uint32_t len = shape_len(s);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < len; i += gridDim.x * blockDim.x) {
+        const Idx4 id = decompose(s, i);
+        dest[i] = src[offset + compose(s, id)];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+repeat_kernel(float* __restrict__ result, const float* __restrict__ source, const vx_shape sr, const vx_shape ss) {
+    const uint32_t len = shape_len(sr);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < len; i += gridDim.x * blockDim.x) {
+        const Idx4 id = decompose(sr, i);
+        // shape.rs:72-74: the source index wraps around each source dimension
+        const Idx4 w = Idx4{ss.n ? id.n % ss.n : 0, ss.c ? id.c % ss.c : 0, ss.h ? id.h % ss.h : 0, ss.w ? id.w % ss.w : 0};
+        result[compose(sr, id)] = source[compose(ss, w)];
+    }
+}
+
+uint64_t span(const vx_shape& s) {
+    if (s.n == 0 || s.c == 0 || s.h == 0 || s.w == 0) return 0;
+    return (uint64_t)(s.n - 1) * s.n_stride + (uint64_t)(s.c - 1) * s.c_stride + (uint64_t)(s.h - 1) * s.h_stride +
+           (uint64_t)(s.w - 1) * s.w_stride + 1;
+}
+
+unsigned grid_for(const vx_context* ctx, uint32_t len) {
+    const unsigned want = (len + 255) / 256;
+    return std::max(1u, std::min(want, (unsigned)ctx->sm_count * 16));
+}
+
+vx_status cap_check(const vx_context* ctx, const char* what, const vx_shape& s, uint64_t offset, uint64_t cap) {
+    if (cap == 0 || vx::option(ctx, "bounds_check", 1) == 0) return VX_OK;
+    const uint64_t sp = span(s);
+    if (sp != 0 && offset + sp > cap)
+        return fail(VX_ERR_OUT_OF_BOUNDS, "%s layout reaches element %llu of a buffer holding %llu", what,
+                    (unsigned long long)(offset + sp - 1), (unsigned long long)cap);
+    return VX_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+vx_status vx_op_assign(vx_context* ctx, vx_op op, float* a, const vx_shape* shape_a, uint64_t cap_a, const float* b,
+                       const vx_shape* shape_b, uint64_t cap_b, uint32_t offset_a, uint32_t offset_b) {
+    VX_REQUIRE(ctx && shape_a && shape_b, VX_ERR_INVALID_ARGUMENT, "vx_op_assign: null argument");
+    VX_REQUIRE(op >= VX_OP_ADD && op <= VX_OP_COPY, VX_ERR_INVALID_ARGUMENT, "unknown operation %d", (int)op);
+    const uint32_t len = shape_len(*shape_a);
+    if (len == 0) return VX_OK;
+    VX_REQUIRE(a && b, VX_ERR_INVALID_ARGUMENT, "vx_op_assign: null device pointer");
+    // b is indexed with a's ids: what it touches is a's extent walked with b's strides
+    vx_shape touched_b = *shape_b;
+    touched_b.n = shape_a->n; touched_b.c = shape_a->c; touched_b.h = shape_a->h; touched_b.w = shape_a->w;
+    vx_status st;
+    if ((st = cap_check(ctx, "a", *shape_a, offset_a, cap_a)) != VX_OK) return st;
+    if ((st = cap_check(ctx, "b", touched_b, offset_b, cap_b)) != VX_OK) return st;
+    vx::DeviceGuard guard(ctx->device);
+    const unsigned grid = grid_for(ctx, len);
+    switch (op) {
+        case VX_OP_ADD: op_assign_kernel<VX_OP_ADD><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        case VX_OP_SUB: op_assign_kernel<VX_OP_SUB><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        case VX_OP_MUL: op_assign_kernel<VX_OP_MUL><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        case VX_OP_DIV: op_assign_kernel<VX_OP_DIV><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        default: op_assign_kernel<VX_OP_COPY><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+    }
+    VX_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return VX_OK;
+}
+
+vx_status vx_contiguous(vx_context* ctx, void* dest, uint64_t cap_dest, const void* src, const vx_shape* shape_src,
+                        uint64_t cap_src, uint32_t offset) {
+    VX_REQUIRE(ctx && shape_src, VX_ERR_INVALID_ARGUMENT, "vx_contiguous: null argument");
+    const uint32_t len = shape_len(*shape_src);
+    if (len == 0) return VX_OK;
+    VX_REQUIRE(dest && src, VX_ERR_INVALID_ARGUMENT, "vx_contiguous: null device pointer");
+    VX_REQUIRE(cap_dest == 0 || len <= cap_dest, VX_ERR_OUT_OF_BOUNDS, "destination holds %llu elements, %u needed",
+               (unsigned long long)cap_dest, len);
+    vx_status st = cap_check(ctx, "source", *shape_src, offset, cap_src);
+    if (st != VX_OK) return st;
+    vx::DeviceGuard guard(ctx->device);
+    contiguous_kernel<<<grid_for(ctx, len), 256, 0, ctx->stream>>>(static_cast<uint32_t*>(dest),
+                                                                   static_cast<const uint32_t*>(src), *shape_src, offset);
+    VX_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return VX_OK;
+}
+
+vx_status vx_repeat(vx_context* ctx, float* result, const vx_shape* shape_result, uint64_t cap_result,
+                    const float* source, const vx_shape* shape_source, uint64_t cap_source) {
+    VX_REQUIRE(ctx && shape_result && shape_source, VX_ERR_INVALID_ARGUMENT, "vx_repeat: null argument");
+    const uint32_t len = shape_len(*shape_result);
+    if (len == 0) return VX_OK;
+    VX_REQUIRE(result && source, VX_ERR_INVALID_ARGUMENT, "vx_repeat: null device pointer");
+    VX_REQUIRE(shape_len(*shape_source) != 0, VX_ERR_SHAPE, "vx_repeat: empty source");
+    vx_status st;
+    if ((st = cap_check(ctx, "result", *shape_result, 0, cap_result)) != VX_OK) return st;
+    if ((st = cap_check(ctx, "source", *shape_source, 0, cap_source)) != VX_OK) return st;
+    vx::DeviceGuard guard(ctx->device);
+    repeat_kernel<<<grid_for(ctx, len), 256, 0, ctx->stream>>>(result, source, *shape_result, *shape_source);
+    VX_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return VX_OK;
+}
+
+// OpAssign::launch / Repeat::launch level (src/linalg/op_assign.rs:38-143, src/linalg/repeat.rs:24-88):
+// broadcast_assign the two layouts (VX_ERR_SHAPE where the reference panics), canonicalise, apply the
+// view offsets, launch.  is_repeat selects the tiling copy.
+vx_status vx_op_assign_dispatch(vx_context* ctx, vx_op op, int32_t is_repeat, float* a, const vx_layout* layout_a,
+                                uint64_t cap_a, const float* b, const vx_layout* layout_b, uint64_t cap_b) {
+    VX_REQUIRE(ctx && layout_a && layout_b, VX_ERR_INVALID_ARGUMENT, "vx_op_assign_dispatch: null argument");
+    vx_layout ta, tb, ca, cb;
+    vx_status st = vx_layout_broadcast_assign(layout_a, layout_b, &ta, &tb);
+    if (st != VX_OK) return st;
+    if ((st = vx_layout_canonicalize(&ta, &ca)) != VX_OK) return st;
+    if ((st = vx_layout_canonicalize(&tb, &cb)) != VX_OK) return st;
+    vx_shape sa, sb;
+    vx_layout_to_shape(&ca, &sa);
+    vx_layout_to_shape(&cb, &sb);
+    VX_REQUIRE(cap_a == 0 || layout_a->offset <= cap_a, VX_ERR_OUT_OF_BOUNDS, "a view offset beyond its buffer");
+    VX_REQUIRE(cap_b == 0 || layout_b->offset <= cap_b, VX_ERR_OUT_OF_BOUNDS, "b view offset beyond its buffer");
+    float* pa = a ? a + layout_a->offset : nullptr;
+    const float* pb = b ? b + layout_b->offset : nullptr;
+    const uint64_t ra = cap_a ? std::max<uint64_t>(1, cap_a - layout_a->offset) : 0;
+    const uint64_t rb = cap_b ? std::max<uint64_t>(1, cap_b - layout_b->offset) : 0;
+    if (is_repeat) return vx_repeat(ctx, pa, &sa, ra, pb, &sb, rb);
+    return vx_op_assign(ctx, op, pa, &sa, ra, pb, &sb, rb, 0, 0);
+}
+
+}  // extern "C"

@@ -45,6 +45,11 @@ struct StreamParams {
     uint32_t nrows;
     const float* x;
     float* y;
+    // Row-sharded use: besides y, every finished row is stored into these buffers (the same slab
+    // of the full-length y on each peer GPU, mapped into this process), so that no collective is
+    // needed afterwards.  Plain stores to peer memory; nothing is ever loaded from a peer.
+    float* y_peer[vx::kMaxPeers];
+    uint32_t n_peer;
     uint32_t tpr;           // threads per row group (multiple of 32)
     uint32_t stages;
     uint32_t stage_bytes;
@@ -142,6 +147,7 @@ gemv_stream_kernel(const StreamParams p) {
                 float sum = 0.0f;
                 for (uint32_t wv = 0; wv < wpr; ++wv) sum += slot[lane * kWarps + wv];
                 p.y[row] = sum;
+                for (uint32_t d = 0; d < p.n_peer; ++d) p.y_peer[d][row] = sum;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(b));
@@ -363,7 +369,7 @@ namespace vx {
 // One vector (batch 1).  *eligible = false (nothing launched) when the row is too long for
 // the shared-memory ring or the register-resident x.
 vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
-                             const float* x, float* y, bool* eligible) {
+                             const float* x, float* y, float* const* y_peer, uint32_t n_peer, bool* eligible) {
     const uint32_t TR = option(ctx, "gemv.tile_rows", 8) == 4 ? 4 : 8;
     *eligible = false;
     const uint32_t nb = (uint32_t)w->blocks_per_row;
@@ -412,6 +418,8 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
     p.nrows = nrows;
     p.x = x;
     p.y = y;
+    p.n_peer = std::min<uint32_t>(n_peer, kMaxPeers);
+    for (uint32_t d = 0; d < (uint32_t)kMaxPeers; ++d) p.y_peer[d] = d < p.n_peer ? y_peer[d] : nullptr;
     p.tpr = tpr;
     p.stages = stages;
     p.stage_bytes = stage_bytes;

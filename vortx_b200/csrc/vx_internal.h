@@ -104,7 +104,14 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
 
 // Streaming GEMV (vx_gemv_stream.cu), one vector.  *eligible = false when the row shape does
 // not fit its shared-memory ring or register-resident x; nothing is launched then.
+// y_peer / n_peer: further buffers that receive every row as well (peer GPUs' y), or null / 0.
+constexpr int kMaxPeers = 7;
+// Arrival flags of the cross-GPU barrier: flags[r] is rank r's array of `world` counters (its
+// own memory for r == this rank, a mapped peer pointer otherwise).
+struct PeerFlags {
+    uint32_t* flags[kMaxPeers + 1];
+};
 vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
-                             const float* x, float* y, bool* eligible);
+                             const float* x, float* y, float* const* y_peer, uint32_t n_peer, bool* eligible);
 
 }  // namespace vx

@@ -1,0 +1,130 @@
+// Multi-GPU plumbing for the row-sharded GEMV without a collective: CUDA IPC mapping of peer
+// buffers (one process per GPU), the GEMV whose epilogue also stores every row into the peers'
+// copies of y, and a small cross-GPU arrival barrier.
+//
+// vortx has no multi-device notion beyond a device ordinal (src/linalg/gemm.rs:353); nothing here
+// has a reference counterpart.  Design rules: a GPU only ever STORES to a peer (plain st.global
+// through an NVLink-mapped pointer) and only loads from its own memory; no TMA touches peer
+// memory; every device-side wait is bounded and reports through the context's status word.
+#include <cstring>
+
+#include "vx_internal.h"
+
+namespace {
+
+using vx::fail;
+
+// Each rank owns an array of 64 u32 in its own memory: entries [0, world) are arrival counters,
+// entry 32 is the rank's own count of barriers executed.  A barrier takes the next epoch e from
+// that count (so a replayed CUDA graph keeps advancing, and all ranks, which run the same
+// sequence of barriers, agree on e), stores e into entry [rank] of EVERY rank's array (its own
+// included), then waits until all world entries of its own array have reached e.  Stores made
+// before the announcement (the GEMV's rows, written by an earlier kernel of the same stream) are
+// ordered before it by the system-scope fence.
+constexpr uint32_t kEpochSlot = 32;
+
+__global__ void peer_barrier_kernel(vx::PeerFlags peers, uint32_t world, uint32_t rank, vx::DeviceStatus* status) {
+    const uint32_t t = threadIdx.x;
+    // Let a dependent-launch GEMV behind this kernel become resident and prefetch its weights
+    // now; it reads x and writes y only after this kernel has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint32_t epoch = 0;
+    if (t == 0) {
+        epoch = peers.flags[rank][kEpochSlot] + 1;
+        peers.flags[rank][kEpochSlot] = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    if (t < world) {
+        __threadfence_system();
+        volatile uint32_t* dst = peers.flags[t] + rank;  // my entry in rank t's array
+        *dst = epoch;
+        __threadfence_system();
+        // wait for rank t's announcement in my own array (bounded: ~0.2 s of SM clocks)
+        volatile uint32_t* mine = peers.flags[rank] + t;
+        const long long start = clock64();
+        bool ok = false;
+        while (!ok) {
+            for (int i = 0; i < 32 && !ok; ++i) ok = (int32_t)(*mine - epoch) >= 0;
+            if (!ok && clock64() - start > 400ll * 1000 * 1000) break;
+        }
+        if (!ok) {
+            volatile vx::DeviceStatus* v = status;
+            v->detail = t;
+            v->code = 31;
+            __threadfence_system();
+        }
+        __threadfence_system();
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+vx_status vx_ipc_export(vx_context* ctx, const void* device_ptr, void* handle64) {
+    VX_REQUIRE(ctx && device_ptr && handle64, VX_ERR_INVALID_ARGUMENT, "vx_ipc_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    vx::DeviceGuard guard(ctx->device);
+    cudaIpcMemHandle_t h;
+    VX_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(device_ptr)));
+    memcpy(handle64, &h, 64);
+    return VX_OK;
+}
+
+vx_status vx_ipc_import(vx_context* ctx, const void* handle64, void** device_ptr) {
+    VX_REQUIRE(ctx && handle64 && device_ptr, VX_ERR_INVALID_ARGUMENT, "vx_ipc_import: null argument");
+    *device_ptr = nullptr;
+    vx::DeviceGuard guard(ctx->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    VX_CUDA(cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return VX_OK;
+}
+
+vx_status vx_ipc_release(vx_context* ctx, void* device_ptr) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_ipc_release: null context");
+    if (!device_ptr) return VX_OK;
+    vx::DeviceGuard guard(ctx->device);
+    VX_CUDA(cudaStreamSynchronize(ctx->stream));
+    VX_CUDA(cudaIpcCloseMemHandle(device_ptr));
+    return VX_OK;
+}
+
+vx_status vx_gemv_q_rows_scatter(vx_context* ctx, const vx_qweights* w, size_t row0, size_t nrows, const float* x,
+                                 float* y, float* const* peer_y, size_t n_peers) {
+    VX_REQUIRE(ctx && w, VX_ERR_INVALID_ARGUMENT, "vx_gemv_q_rows_scatter: null context or weights");
+    VX_REQUIRE(w->device == ctx->device, VX_ERR_INVALID_ARGUMENT, "weights live on device %d, context on %d",
+               w->device, ctx->device);
+    VX_REQUIRE(row0 <= w->rows && nrows <= w->rows - row0, VX_ERR_OUT_OF_BOUNDS,
+               "rows [%zu, %zu) outside a matrix of %zu rows", row0, row0 + nrows, w->rows);
+    VX_REQUIRE(n_peers <= (size_t)vx::kMaxPeers, VX_ERR_INVALID_ARGUMENT, "at most %d peers", vx::kMaxPeers);
+    if (nrows == 0) return VX_OK;
+    VX_REQUIRE(x && y && (peer_y || n_peers == 0), VX_ERR_INVALID_ARGUMENT, "vx_gemv_q_rows_scatter: null vector");
+    for (size_t i = 0; i < n_peers; ++i)
+        VX_REQUIRE(peer_y[i], VX_ERR_INVALID_ARGUMENT, "peer buffer %zu is null", i);
+    vx::DeviceGuard guard(ctx->device);
+    bool eligible = false;
+    vx_status st = vx::launch_gemv_stream(ctx, w, row0, (uint32_t)nrows, x, y, peer_y, (uint32_t)n_peers, &eligible);
+    if (st != VX_OK) return st;
+    VX_REQUIRE(eligible, VX_ERR_UNSUPPORTED, "rows of %zu columns do not fit the streaming kernel", w->cols);
+    return VX_OK;
+}
+
+vx_status vx_peer_barrier(vx_context* ctx, uint32_t* const* flags, size_t world, size_t rank) {
+    VX_REQUIRE(ctx && flags, VX_ERR_INVALID_ARGUMENT, "vx_peer_barrier: null argument");
+    VX_REQUIRE(world >= 1 && world <= (size_t)vx::kMaxPeers + 1 && rank < world, VX_ERR_INVALID_ARGUMENT,
+               "world %zu / rank %zu out of range", world, rank);
+    vx::PeerFlags p;
+    for (size_t i = 0; i < (size_t)vx::kMaxPeers + 1; ++i) {
+        p.flags[i] = i < world ? flags[i] : nullptr;
+        VX_REQUIRE(i >= world || flags[i], VX_ERR_INVALID_ARGUMENT, "flag array of rank %zu is null", i);
+    }
+    vx::DeviceGuard guard(ctx->device);
+    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(p, (uint32_t)world, (uint32_t)rank, ctx->d_status);
+    VX_CUDA(cudaGetLastError());
+    ctx->launches++;
+    ctx->status_dirty = true;
+    return VX_OK;
+}
+
+}  // extern "C"

@@ -119,6 +119,62 @@ class Reduce:
         _lib.check(st)
 
 
+class OpAssignVariant:
+    """src/linalg/op_assign.rs:12-24"""
+
+    Add, Sub, Mul, Div, Copy = 0, 1, 2, 3, 4
+
+
+class OpAssign:
+    """src/linalg/op_assign.rs:26-143: a op= b with b broadcast to a."""
+
+    @classmethod
+    def from_backend(cls, backend: Backend) -> "OpAssign":
+        return cls()
+
+    def launch(self, backend: Backend, shapes, pass_, variant: int, a, b, _repeat: int = 0) -> None:
+        am, br = a.as_tensor_mut(), b.as_tensor_ref()
+        ab, bb = am.raw_buffer(), br.raw_buffer()
+        if ab.dtype != np.float32 or bb.dtype != np.float32:
+            raise TypeError("OpAssign / Repeat take f32 tensors")
+        _lib.check(_lib.load().vx_op_assign_dispatch(backend._ctx, variant, _repeat, ab.ptr, C.byref(am.layout()._c),
+                                                     ab.len(), bb.ptr, C.byref(br.layout()._c), bb.len()))
+
+
+class Repeat:
+    """src/linalg/repeat.rs:16-88: tiles `source` into `destination` by wrapping indices."""
+
+    @classmethod
+    def from_backend(cls, backend: Backend) -> "Repeat":
+        return cls()
+
+    def launch(self, backend: Backend, shapes, pass_, destination, source) -> None:
+        OpAssign().launch(backend, shapes, pass_, OpAssignVariant.Copy, destination, source, _repeat=1)
+
+
+class Contiguous:
+    """src/linalg/contiguous.rs:13-129: gathers a strided view of 4-byte elements into a row-major tensor."""
+
+    @classmethod
+    def from_backend(cls, backend: Backend) -> "Contiguous":
+        return cls()
+
+    def launch(self, backend: Backend, shapes, pass_, out, tensor, offset: Optional[int] = None) -> None:
+        o, t = out.as_tensor_mut(), tensor.as_tensor_ref()
+        ob, tb = o.raw_buffer(), t.raw_buffer()
+        if ob.dtype.itemsize != 4 or tb.dtype.itemsize != 4:
+            raise TypeError("Contiguous only supports tensors with 4-bytes elements.")
+        if tuple(t.layout().size) != tuple(o.layout().size):
+            raise _lib.ShapeMismatch(_lib.VX_ERR_SHAPE, f"{t.layout()} vs {o.layout()}")
+        if not o.is_contiguous():
+            raise ValueError(f"Output tensor must be contiguous: {o.layout()}.")
+        shape = t.layout().canonicalize().into_gpu()
+        # with an explicit offset the reference binds the raw buffer and adds the offset in the kernel
+        off = t.layout().offset if offset is None else offset
+        _lib.check(_lib.load().vx_contiguous(backend._ctx, ob.ptr + o.layout().offset * 4, ob.len() - o.layout().offset,
+                                             tb.ptr, C.byref(shape), tb.len(), off))
+
+
 # --------------------------------------------------------------------- quantised --------
 
 Q8_0 = _lib.VX_Q8_0

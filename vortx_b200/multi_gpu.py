@@ -31,6 +31,91 @@ def shard_blocks(blocks: np.ndarray, rows: int, cols: int, block_bytes: int, wor
     return blocks[row0 * per_row:(row0 + n) * per_row]
 
 
+class PeerBuffers:
+    """One device buffer per rank, each mapped into every other rank's process with CUDA IPC.
+
+    `local` is this rank's buffer (a GpuBuffer from vx_alloc), `ptrs[r]` the device pointer through which
+    this process reaches rank r's buffer (its own pointer for r == rank).  Handles travel through the
+    process group (all_gather_object); the mapping is peer-store only by convention of its users."""
+
+    def __init__(self, backend, nbytes: int, group=None):
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _lib
+        self.backend, self.group = backend, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        lib = _lib.load()
+        self.local = backend.uninit_buffer(nbytes, dtype=np.uint8)
+        _lib.check(lib.vx_memset(backend._ctx, self.local.ptr, 0, nbytes))
+        backend.synchronize()
+        handle = (C.c_ubyte * 64)()
+        _lib.check(lib.vx_ipc_export(backend._ctx, self.local.ptr, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.ptrs = []
+        self._mapped = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(self.local.ptr)
+                continue
+            p = C.c_void_p()
+            buf = (C.c_ubyte * 64).from_buffer_copy(h)
+            _lib.check(lib.vx_ipc_import(backend._ctx, buf, C.byref(p)))
+            self.ptrs.append(p.value)
+            self._mapped.append(p.value)
+
+    def close(self) -> None:
+        from . import _lib
+        lib = _lib.load()
+        for p in self._mapped:
+            lib.vx_ipc_release(self.backend._ctx, p)
+        self._mapped = []
+
+
+class PeerScatterGemv:
+    """Row-sharded GEMV whose kernel stores each finished row into every peer's y directly (NVLink
+    stores from the epilogue), followed by a one-warp arrival barrier across the GPUs — no collective.
+
+    y lives in `PeerBuffers` (f32, `slots` full-length vectors); `dispatch(x_ptr, slot)` computes this rank's
+    rows of y[slot] and returns once the barrier kernel is queued: after it, on this rank's stream, y[slot]
+    is complete on this GPU."""
+
+    def __init__(self, backend, rows: int, cols: int, slots: int, group=None):
+        import torch.distributed as dist
+        self.backend, self.rows, self.cols, self.slots = backend, rows, cols, slots
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 GPUs of one node")
+        self.row0, self.nrows = row_shard(rows, self.world, self.rank)
+        self.y = PeerBuffers(backend, slots * rows * 4, group)
+        self.flags = PeerBuffers(backend, 64 * 4, group)
+        self.epoch = 0
+        dist.barrier(group=group)
+
+    def y_ptr(self, slot: int) -> int:
+        return self.y.local.ptr + slot * self.rows * 4
+
+    def dispatch(self, weights, x_ptr: int, slot: int) -> None:
+        """weights: this rank's QuantizedMatrix slab (nrows x cols)."""
+        import ctypes as C
+        from . import _lib
+        lib = _lib.load()
+        off = (slot * self.rows + self.row0) * 4
+        peers = [self.y.ptrs[r] + off for r in range(self.world) if r != self.rank]
+        arr = (C.c_void_p * max(1, len(peers)))(*peers)
+        _lib.check(lib.vx_gemv_q_rows_scatter(self.backend._ctx, weights._h, 0, self.nrows, x_ptr,
+                                              self.y.local.ptr + off, arr, len(peers)))
+        flags = (C.c_void_p * self.world)(*self.flags.ptrs)
+        _lib.check(lib.vx_peer_barrier(self.backend._ctx, flags, self.world, self.rank))
+
+    def close(self) -> None:
+        self.backend.synchronize()
+        self.y.close()
+        self.flags.close()
+
+
 class ShardedGemv:
     """y = W x with W split by rows across the ranks of `group`.
 
