@@ -161,7 +161,7 @@ def run_reference(args):
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------ GPU arm ----
@@ -209,12 +209,19 @@ def run_ours(args):
     x_dev = torch.from_numpy(x_host).to(dev)
     y_full = torch.zeros(LAYERS, ROWS, device=dev, dtype=torch.float32)  # one y per layer
 
-    # N > 1: how the slabs of y reach every GPU.  "peer" (default): the GEMV's epilogue stores each row
-    # into every peer's y over NVLink and a one-warp barrier kernel follows; "nccl": all-gather after the kernel.
-    scatter = None
+    # N > 1: how the rows of y reach every GPU.
+    #   "peer" (default): the step is a CHAIN.  Rows are dealt out in turn (rank r owns rows r, r + N, ...);
+    #       the GEMV's epilogue stores each row as a {value, generation} pair into an exchange vector on
+    #       every GPU over NVLink, and the next GEMV takes its x from the first COLS elements of that vector
+    #       (rows of every rank), re-reading pairs that have not arrived yet while its weights already stream.
+    #       GEMV 0 of a step reads the plain x; the step ends by unpacking the last vector to plain f32.
+    #   "peer-barrier": plain peer stores from the epilogue + a one-warp barrier kernel after every GEMV.
+    #   "nccl": all-gather after every GEMV.
+    scatter = chain = None
     if n > 1:
         from vortx_b200.multi_gpu import PeerScatterGemv
-        scatter = PeerScatterGemv(be, ROWS, COLS, LAYERS)
+        scatter = PeerScatterGemv(be, ROWS, COLS, LAYERS, vectors=0)
+        chain = PeerScatterGemv(be, ROWS, COLS, 1, vectors=2, cyclic=True)
 
     def gemv(layer: int, xptr: int):
         yptr = y_full[layer].data_ptr() + row0 * 4
@@ -223,8 +230,14 @@ def run_ours(args):
             raise RuntimeError(_lib.last_error())
 
     def step_device(exchange=args.exchange):
+        if n > 1 and exchange == "peer":
+            chain.dispatch_chained(layers[0], 0, x_ptr=x_dev.data_ptr())
+            for l in range(1, LAYERS):
+                chain.dispatch_chained(layers[l], l % 2, x_vec=(l - 1) % 2)
+            chain.unpack((LAYERS - 1) % 2, chain.y_ptr(0))
+            return
         for l in range(LAYERS):
-            if n > 1 and exchange == "peer":
+            if n > 1 and exchange == "peer-barrier":
                 scatter.dispatch(layers[l], x_dev.data_ptr(), l)
             else:
                 gemv(l, x_dev.data_ptr())
@@ -304,8 +317,8 @@ def run_ours(args):
     def step_e2e():
         for l in range(LAYERS):
             _lib.check(lib.vx_upload(be._ctx, x_stage.data_ptr(), x_pin.data_ptr(), COLS * 4))
-            if n > 1 and args.exchange == "peer":
-                scatter.dispatch(layers[l], x_stage.data_ptr(), l)
+            if n > 1 and args.exchange.startswith("peer"):
+                scatter.dispatch(layers[l], x_stage.data_ptr(), l)   # y is read back at once: barrier form
                 src = scatter.y_ptr(l)
             else:
                 gemv(l, x_stage.data_ptr())
@@ -332,26 +345,28 @@ def run_ours(args):
     note("end-to-end timing done")
     extra = {}
     if n > 1:
-        # the other way of exchanging y, timed the same way, for comparison
-        other = "nccl" if args.exchange == "peer" else "peer"
-        step_device(other)
-        torch.cuda.synchronize()
-        og = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(og, stream=stream):
+        # the other ways of exchanging y, timed the same way, for comparison
+        for other in ("peer", "peer-barrier", "nccl"):
+            if other == args.exchange:
+                continue
             step_device(other)
-        for _ in range(3):
-            og.replay()
-        barrier()
-        o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        o0.record(stream)
-        for _ in range(args.steps):
-            og.replay()
-        o1.record(stream)
-        barrier()
-        t = torch.tensor([o0.elapsed_time(o1)], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        other_ms = float(t.item()) / args.steps
-        extra[f"exchange_{other}"] = {"ms_per_step": other_ms, "GB/s": bytes_per_step / (other_ms * 1e-3) / 1e9}
+            torch.cuda.synchronize()
+            og = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(og, stream=stream):
+                step_device(other)
+            for _ in range(3):
+                og.replay()
+            barrier()
+            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            o0.record(stream)
+            for _ in range(args.steps):
+                og.replay()
+            o1.record(stream)
+            barrier()
+            t = torch.tensor([o0.elapsed_time(o1)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            other_ms = float(t.item()) / args.steps
+            extra[f"exchange_{other}"] = {"ms_per_step": other_ms, "GB/s": bytes_per_step / (other_ms * 1e-3) / 1e9}
         extra["kernels_only"] = {"us_per_launch": launch_us, "GB/s_per_gpu": achieved}
     cpu = None
     if rank == 0 and n == 1:
@@ -372,8 +387,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": "q4_0_gemv_28672x8192_x32", "rows": ROWS, "cols": COLS, "batch": 1,
                        "gemv_per_step": LAYERS,
-                       "sharding": (f"rows/{n} per GPU; y exchanged by " + ("peer stores from the kernel epilogue + barrier kernel"
-                                    if args.exchange == "peer" else "NCCL all-gather")) if n > 1 else "none",
+                       "sharding": (f"rows/{n} per GPU; y exchanged by " + EXCHANGE_TEXT[args.exchange]) if n > 1 else "none",
                        "l2": "inputs larger than L2: 32 weight copies walked in turn", "launch": "CUDA graph replay"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": LAYERS * COLS * 4, "d2h_bytes_per_step": LAYERS * ROWS * 4},
@@ -388,7 +402,7 @@ def run_ours(args):
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line), flush=True)
+        emit(line)
     if n > 1:
         # NCCL's communicator teardown was seen to hang on this pool's boxes after all work had
         # completed; every rank has synchronised and rank 0 has printed, so leave without it.
@@ -513,8 +527,37 @@ def run_profile_case(name: str):
         for _ in range(4):
             _lib.check(lib.vx_gemm_f32(be._ctx, mode, c.ptr, a.ptr, b.ptr, C.byref(sh), 0, 0, 0))
     be.synchronize()
-    print(json.dumps({"profile_case": name, "kernels_launched": be.launch_count()}), flush=True)
+    emit({"profile_case": name, "kernels_launched": be.launch_count()})
     be.close()
+
+
+_REAL_STDOUT = None
+
+
+def isolate_stdout():
+    """Libraries (NCCL's version banner, for one) write to file descriptor 1.  Point it at stderr for the
+    run and keep the original for the one JSON line."""
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, data)
+
+
+EXCHANGE_TEXT = {
+    "peer": "chain of dependent GEMVs: rows stored as {value, generation} pairs into every GPU's exchange vector from "
+            "the kernel epilogue, awaited pair by pair in the next GEMV's prologue; nothing between the GEMVs",
+    "peer-barrier": "peer stores from the kernel epilogue + a barrier kernel after every GEMV",
+    "nccl": "NCCL all-gather after every GEMV",
+}
 
 
 def main():
@@ -523,11 +566,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
-                    help="N > 1: how y is exchanged (peer stores from the kernel, or an NCCL all-gather)")
+    ap.add_argument("--exchange", choices=sorted(EXCHANGE_TEXT), default="peer",
+                    help="N > 1: how the slabs of y reach every GPU")
     ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), default=None,
                     help="run a few launches of one kernel on a small footprint (for ncu) and exit")
     args = ap.parse_args()
+    isolate_stdout()
     if args.profile_case:
         run_profile_case(args.profile_case)
     elif args.impl == "reference":

@@ -164,7 +164,31 @@ VX_API vx_status vx_ipc_release(vx_context* ctx, void* device_ptr);
  * pointers are already advanced to where the slab belongs in each full-length y. */
 VX_API vx_status vx_gemv_q_rows_scatter(vx_context* ctx, const vx_qweights* w, size_t row0, size_t nrows,
                                         const float* x, float* y, float* const* peer_y, size_t n_peers);
-/* flags[r] (r < world <= 8) is rank r's array of 64 u32, zero-initialised: its own for
+/* The same GEMV with the exchange fused into the kernel, for chains of dependent GEMVs (y of one is
+ * x of the next): nothing runs between the links, no flag, fence or collective.
+ * An exchange vector of n elements is vx_xvec_bytes(n) bytes of zero-initialised device memory,
+ * 16-byte aligned, one per rank and mapped into the peers: a 256-byte header that only its owner
+ * uses (word 0 = generation, how many times the vector has been written completely) and one 8-byte
+ * pair {f32 value, u32 generation} per element.  Value and arrival mark travel in one 64-bit store.
+ *   writer  row row0 + r of W times x (r < nrows) goes, tagged generation + 1, into element
+ *           y_row0 + r * y_stride of y_xvec (this rank's) and of every peer_y_xvec[i] — stride 1
+ *           for a contiguous slab of rows, the world size for rows dealt out in turn; into the
+ *           plain y[r] as well unless y is null.  The grid's last block bumps the header.
+ *   reader  with x_xvec non-null, x is that flagged vector (w's column count; the plain x is
+ *           ignored): the weight stream starts at once, and each thread re-reads, for at most about
+ *           0.2 s, the pairs that do not carry x_xvec's generation yet.
+ * Every rank issues the same sequence of launches on the same vectors; a rank with no rows cannot
+ * take part.  A vector is written again only after every rank has read it: a chain alternates
+ * between two vectors (a rank can start link l + 1 only with all rows of link l, which every rank
+ * produces after it has read its x).  vx_xvec_unpack turns a vector into plain f32, waiting the
+ * same way; it is how a chain ends. */
+VX_API size_t vx_xvec_bytes(size_t n);
+VX_API vx_status vx_gemv_q_rows_exchange(vx_context* ctx, const vx_qweights* w, size_t row0, size_t nrows,
+                                         const void* x_xvec, const float* x, float* y, void* y_xvec,
+                                         void* const* peer_y_xvec, size_t n_peers, size_t y_row0,
+                                         size_t y_stride);
+VX_API vx_status vx_xvec_unpack(vx_context* ctx, const void* xvec, size_t n, float* out);
+/* flags[r] (r < world <= 8) is rank r's sync block of 64 u32, zero-initialised: its own for
  * r == rank, a mapped peer pointer otherwise.  Stream-ordered: after all earlier work of this
  * context it announces this rank's next barrier number to every rank, then waits, on the device
  * and for at most about 0.2 s, until every rank has announced the same number (all ranks must

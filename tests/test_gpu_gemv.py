@@ -119,3 +119,49 @@ def test_gemv_linearity_full_size(backend):
     y = _run(backend, vb.Q4_0, blocks.ravel(), rows, cols, xs)
     lin = 2.0 * y[0].astype(np.float64) - 0.5 * y[1].astype(np.float64)
     assert np.abs(y[2] - lin).max() / np.abs(lin).max() < 1e-5
+
+
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("n", [256, 1024, 4096, 16384])
+def test_exchange_chain_on_one_gpu_matches_plain_chain(backend, qt, n):
+    """The flagged form of the GEMV (x read from {value, generation} pairs, rows written as pairs) with no
+    peers: a chain of square products ends on the same bits as the same chain through plain vectors."""
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    if qt == vb.Q8_0 and n > 8192:
+        pytest.skip("a Q8_0 row of 16384 columns does not fit the streaming kernel's shared-memory ring")
+    links = 5
+    w = synth.normal_matrix(n, n, seed=n + 5) * np.float32(50.0 / np.sqrt(n))
+    blocks = vb.quantize(qt, w)
+    x0 = synth.normal_vectors(1, n, seed=3)[0]
+    xd = backend.init_buffer(x0)
+    full = vb.QuantizedMatrix(backend, qt, blocks, n, n)
+    # plain chain
+    ya = backend.uninit_buffer(n)
+    yb = backend.uninit_buffer(n)
+    src = xd
+    for l in range(links):
+        dst = ya if l % 2 == 0 else yb
+        vb.Gemv().dispatch(backend, None, dst, full, src)
+        src = dst
+    want = np.empty(n, np.float32)
+    backend.slow_read_buffer(src, want)
+    # flagged chain
+    nbytes = lib.vx_xvec_bytes(n)
+    assert nbytes == 256 + 8 * n
+    vecs = [backend.uninit_buffer(nbytes, dtype=np.uint8) for _ in range(2)]
+    for v in vecs:
+        _lib.check(lib.vx_memset(backend._ctx, v.ptr, 0, nbytes))
+    out = backend.uninit_buffer(n)
+    plain = backend.uninit_buffer(n)
+    got = np.empty(n, np.float32)
+    for rep in range(2):                      # twice: generations keep advancing
+        for l in range(links):
+            _lib.check(lib.vx_gemv_q_rows_exchange(
+                backend._ctx, full._h, 0, n, vecs[(l - 1) % 2].ptr if l else None, xd.ptr if l == 0 else None,
+                plain.ptr, vecs[l % 2].ptr, None, 0, 0, 1))
+        _lib.check(lib.vx_xvec_unpack(backend._ctx, vecs[(links - 1) % 2].ptr, n, out.ptr))
+        backend.slow_read_buffer(out, got)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        backend.slow_read_buffer(plain, got)   # the plain copy of the last link's rows
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

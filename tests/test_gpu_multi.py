@@ -72,6 +72,108 @@ def _worker(rank, world, port, out_dir):
     os._exit(0)   # skip NCCL teardown, which has hung on these boxes after all work was done
 
 
+def _chain_worker(rank, world, port, out_dir):
+    """A chain of GEMVs whose exchange is fused into the kernel: link l reads the exchange vector link l - 1
+    wrote on every GPU, pair by pair as the rows arrive.  Run twice from different x0 so that a link that read
+    too early would pick up the first run's values; with contiguous slabs and with rows dealt out in turn."""
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import vortx_b200 as vb
+    from vortx_b200 import synth
+    from vortx_b200.multi_gpu import PeerScatterGemv, shard_blocks
+    be = vb.Backend(rank)
+    n, links = 2048, 6
+    w = synth.normal_matrix(n, n, seed=31) * np.float32(50.0 / 45.0)
+    blocks = vb.quantize(vb.Q4_0, w)
+    results = {}
+    x0 = synth.normal_vectors(2, n, seed=32)
+    xd = be.init_buffer(x0.ravel())
+    for cyclic in (False, True):
+        g = PeerScatterGemv(be, n, n, links, cyclic=cyclic)
+        if cyclic:
+            per_row = n // 32 * 18
+            mine = np.ascontiguousarray(blocks.reshape(n, per_row)[rank::world]).ravel()
+        else:
+            mine = shard_blocks(blocks, n, n, 18, world, rank)
+        qm = vb.QuantizedMatrix(be, vb.Q4_0, mine, g.nrows, n)
+        for run in range(2):
+            # link l reads vector (l - 1) % 2 and writes vector l % 2; every link is also unpacked into
+            # y[l] so that each can be checked on its own
+            for l in range(links):
+                if l == 0:
+                    g.dispatch_chained(qm, 0, x_ptr=xd.ptr + run * n * 4)
+                else:
+                    g.dispatch_chained(qm, l % 2, x_vec=(l - 1) % 2)
+                g.unpack(l % 2, g.y_ptr(l))
+            be.synchronize()
+            y = np.empty(links * n, np.float32)
+            be.slow_read_buffer(g.y.local, y.view(np.uint8))
+            results[f"run{run}_{int(cyclic)}"] = y.reshape(links, n).copy()
+            # the same chain with nothing between the links: only the in-kernel waits order them
+            for rep in range(3):
+                g.dispatch_chained(qm, 0, x_ptr=xd.ptr + run * n * 4)
+                for l in range(1, links):
+                    g.dispatch_chained(qm, l % 2, x_vec=(l - 1) % 2)
+                g.unpack((links - 1) % 2, g.y_ptr(0))
+            be.synchronize()
+            be.slow_read_buffer(g.y.local, y.view(np.uint8))
+            results[f"pure{run}_{int(cyclic)}"] = y[:n].copy()
+            dist.barrier()
+        g.close()
+    np.savez(os.path.join(out_dir, f"chain{rank}.npz"), **results)
+    dist.barrier()
+    be.close()
+    os._exit(0)
+
+
+def _run_ranks(target, world, out_dir):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, out_dir)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    for p in procs:
+        if p.is_alive():
+            p.kill()          # the exact child started above
+            pytest.fail("a rank did not finish in time")
+        assert p.exitcode == 0
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_chained_gemv_with_fused_exchange_on_two_gpus(tmp_path, oracle):
+    import vortx_b200 as vb
+    from vortx_b200 import synth
+    world = 2
+    _run_ranks(_chain_worker, world, str(tmp_path))
+    n, links = 2048, 6
+    w = synth.normal_matrix(n, n, seed=31) * np.float32(50.0 / 45.0)
+    blocks = vb.quantize(vb.Q4_0, w)
+    x0 = synth.normal_vectors(2, n, seed=32)
+    got = [np.load(tmp_path / f"chain{r}.npz") for r in range(world)]
+    for cyclic in (0, 1):
+        for run in range(2):
+            key = f"run{run}_{cyclic}"
+            ys = got[0][key]
+            for r in range(1, world):
+                assert np.array_equal(ys.view(np.uint32), got[r][key].view(np.uint32))   # one y everywhere
+            prev = x0[run]
+            for l in range(links):
+                y64, absdot = oracle.gemv_f64(vb.Q4_0, blocks, n, n, prev[None, :])
+                assert (np.abs(ys[l] - y64[0]) <= 2e-6 * absdot[0]).all(), f"{key} link {l}"
+                prev = ys[l]
+            for r in range(world):   # the kernel is deterministic: the unattended chain ends on the same bits
+                assert np.array_equal(got[r][f"pure{run}_{cyclic}"].view(np.uint32), ys[links - 1].view(np.uint32))
+        assert not np.array_equal(got[0][f"run0_{cyclic}"], got[0][f"run1_{cyclic}"])
+
+
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
 def test_peer_scatter_and_nccl_gemv_on_two_gpus(tmp_path, oracle):
     import torch.multiprocessing as mp

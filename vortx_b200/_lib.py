@@ -106,6 +106,10 @@ SIGNATURES = {
     "vx_ipc_import": (C.c_int32, [_P, _P, C.POINTER(_P)]),
     "vx_ipc_release": (C.c_int32, [_P, _P]),
     "vx_gemv_q_rows_scatter": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t, _P, _P, C.POINTER(_P), C.c_size_t]),
+    "vx_xvec_bytes": (C.c_size_t, [C.c_size_t]),
+    "vx_gemv_q_rows_exchange": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t, _P, _P, _P, _P, C.POINTER(_P),
+                                            C.c_size_t, C.c_size_t, C.c_size_t]),
+    "vx_xvec_unpack": (C.c_int32, [_P, _P, C.c_size_t, _P]),
     "vx_peer_barrier": (C.c_int32, [_P, C.POINTER(_P), C.c_size_t, C.c_size_t]),
     "vx_reduce": (C.c_int32, [_P, C.c_int, C.c_int, C.c_int, _P, C.POINTER(VxShape), C.c_uint64, _P]),
     "vx_reduce_static": (C.c_int32, [C.c_int32, _P, C.c_int, C.c_int, _P, C.POINTER(VxShape), _P]),

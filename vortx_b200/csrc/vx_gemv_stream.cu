@@ -50,6 +50,20 @@ struct StreamParams {
     // needed afterwards.  Plain stores to peer memory; nothing is ever loaded from a peer.
     float* y_peer[vx::kMaxPeers];
     uint32_t n_peer;
+    // Fused exchange (optional).  An exchange vector is a 256-byte header (word 0: how many times
+    // the vector has been written completely, its generation; word 1: thread blocks of the
+    // current launch that have finished) followed by one 8-byte pair {f32 value, u32 generation}
+    // per element.  A value and the generation that says it has arrived travel in ONE 64-bit
+    // store, so neither side needs a fence or a flag: the writer stores pairs tagged
+    // generation + 1 into its own vector and into every peer's, the reader takes the generation
+    // from its own header and re-reads any pair that does not carry it yet.
+    const uint64_t* x_pairs;              // flagged x (p.x is ignored then), or null
+    const uint32_t* x_hdr;
+    uint64_t* y_pairs;                    // this rank's vector, advanced to the slab's first row, or null
+    uint64_t* y_pairs_peer[vx::kMaxPeers];
+    uint32_t n_pair_peer;
+    uint32_t y_pair_stride;               // row r of the slab is element r * stride of y_pairs
+    uint32_t* y_hdr;
     uint32_t tpr;           // threads per row group (multiple of 32)
     uint32_t stages;
     uint32_t stage_bytes;
@@ -88,7 +102,9 @@ __device__ __forceinline__ float transposed_reduce(float (&v)[NR], uint32_t lane
 
 // QT: 0 = Q8_0 (16 weights per 16-byte chunk), 1 = Q4_0 (32 weights per chunk).
 // CPT: chunk positions per thread.  RP: row groups working side by side.  TR: rows per tile.
-template <int QT, int CPT, int RP, int TR>
+// XCH: reads a flagged x and / or writes flagged pairs (the cross-GPU exchange); a template
+// switch so that the plain kernel keeps its register count (two CTAs per SM need <= 102).
+template <int QT, int CPT, int RP, int TR, bool XCH>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_stream_kernel(const StreamParams p) {
     constexpr int W = QT == 1 ? 32 : 16;
@@ -137,6 +153,9 @@ gemv_stream_kernel(const StreamParams p) {
         // y may still be read by the previous kernel in the stream: write it only once that
         // kernel has completed.
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        // Generation this launch writes.  The header only changes when the last block of a grid
+        // retires, and the previous grid has completed.
+        const uint32_t gen = XCH && p.y_pairs ? *(volatile const uint32_t*)p.y_hdr + 1 : 0;
         uint32_t k = 0;
         for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
             const uint32_t b = k % kRedBufs;
@@ -146,11 +165,24 @@ gemv_stream_kernel(const StreamParams p) {
             if (lane < (uint32_t)TR && row < p.nrows) {
                 float sum = 0.0f;
                 for (uint32_t wv = 0; wv < wpr; ++wv) sum += slot[lane * kWarps + wv];
-                p.y[row] = sum;
+                if (p.y) p.y[row] = sum;
                 for (uint32_t d = 0; d < p.n_peer; ++d) p.y_peer[d][row] = sum;
+                if (XCH && p.y_pairs) {
+                    const uint64_t pair = ((uint64_t)gen << 32) | __float_as_uint(sum);
+                    const size_t at = (size_t)row * p.y_pair_stride;
+                    st_relaxed_sys_u64(p.y_pairs + at, pair);
+                    for (uint32_t d = 0; d < p.n_pair_peer; ++d) st_relaxed_sys_u64(p.y_pairs_peer[d] + at, pair);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(red_empty(b));
+        }
+        if (XCH && p.y_pairs && lane == 0) {
+            // The last block to retire publishes the new generation to later kernels of this GPU.
+            if (atomicAdd(p.y_hdr + 1, 1u) == gridDim.x - 1) {
+                *(volatile uint32_t*)p.y_hdr = gen;
+                *(volatile uint32_t*)(p.y_hdr + 1) = 0;
+            }
         }
         return;
     }
@@ -193,6 +225,8 @@ gemv_stream_kernel(const StreamParams p) {
     // warp is already streaming weights, which no kernel writes).
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    const uint32_t x_gen = XCH && p.x_pairs ? *(volatile const uint32_t*)p.x_hdr : 0;
+
     // x -> three byte planes per chunk, kept in registers.
     uint32_t DA[CPT][DR], DB[CPT][DR], DC[CPT][DR];
     float sxs[CPT];
@@ -204,7 +238,29 @@ gemv_stream_kernel(const StreamParams p) {
         const bool valid = active && c < p.nchunks;
         chunk[j] = valid ? c : 0;
         float xv[W];
-        if (valid) {
+        if (XCH && valid && p.x_pairs) {
+            // Flagged x: two pairs per 16-byte load; anything that does not carry this vector's
+            // generation yet is still on its way from a peer and is read again (bounded).
+            const uint64_t* src = p.x_pairs + (size_t)c * W;
+            const long long start = clock64();
+            bool ok = false;
+            while (!ok) {
+                ok = true;
+#pragma unroll
+                for (int i = 0; i < W / 2; ++i) {
+                    uint64_t a, b;
+                    ld_volatile_v2_u64(src + 2 * i, a, b);
+                    ok = ok && (uint32_t)(a >> 32) == x_gen && (uint32_t)(b >> 32) == x_gen;
+                    xv[2 * i] = __uint_as_float((uint32_t)a);
+                    xv[2 * i + 1] = __uint_as_float((uint32_t)b);
+                }
+                if (!ok && (*abort_flag != 0u || clock64() - start > kWaitCycles)) break;
+            }
+            if (!ok) {
+                if (*abort_flag == 0u) report(p.status, 16);
+                *abort_flag = 1u;
+            }
+        } else if (valid) {
             const float* src = p.x + (size_t)c * W;
             if (p.x_vec) {
 #pragma unroll
@@ -325,9 +381,9 @@ gemv_stream_kernel(const StreamParams p) {
     }
 }
 
-template <int QT, int CPT, int RP, int TR>
+template <int QT, int CPT, int RP, int TR, bool XCH>
 vx_status launch_one(vx_context* ctx, const StreamParams& p, dim3 grid, size_t smem) {
-    auto kernel = gemv_stream_kernel<QT, CPT, RP, TR>;
+    auto kernel = gemv_stream_kernel<QT, CPT, RP, TR, XCH>;
     // Raise the dynamic shared-memory limit once per device and kernel instance.
     static size_t granted[64] = {};
     const int dev = ctx->device & 63;
@@ -349,17 +405,24 @@ vx_status launch_one(vx_context* ctx, const StreamParams& p, dim3 grid, size_t s
     return VX_OK;
 }
 
-template <int QT, int TR>
+template <int QT, int TR, bool XCH>
 vx_status launch_qt(vx_context* ctx, int cpt, int rp, const StreamParams& p, dim3 grid, size_t smem) {
     if (cpt == 1) {
         switch (rp) {
-            case 1: return launch_one<QT, 1, 1, TR>(ctx, p, grid, smem);
-            case 2: return launch_one<QT, 1, 2, TR>(ctx, p, grid, smem);
-            default: return launch_one<QT, 1, 4, TR>(ctx, p, grid, smem);
+            case 1: return launch_one<QT, 1, 1, TR, XCH>(ctx, p, grid, smem);
+            case 2: return launch_one<QT, 1, 2, TR, XCH>(ctx, p, grid, smem);
+            default: return launch_one<QT, 1, 4, TR, XCH>(ctx, p, grid, smem);
         }
     }
-    if (cpt == 2) return launch_one<QT, 2, 1, TR>(ctx, p, grid, smem);
-    return launch_one<QT, 4, 1, TR>(ctx, p, grid, smem);
+    if (cpt == 2) return launch_one<QT, 2, 1, TR, XCH>(ctx, p, grid, smem);
+    return launch_one<QT, 4, 1, TR, XCH>(ctx, p, grid, smem);
+}
+
+template <bool XCH>
+vx_status launch_tr(vx_context* ctx, int qtype, uint32_t tr, int cpt, int rp, const StreamParams& p, dim3 grid, size_t smem) {
+    if (tr == 8)
+        return qtype == VX_Q4_0 ? launch_qt<1, 8, XCH>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 8, XCH>(ctx, cpt, rp, p, grid, smem);
+    return qtype == VX_Q4_0 ? launch_qt<1, 4, XCH>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 4, XCH>(ctx, cpt, rp, p, grid, smem);
 }
 
 }  // namespace
@@ -369,7 +432,8 @@ namespace vx {
 // One vector (batch 1).  *eligible = false (nothing launched) when the row is too long for
 // the shared-memory ring or the register-resident x.
 vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
-                             const float* x, float* y, float* const* y_peer, uint32_t n_peer, bool* eligible) {
+                             const float* x, float* y, float* const* y_peer, uint32_t n_peer,
+                             const Exchange* xch, bool* eligible) {
     const uint32_t TR = option(ctx, "gemv.tile_rows", 8) == 4 ? 4 : 8;
     *eligible = false;
     const uint32_t nb = (uint32_t)w->blocks_per_row;
@@ -396,6 +460,7 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
     // prefetch its first tiles while this one is still running.
     int64_t per_sm = option(ctx, "gemv.ctas_per_sm", 0);
     if (per_sm <= 0) per_sm = tiles >= 16u * (uint32_t)ctx->sm_count ? 2 : 1;
+    if (xch && (xch->x_vec || xch->y_vec)) per_sm = 1;  // the flagged kernel's registers allow one CTA per SM
     per_sm = std::min<int64_t>(per_sm, 4);
     const size_t budget = (size_t)(200 * 1024) / (size_t)per_sm - fixed;
     int64_t want_stages = option(ctx, "gemv.stages", 0);
@@ -418,6 +483,22 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
     p.nrows = nrows;
     p.x = x;
     p.y = y;
+    p.x_pairs = xch && xch->x_vec ? reinterpret_cast<const uint64_t*>(static_cast<const uint8_t*>(xch->x_vec) + kExchangeHeader) : nullptr;
+    p.x_hdr = xch ? static_cast<const uint32_t*>(xch->x_vec) : nullptr;
+    p.y_pairs = nullptr;
+    p.y_hdr = nullptr;
+    p.n_pair_peer = 0;
+    p.y_pair_stride = xch ? (uint32_t)xch->y_stride : 1;
+    for (uint32_t d = 0; d < (uint32_t)kMaxPeers; ++d) p.y_pairs_peer[d] = nullptr;
+    if (xch && xch->y_vec) {
+        auto pairs = [&](void* base) {
+            return reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(base) + kExchangeHeader) + xch->y_row0;
+        };
+        p.y_pairs = pairs(xch->y_vec);
+        p.y_hdr = static_cast<uint32_t*>(xch->y_vec);
+        p.n_pair_peer = std::min<uint32_t>(xch->n_peers, kMaxPeers);
+        for (uint32_t d = 0; d < p.n_pair_peer; ++d) p.y_pairs_peer[d] = pairs(xch->peer_y_vec[d]);
+    }
     p.n_peer = std::min<uint32_t>(n_peer, kMaxPeers);
     for (uint32_t d = 0; d < (uint32_t)kMaxPeers; ++d) p.y_peer[d] = d < p.n_peer ? y_peer[d] : nullptr;
     p.tpr = tpr;
@@ -430,11 +511,10 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
     const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * per_sm);
     dim3 grid(std::min(tiles, slots));
     const size_t smem = (size_t)stages * stage_bytes + fixed;
-    vx_status st;
-    if (TR == 8)
-        st = w->type == VX_Q4_0 ? launch_qt<1, 8>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 8>(ctx, cpt, rp, p, grid, smem);
-    else
-        st = w->type == VX_Q4_0 ? launch_qt<1, 4>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 4>(ctx, cpt, rp, p, grid, smem);
+    // The flagged kernel needs more registers than two CTAs per SM leave it.
+    const bool flagged = p.x_pairs || p.y_pairs;
+    const vx_status st = flagged ? launch_tr<true>(ctx, w->type, TR, cpt, rp, p, grid, smem)
+                                 : launch_tr<false>(ctx, w->type, TR, cpt, rp, p, grid, smem);
     if (st != VX_OK) return st;
     ctx->launches++;
     ctx->status_dirty = true;

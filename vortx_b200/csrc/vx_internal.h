@@ -111,7 +111,21 @@ constexpr int kMaxPeers = 7;
 struct PeerFlags {
     uint32_t* flags[kMaxPeers + 1];
 };
+// Fused exchange of the row-sharded GEMV through exchange vectors (256-byte header, then one
+// {f32, generation} pair per element; see StreamParams in vx_gemv_stream.cu).  x_vec: flagged x to
+// read instead of the plain x, or null.  y_vec: this rank's full-length vector that receives the
+// slab at elements y_row0 + r * y_stride, with peer_y_vec[d] the same vector of each peer; or null.
+constexpr size_t kExchangeHeader = 256;
+struct Exchange {
+    const void* x_vec;
+    void* y_vec;
+    void* const* peer_y_vec;
+    uint32_t n_peers;
+    size_t y_row0;
+    size_t y_stride;  // row r of the slab goes to element y_row0 + r * y_stride
+};
 vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
-                             const float* x, float* y, float* const* y_peer, uint32_t n_peer, bool* eligible);
+                             const float* x, float* y, float* const* y_peer, uint32_t n_peer,
+                             const Exchange* xch, bool* eligible);
 
 }  // namespace vx

@@ -584,7 +584,7 @@ vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t row0, siz
         for (; v < batch; ++v) {
             bool eligible = false;
             vx_status st = vx::launch_gemv_stream(ctx, w, row0, (uint32_t)nrows, x + v * x_stride,
-                                                  y + v * y_stride, nullptr, 0, &eligible);
+                                                  y + v * y_stride, nullptr, 0, nullptr, &eligible);
             if (st != VX_OK) return st;
             if (!eligible) break;
         }

@@ -74,46 +74,88 @@ class PeerBuffers:
 
 
 class PeerScatterGemv:
-    """Row-sharded GEMV whose kernel stores each finished row into every peer's y directly (NVLink
-    stores from the epilogue), followed by a one-warp arrival barrier across the GPUs — no collective.
+    """Row-sharded GEMV whose kernel stores each finished row into every peer's memory directly (NVLink
+    stores from the epilogue) — no collective.  Two forms:
 
-    y lives in `PeerBuffers` (f32, `slots` full-length vectors); `dispatch(x_ptr, slot)` computes this rank's
-    rows of y[slot] and returns once the barrier kernel is queued: after it, on this rank's stream, y[slot]
-    is complete on this GPU."""
+    * `dispatch(weights, x_ptr, slot)`: plain f32 rows into y[slot] everywhere, then a one-warp arrival
+      barrier kernel across the GPUs; after it, on this rank's stream, y[slot] is complete on this GPU.
+    * `dispatch_chained(...)`: for chains of dependent GEMVs.  Rows travel as {value, generation} pairs into
+      an exchange vector on every GPU, and the next link reads its x from such a vector, re-reading pairs
+      that have not arrived yet while its weight stream is already running.  Nothing runs between the links:
+      no barrier, no flag, no fence.  `unpack(vec, out_ptr)` ends a chain with plain f32 on this GPU.
 
-    def __init__(self, backend, rows: int, cols: int, slots: int, group=None):
+    `cyclic=True` deals the rows out in turn (rank r owns rows r, r + world, ...; its slab is still one
+    contiguous block stream) instead of contiguous slabs; only the chained form supports it."""
+
+    def __init__(self, backend, rows: int, cols: int, slots: int, group=None, vectors: int = 2, cyclic: bool = False):
+        import ctypes as C
         import torch.distributed as dist
+        from . import _lib
         self.backend, self.rows, self.cols, self.slots = backend, rows, cols, slots
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if self.world > 8:
             raise ValueError("at most 8 GPUs of one node")
-        self.row0, self.nrows = row_shard(rows, self.world, self.rank)
-        self.y = PeerBuffers(backend, slots * rows * 4, group)
+        self.cyclic = cyclic
+        if cyclic:
+            self.row0, self.nrows = self.rank, len(range(self.rank, rows, self.world))
+        else:
+            self.row0, self.nrows = row_shard(rows, self.world, self.rank)
+        self.y = PeerBuffers(backend, max(1, slots) * rows * 4, group)
         self.flags = PeerBuffers(backend, 64 * 4, group)
-        self.epoch = 0
+        self.vectors = [PeerBuffers(backend, _lib.load().vx_xvec_bytes(rows), group) for _ in range(vectors)]
+        self._others = [r for r in range(self.world) if r != self.rank]
+        self._flags_all = (C.c_void_p * self.world)(*self.flags.ptrs)
+        self._vec_peers = [(C.c_void_p * max(1, len(self._others)))(*[v.ptrs[r] for r in self._others])
+                           for v in self.vectors]
         dist.barrier(group=group)
 
     def y_ptr(self, slot: int) -> int:
         return self.y.local.ptr + slot * self.rows * 4
 
+    def _peer_y(self, off: int):
+        import ctypes as C
+        return (C.c_void_p * max(1, len(self._others)))(*[self.y.ptrs[r] + off for r in self._others])
+
     def dispatch(self, weights, x_ptr: int, slot: int) -> None:
         """weights: this rank's QuantizedMatrix slab (nrows x cols)."""
-        import ctypes as C
         from . import _lib
+        if self.cyclic:
+            raise ValueError("the barrier form takes contiguous slabs")
         lib = _lib.load()
         off = (slot * self.rows + self.row0) * 4
-        peers = [self.y.ptrs[r] + off for r in range(self.world) if r != self.rank]
-        arr = (C.c_void_p * max(1, len(peers)))(*peers)
         _lib.check(lib.vx_gemv_q_rows_scatter(self.backend._ctx, weights._h, 0, self.nrows, x_ptr,
-                                              self.y.local.ptr + off, arr, len(peers)))
-        flags = (C.c_void_p * self.world)(*self.flags.ptrs)
-        _lib.check(lib.vx_peer_barrier(self.backend._ctx, flags, self.world, self.rank))
+                                              self.y.local.ptr + off, self._peer_y(off), len(self._others)))
+        self.finish()
+
+    def dispatch_chained(self, weights, y_vec: int, x_vec: Optional[int] = None, x_ptr: int = 0) -> None:
+        """One link: this rank's rows of W x into exchange vector `y_vec` on every GPU.  x is exchange vector
+        `x_vec` (its first `cols` elements, awaited pair by pair) or, for the first link, the plain `x_ptr`.
+        A vector may be written again only after every rank has read it: alternate two."""
+        from . import _lib
+        lib = _lib.load()
+        xv = self.vectors[x_vec].local.ptr if x_vec is not None else None
+        _lib.check(lib.vx_gemv_q_rows_exchange(self.backend._ctx, weights._h, 0, self.nrows, xv, x_ptr or None, None,
+                                               self.vectors[y_vec].local.ptr, self._vec_peers[y_vec],
+                                               len(self._others), self.row0, self.world if self.cyclic else 1))
+
+    def unpack(self, vec: int, out_ptr: int, n: Optional[int] = None) -> None:
+        """Exchange vector -> plain f32 at out_ptr, waiting on the device for the pairs still under way."""
+        from . import _lib
+        _lib.check(_lib.load().vx_xvec_unpack(self.backend._ctx, self.vectors[vec].local.ptr,
+                                              self.rows if n is None else n, out_ptr))
+
+    def finish(self) -> None:
+        """Arrival barrier across the GPUs, stream-ordered: after it every rank's earlier rows have landed."""
+        from . import _lib
+        _lib.check(_lib.load().vx_peer_barrier(self.backend._ctx, self._flags_all, self.world, self.rank))
 
     def close(self) -> None:
         self.backend.synchronize()
         self.y.close()
         self.flags.close()
+        for v in self.vectors:
+            v.close()
 
 
 class ShardedGemv:
