@@ -229,8 +229,21 @@ def run_ours(args):
         if st != 0:
             raise RuntimeError(_lib.last_error())
 
+    # The step's 32 products as ONE persistent launch (a GEMV list): plain and independent at N = 1 and for
+    # the kernel-only figure; chained through the exchange vectors for "peer".
+    plain_batch = vb.GemvBatch(be, [{"w": layers[l], "x": x_dev.data_ptr(), "y": y_full[l].data_ptr() + row0 * 4}
+                                    for l in range(LAYERS)])
+    chain_batch = chain.chain_batch(layers, x_dev.data_ptr()) if n > 1 else None
+
     def step_device(exchange=args.exchange):
+        if n == 1 and exchange != "separate":
+            plain_batch.launch()
+            return
         if n > 1 and exchange == "peer":
+            chain_batch.launch()
+            chain.unpack((LAYERS - 1) % 2, chain.y_ptr(0))
+            return
+        if n > 1 and exchange == "peer-launches":      # the same chain, one launch per GEMV
             chain.dispatch_chained(layers[0], 0, x_ptr=x_dev.data_ptr())
             for l in range(1, LAYERS):
                 chain.dispatch_chained(layers[l], l % 2, x_vec=(l - 1) % 2)
@@ -241,7 +254,7 @@ def run_ours(args):
                 scatter.dispatch(layers[l], x_dev.data_ptr(), l)
             else:
                 gemv(l, x_dev.data_ptr())
-                if n > 1:
+                if n > 1 and exchange == "nccl":
                     dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
 
     note("weights uploaded")
@@ -284,28 +297,33 @@ def run_ours(args):
     value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
 
     note("timed region done")
-    # Kernel-only figure for the roofline: the same launches without the collective (N = 1: the
-    # step itself), timed live with CUDA events on the launching stream.
-    def kernels_only():
-        for l in range(LAYERS):
-            gemv(l, x_dev.data_ptr())
-    kgraph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(kgraph, stream=stream):
-        kernels_only()
-    for _ in range(3):
-        kgraph.replay()
-    torch.cuda.synchronize()
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k0.record(stream)
+    # Kernel-only figure for the roofline: the step's products on this GPU's rows without any exchange
+    # (N = 1: the step itself), timed live with CUDA events on the launching stream.  The dominant kernel is
+    # the list launch: LAYERS products per launch.
+    def time_graph(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record(stream)
+        for _ in range(reps):
+            g.replay()
+        k1.record(stream)
+        torch.cuda.synchronize()
+        return k0.elapsed_time(k1) * 1e3 / reps      # us per replay
+
     reps = max(3, args.steps)
-    for _ in range(reps):
-        kgraph.replay()
-    k1.record(stream)
-    torch.cuda.synchronize()
-    launch_us = k0.elapsed_time(k1) * 1e3 / (reps * LAYERS)
+    launch_us = time_graph(plain_batch.launch, reps)
+    separate_us = time_graph(lambda: [gemv(l, x_dev.data_ptr()) for l in range(LAYERS)], reps) / LAYERS
     shard_bytes = gemv_bytes(shard, COLS)
+    list_bytes = LAYERS * shard_bytes
     peak, peak_kind = measured_peak_hbm()
-    achieved = shard_bytes / (launch_us * 1e-6) / 1e9
+    achieved = list_bytes / (launch_us * 1e-6) / 1e9
 
     note("kernel-only timing done")
     # End to end through the public API with host buffers: per GEMV, x from pinned host memory,
@@ -346,7 +364,7 @@ def run_ours(args):
     extra = {}
     if n > 1:
         # the other ways of exchanging y, timed the same way, for comparison
-        for other in ("peer", "peer-barrier", "nccl"):
+        for other in ("peer", "peer-launches", "peer-barrier", "nccl"):
             if other == args.exchange:
                 continue
             step_device(other)
@@ -367,7 +385,7 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             other_ms = float(t.item()) / args.steps
             extra[f"exchange_{other}"] = {"ms_per_step": other_ms, "GB/s": bytes_per_step / (other_ms * 1e-3) / 1e9}
-        extra["kernels_only"] = {"us_per_launch": launch_us, "GB/s_per_gpu": achieved}
+        extra["kernels_only"] = {"us_per_list_launch": launch_us, "GB/s_per_gpu": achieved}
     cpu = None
     if rank == 0 and n == 1:
         extra = side_configs(be, lib, torch, stream)
@@ -388,15 +406,18 @@ def run_ours(args):
             "config": {"workload": "q4_0_gemv_28672x8192_x32", "rows": ROWS, "cols": COLS, "batch": 1,
                        "gemv_per_step": LAYERS,
                        "sharding": (f"rows/{n} per GPU; y exchanged by " + EXCHANGE_TEXT[args.exchange]) if n > 1 else "none",
-                       "l2": "inputs larger than L2: 32 weight copies walked in turn", "launch": "CUDA graph replay"},
+                       "l2": "inputs larger than L2: 32 weight copies walked in turn",
+                       "launch": "CUDA graph replay; the 32 products of a step are one persistent list launch"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": LAYERS * COLS * 4, "d2h_bytes_per_step": LAYERS * ROWS * 4},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": "gemv_stream_kernel",
-                         "bytes_per_launch": shard_bytes, "us_per_launch": launch_us,
-                         "traffic": 135_400_000 if n == 1 else None,
-                         "traffic_source": "ncu dram__bytes_read + write of one launch of this shape, profiles/gemv_stream_q4_0_28672x8192.md"},
+                         "bytes_per_launch": list_bytes, "us_per_launch": launch_us, "gemvs_per_launch": LAYERS,
+                         "one_gemv_per_launch": {"us_per_launch": separate_us, "bytes_per_launch": shard_bytes,
+                                                 "achieved": shard_bytes / (separate_us * 1e-6) / 1e9},
+                         "traffic": LAYERS * 135_400_000 if n == 1 else None,
+                         "traffic_source": "ncu dram__bytes_read + write of one 28672 x 8192 product (135.4 MB, profiles/gemv_stream_q4_0_28672x8192.md) x the 32 products of the list launch"},
             "clocks": clocks,
             "extra": extra,
         }
@@ -481,6 +502,7 @@ PROFILE_CASES = {
     # name: (kind, rows/dim, cols, qtype name, weight copies)
     "gemv_q4_0_28672x8192": ("gemv", 28672, 8192, "Q4_0", 2),
     "gemv_q4_0_8192x8192": ("gemv", 8192, 8192, "Q4_0", 4),
+    "gemv_list_q4_0_28672x8192_x8": ("gemv_list", 28672, 8192, "Q4_0", 8),   # one list launch over 8 weight copies
     "gemv_q8_0_4096x4096": ("gemv", 4096, 4096, "Q8_0", 8),
     "gemm_simt_exact_1024": ("gemm", 1024, 1024, "SIMT", 0),
     "gemm_tf32_4096": ("gemm", 4096, 4096, "TF32", 0),
@@ -498,7 +520,7 @@ def run_profile_case(name: str):
     be = vb.Backend(0)
     lib = _lib.load()
     rng = np.random.Generator(np.random.Philox(1))
-    if kind == "gemv":
+    if kind in ("gemv", "gemv_list"):
         qt = vb.Q4_0 if what == "Q4_0" else vb.Q8_0
         bb = lib.vx_qblock_bytes(qt)
         nblocks = rows * cols // 32
@@ -510,9 +532,14 @@ def run_profile_case(name: str):
         ws = [vb.QuantizedMatrix(be, qt, blocks.ravel(), rows, cols) for _ in range(copies)]
         x = be.init_buffer(rng.standard_normal(cols, dtype=np.float32))
         y = be.uninit_buffer(rows)
-        for _ in range(3):
-            for w in ws:
-                vb.Gemv().dispatch(be, None, y, w, x)
+        if kind == "gemv_list":
+            batch = vb.GemvBatch(be, [{"w": w, "x": x.ptr, "y": y.ptr} for w in ws])
+            for _ in range(3):
+                batch.launch()
+        else:
+            for _ in range(3):
+                for w in ws:
+                    vb.Gemv().dispatch(be, None, y, w, x)
     else:
         mode = _lib.VX_GEMM_SIMT_EXACT if what == "SIMT" else _lib.VX_GEMM_TF32
         a = be.init_buffer(rng.random(rows * cols, dtype=np.float32) * 2 - 1)
@@ -553,8 +580,10 @@ def emit(line: dict) -> None:
 
 
 EXCHANGE_TEXT = {
-    "peer": "chain of dependent GEMVs: rows stored as {value, generation} pairs into every GPU's exchange vector from "
-            "the kernel epilogue, awaited pair by pair in the next GEMV's prologue; nothing between the GEMVs",
+    "peer": "chain of dependent GEMVs in one persistent launch per GPU: rows stored as {value, generation} pairs into "
+            "every GPU's exchange vector from the kernel epilogue, awaited pair by pair where the next GEMV reads its x",
+    "peer-launches": "the same chain with one launch per GEMV",
+    "separate": "N = 1 only: one launch per GEMV instead of the list launch",
     "peer-barrier": "peer stores from the kernel epilogue + a barrier kernel after every GEMV",
     "nccl": "NCCL all-gather after every GEMV",
 }

@@ -188,6 +188,38 @@ VX_API vx_status vx_gemv_q_rows_exchange(vx_context* ctx, const vx_qweights* w, 
                                          void* const* peer_y_xvec, size_t n_peers, size_t y_row0,
                                          size_t y_stride);
 VX_API vx_status vx_xvec_unpack(vx_context* ctx, const void* xvec, size_t n, float* out);
+
+/* ------------------------------------------------ a list of GEMVs in one launch ---- */
+/* No reference counterpart.  A decode step is a fixed list of matrix-vector products; launched one
+ * by one, each pays its own launch, prologue and tail (about 4 us on B200, a fifth of a
+ * 28672 x 8192 Q4_0 product).  A vx_gemv_batch runs the list in ONE persistent launch with one
+ * continuous weight stream.  All entries share the quantisation type and the column count; the
+ * fields of an entry mean what the arguments of vx_gemv_q_rows_exchange mean (x_xvec / y_xvec /
+ * peers optional; with y_xvec null the entry is a plain product into y).
+ * Entries run in order on every thread block but blocks are not synchronised with each other, so
+ * an entry may only depend on an earlier one through an exchange vector: the earlier entry writes
+ * it (y_xvec), the later one reads it (x_xvec) and waits pair by pair — on one GPU or across
+ * GPUs alike.  A plain y of the list must not be the plain x of a later entry.  A vector may be
+ * written again by a later entry only after every reader of its previous contents has read it;
+ * a chain that alternates between two vectors satisfies this.
+ * The list is uploaded once at creation (pointers are captured, not the data they point to) and
+ * can be launched any number of times, also inside a CUDA graph. */
+typedef struct vx_gemv_batch vx_gemv_batch;
+typedef struct {
+    const vx_qweights* w;
+    size_t row0, nrows;         /* nrows >= 1                                       */
+    const void* x_xvec;         /* flagged x, or NULL to read the plain x           */
+    const float* x;
+    float* y;                   /* plain rows, or NULL                              */
+    void* y_xvec;               /* this rank's exchange vector, or NULL             */
+    void* const* peer_y_xvec;   /* the same vector of every peer (n_peers entries)  */
+    size_t n_peers;
+    size_t y_row0, y_stride;    /* row r goes to element y_row0 + r * y_stride      */
+} vx_gemv_op;
+VX_API vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_ops,
+                                      vx_gemv_batch** out);
+VX_API vx_status vx_gemv_batch_launch(vx_context* ctx, const vx_gemv_batch* batch);
+VX_API vx_status vx_gemv_batch_free(vx_context* ctx, vx_gemv_batch* batch);
 /* flags[r] (r < world <= 8) is rank r's sync block of 64 u32, zero-initialised: its own for
  * r == rank, a mapped peer pointer otherwise.  Stream-ordered: after all earlier work of this
  * context it announces this rank's next barrier number to every rank, then waits, on the device

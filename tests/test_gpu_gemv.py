@@ -165,3 +165,73 @@ def test_exchange_chain_on_one_gpu_matches_plain_chain(backend, qt, n):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
         backend.slow_read_buffer(plain, got)   # the plain copy of the last link's rows
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("rows,cols,count", [(8, 64, 3), (100, 1056, 5), (1300, 2048, 7), (7000, 4096, 4),
+                                             (3000, 8192, 6), (64, 16384, 3)])
+def test_batch_of_independent_gemvs_matches_single_launches(backend, qt, rows, cols, count):
+    """One persistent launch over a list of products (different weights, row counts and x) gives the bits the
+    products give when launched one by one."""
+    if qt == vb.Q8_0 and cols > 8192:
+        pytest.skip("a Q8_0 row of 16384 columns does not fit the streaming kernel's shared-memory ring")
+    ws, entries, singles = [], [], []
+    xs = synth.normal_vectors(2, cols, seed=cols)
+    xd = backend.init_buffer(xs.ravel())
+    for i in range(count):
+        r = max(1, rows - 37 * i)             # ragged row counts: the tile rotation differs per entry
+        w = vb.QuantizedMatrix.from_f32(backend, qt, synth.normal_matrix(r, cols, seed=100 * i + rows))
+        ws.append(w)
+        xp = xd.ptr + ((i // 2) % 2) * cols * 4   # two x in turn: every other entry shares it with its predecessor
+        ya = backend.init_buffer(np.full(r, np.nan, np.float32))
+        yb = backend.init_buffer(np.full(r, np.nan, np.float32))
+        entries.append({"w": w, "x": xp, "y": ya.ptr})
+        singles.append((w, xp, ya, yb, r))
+    batch = vb.GemvBatch(backend, entries)
+    for rep in range(2):
+        batch.launch()
+    for w, xp, ya, yb, r in singles:
+        vb.Gemv().dispatch(backend, None, yb, w, xp)
+        a, b = np.empty(r, np.float32), np.empty(r, np.float32)
+        backend.slow_read_buffer(ya, a)
+        backend.slow_read_buffer(yb, b)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    batch.free()
+
+
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("n", [256, 2048, 8192])
+def test_batch_chain_through_exchange_vectors_on_one_gpu(backend, qt, n):
+    """A chain of dependent products in ONE launch: each entry reads the exchange vector its predecessor
+    writes, pair by pair as other thread blocks of the same grid deliver them.  Same bits as the plain chain."""
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    links = 6
+    w = synth.normal_matrix(n, n, seed=n + 9) * np.float32(50.0 / np.sqrt(n))
+    full = vb.QuantizedMatrix.from_f32(backend, qt, w)
+    x0 = synth.normal_vectors(1, n, seed=4)[0]
+    xd = backend.init_buffer(x0)
+    ya, yb = backend.uninit_buffer(n), backend.uninit_buffer(n)
+    src = xd
+    for l in range(links):
+        dst = ya if l % 2 == 0 else yb
+        vb.Gemv().dispatch(backend, None, dst, full, src)
+        src = dst
+    want = np.empty(n, np.float32)
+    backend.slow_read_buffer(src, want)
+    nbytes = lib.vx_xvec_bytes(n)
+    vecs = [backend.uninit_buffer(nbytes, dtype=np.uint8) for _ in range(2)]
+    for v in vecs:
+        _lib.check(lib.vx_memset(backend._ctx, v.ptr, 0, nbytes))
+    entries = [{"w": full, "x": xd.ptr, "y_xvec": vecs[0].ptr}]
+    for l in range(1, links):
+        entries.append({"w": full, "x_xvec": vecs[(l - 1) % 2].ptr, "y_xvec": vecs[l % 2].ptr})
+    batch = vb.GemvBatch(backend, entries)
+    out = backend.uninit_buffer(n)
+    got = np.empty(n, np.float32)
+    for rep in range(3):                       # generations advance by three per vector and launch
+        batch.launch()
+        _lib.check(lib.vx_xvec_unpack(backend._ctx, vecs[(links - 1) % 2].ptr, n, out.ptr))
+        backend.slow_read_buffer(out, got)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    batch.free()

@@ -123,6 +123,15 @@ def _chain_worker(rank, world, port, out_dir):
             be.synchronize()
             be.slow_read_buffer(g.y.local, y.view(np.uint8))
             results[f"pure{run}_{int(cyclic)}"] = y[:n].copy()
+            # and as one persistent launch per GPU
+            batch = g.chain_batch([qm] * links, xd.ptr + run * n * 4)
+            for rep in range(3):
+                batch.launch()
+                g.unpack((links - 1) % 2, g.y_ptr(1))
+            be.synchronize()
+            be.slow_read_buffer(g.y.local, y.view(np.uint8))
+            results[f"batch{run}_{int(cyclic)}"] = y[n:2 * n].copy()
+            batch.free()
             dist.barrier()
         g.close()
     np.savez(os.path.join(out_dir, f"chain{rank}.npz"), **results)
@@ -171,6 +180,7 @@ def test_chained_gemv_with_fused_exchange_on_two_gpus(tmp_path, oracle):
                 prev = ys[l]
             for r in range(world):   # the kernel is deterministic: the unattended chain ends on the same bits
                 assert np.array_equal(got[r][f"pure{run}_{cyclic}"].view(np.uint32), ys[links - 1].view(np.uint32))
+                assert np.array_equal(got[r][f"batch{run}_{cyclic}"].view(np.uint32), ys[links - 1].view(np.uint32))
         assert not np.array_equal(got[0][f"run0_{cyclic}"], got[0][f"run1_{cyclic}"])
 
 

@@ -47,6 +47,14 @@ class VxLayout(C.Structure):
                 ("rank", C.c_uint32), ("offset", C.c_uint32)]
 
 
+class VxGemvOp(C.Structure):
+    """vx_gemv_op: one entry of a GEMV list."""
+
+    _fields_ = [("w", C.c_void_p), ("row0", C.c_size_t), ("nrows", C.c_size_t), ("x_xvec", C.c_void_p),
+                ("x", C.c_void_p), ("y", C.c_void_p), ("y_xvec", C.c_void_p), ("peer_y_xvec", C.POINTER(C.c_void_p)),
+                ("n_peers", C.c_size_t), ("y_row0", C.c_size_t), ("y_stride", C.c_size_t)]
+
+
 class VortxError(RuntimeError):
     """A non-zero vx_status; `.status` holds the code."""
 
@@ -110,6 +118,9 @@ SIGNATURES = {
     "vx_gemv_q_rows_exchange": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t, _P, _P, _P, _P, C.POINTER(_P),
                                             C.c_size_t, C.c_size_t, C.c_size_t]),
     "vx_xvec_unpack": (C.c_int32, [_P, _P, C.c_size_t, _P]),
+    "vx_gemv_batch_create": (C.c_int32, [_P, _P, C.c_size_t, C.POINTER(_P)]),
+    "vx_gemv_batch_launch": (C.c_int32, [_P, _P]),
+    "vx_gemv_batch_free": (C.c_int32, [_P, _P]),
     "vx_peer_barrier": (C.c_int32, [_P, C.POINTER(_P), C.c_size_t, C.c_size_t]),
     "vx_reduce": (C.c_int32, [_P, C.c_int, C.c_int, C.c_int, _P, C.POINTER(VxShape), C.c_uint64, _P]),
     "vx_reduce_static": (C.c_int32, [C.c_int32, _P, C.c_int, C.c_int, _P, C.POINTER(VxShape), _P]),

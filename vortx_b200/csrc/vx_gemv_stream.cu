@@ -19,10 +19,17 @@
 //     reduction (values halve as lanes pair up); each warp then drops its partials into a small
 //     shared-memory buffer and signals an mbarrier.  A tenth warp adds the warps' partials and
 //     writes y, so the consumer warps never meet at a CTA barrier.
+//   * One launch runs a LIST of GEMVs of one row shape (a batch): the three roles walk the
+//     list with one continuous ring, so the weight stream of the next product is already in
+//     flight while the last rows of the current one are reduced, and prologue, tail and launch
+//     latency are paid once per list, not once per product.  Products of a list that depend on
+//     each other exchange their vectors as flagged pairs (below), which needs no grid barrier.
 // No scratch memory in global memory, no split along K, every weight byte read once.
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <memory>
+#include <vector>
 
 #include "vx_internal.h"
 #include "vx_sm100.cuh"
@@ -36,15 +43,17 @@ constexpr int kThreads = kConsumers + 64;  // + producer warp + epilogue warp
 constexpr int kWarps = kConsumers / 32;
 constexpr int kRedBufs = 4;                // partial-sum buffers between consumers and the epilogue warp
 
-struct StreamParams {
+constexpr int kMaxVecs = 8;
+
+// One GEMV of the list.
+struct OpParams {
     const uint8_t* quants;
     const uint8_t* scales;  // f16 plane, addressed in bytes
-    uint32_t nchunks;       // 16-byte chunks per row
-    uint32_t nb;            // blocks per row
     uint64_t row0;
     uint32_t nrows;
+    uint32_t x_aligned;     // x is 16-byte aligned
     const float* x;
-    float* y;
+    float* y;               // plain f32 rows, or null
     // Row-sharded use: besides y, every finished row is stored into these buffers (the same slab
     // of the full-length y on each peer GPU, mapped into this process), so that no collective is
     // needed afterwards.  Plain stores to peer memory; nothing is ever loaded from a peer.
@@ -54,22 +63,36 @@ struct StreamParams {
     // the vector has been written completely, its generation; word 1: thread blocks of the
     // current launch that have finished) followed by one 8-byte pair {f32 value, u32 generation}
     // per element.  A value and the generation that says it has arrived travel in ONE 64-bit
-    // store, so neither side needs a fence or a flag: the writer stores pairs tagged
-    // generation + 1 into its own vector and into every peer's, the reader takes the generation
-    // from its own header and re-reads any pair that does not carry it yet.
-    const uint64_t* x_pairs;              // flagged x (p.x is ignored then), or null
-    const uint32_t* x_hdr;
-    uint64_t* y_pairs;                    // this rank's vector, advanced to the slab's first row, or null
+    // store, so neither side needs a fence or a flag: the writer stores pairs tagged with the
+    // next generation into its own vector and into every peer's, the reader knows which
+    // generation to expect from its own header and re-reads any pair that does not carry it yet.
+    // Headers only change when the last block of a launch retires; within a launch the expected
+    // generation is the header's value plus the number of earlier writes of the list.
+    int32_t x_vec;                        // index into StreamParams::vec_hdr, or -1: plain x
+    uint32_t x_gen_add;
+    int32_t y_vec;                        // or -1: no flagged output
+    uint32_t y_gen_add;
+    const uint64_t* x_pairs;
+    uint64_t* y_pairs;                    // this rank's vector, advanced to the slab's first element
     uint64_t* y_pairs_peer[vx::kMaxPeers];
     uint32_t n_pair_peer;
     uint32_t y_pair_stride;               // row r of the slab is element r * stride of y_pairs
-    uint32_t* y_hdr;
-    uint32_t tpr;           // threads per row group (multiple of 32)
+};
+
+struct StreamParams {
+    uint32_t nchunks;        // 16-byte chunks per row
+    uint32_t nb;             // blocks per row
+    uint32_t tpr;            // threads per row group (multiple of 32)
     uint32_t stages;
     uint32_t stage_bytes;
     uint32_t q_stage_bytes;  // TR * row bytes: where the scales start inside a stage
-    uint32_t x_vec;          // x is 16-byte aligned
+    uint32_t n_ops;          // 1: op0; more: ops[] in device memory
+    uint32_t n_vec;
+    const OpParams* ops;
+    uint32_t* vec_hdr[kMaxVecs];   // headers of the exchange vectors the list touches (own memory)
+    uint32_t vec_writes[kMaxVecs]; // how often the list writes each of them
     vx::DeviceStatus* status;
+    OpParams op0;
 };
 
 __device__ __forceinline__ void report(vx::DeviceStatus* st, uint32_t code) {
@@ -100,13 +123,21 @@ __device__ __forceinline__ float transposed_reduce(float (&v)[NR], uint32_t lane
     return r;
 }
 
+// First tile of GEMV `op` that this block takes; it then strides by the grid.  When the tiles do
+// not divide evenly, the blocks that take one more rotate from one GEMV of the list to the next.
+__device__ __forceinline__ uint32_t first_tile(uint32_t op, uint32_t tiles) {
+    const uint32_t rot = (uint32_t)(((uint64_t)op * (tiles % gridDim.x)) % gridDim.x);
+    const uint32_t t = blockIdx.x + gridDim.x - rot;
+    return t >= gridDim.x ? t - gridDim.x : t;
+}
+
 // QT: 0 = Q8_0 (16 weights per 16-byte chunk), 1 = Q4_0 (32 weights per chunk).
 // CPT: chunk positions per thread.  RP: row groups working side by side.  TR: rows per tile.
 // XCH: reads a flagged x and / or writes flagged pairs (the cross-GPU exchange); a template
 // switch so that the plain kernel keeps its register count (two CTAs per SM need <= 102).
 template <int QT, int CPT, int RP, int TR, bool XCH>
 __global__ void __launch_bounds__(kThreads, 1)
-gemv_stream_kernel(const StreamParams p) {
+gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int W = QT == 1 ? 32 : 16;
     constexpr int DR = W / 4;   // registers per digit plane per chunk
     constexpr int NR = TR / RP; // rows per thread per tile
@@ -142,9 +173,8 @@ gemv_stream_kernel(const StreamParams p) {
     }
     __syncthreads();
 
-    const uint32_t tiles = (p.nrows + TR - 1) / TR;
+    const OpParams* const ops = p.n_ops > 1 ? p.ops : &p.op0;
     const uint32_t row_bytes = p.nchunks * 16;
-
     const uint32_t wpr = p.tpr >> 5;  // warps per row group
 
     if (tid >= kConsumers + 32) {
@@ -153,35 +183,47 @@ gemv_stream_kernel(const StreamParams p) {
         // y may still be read by the previous kernel in the stream: write it only once that
         // kernel has completed.
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        // Generation this launch writes.  The header only changes when the last block of a grid
-        // retires, and the previous grid has completed.
-        const uint32_t gen = XCH && p.y_pairs ? *(volatile const uint32_t*)p.y_hdr + 1 : 0;
         uint32_t k = 0;
-        for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
-            const uint32_t b = k % kRedBufs;
-            if (!mbar_wait(red_full(b), (k / kRedBufs) & 1, abort_flag)) report(p.status, 14);
-            const float* slot = red + (size_t)b * TR * kWarps;
-            const uint32_t row = t * TR + lane;
-            if (lane < (uint32_t)TR && row < p.nrows) {
-                float sum = 0.0f;
-                for (uint32_t wv = 0; wv < wpr; ++wv) sum += slot[lane * kWarps + wv];
-                if (p.y) p.y[row] = sum;
-                for (uint32_t d = 0; d < p.n_peer; ++d) p.y_peer[d][row] = sum;
-                if (XCH && p.y_pairs) {
-                    const uint64_t pair = ((uint64_t)gen << 32) | __float_as_uint(sum);
-                    const size_t at = (size_t)row * p.y_pair_stride;
-                    st_relaxed_sys_u64(p.y_pairs + at, pair);
-                    for (uint32_t d = 0; d < p.n_pair_peer; ++d) st_relaxed_sys_u64(p.y_pairs_peer[d] + at, pair);
+        for (uint32_t o = 0; o < p.n_ops; ++o) {
+            const OpParams& op = ops[o];
+            const uint32_t nrows = op.nrows;
+            const uint32_t tiles = (nrows + TR - 1) / TR;
+            uint32_t t = first_tile(o, tiles);
+            if (t >= tiles) continue;
+            float* const y = op.y;
+            const uint32_t n_peer = op.n_peer;
+            uint64_t* const y_pairs = XCH ? op.y_pairs : nullptr;
+            const uint32_t n_pair_peer = XCH ? op.n_pair_peer : 0;
+            const uint32_t stride = XCH ? op.y_pair_stride : 1;
+            // Generation this GEMV writes.
+            const uint32_t gen = XCH && y_pairs ? *(volatile const uint32_t*)p.vec_hdr[op.y_vec] + op.y_gen_add : 0;
+            for (; t < tiles; t += gridDim.x, ++k) {
+                const uint32_t b = k % kRedBufs;
+                if (!mbar_wait(red_full(b), (k / kRedBufs) & 1, abort_flag)) report(p.status, 14);
+                const float* slot = red + (size_t)b * TR * kWarps;
+                const uint32_t row = t * TR + lane;
+                if (lane < (uint32_t)TR && row < nrows) {
+                    float sum = 0.0f;
+                    for (uint32_t wv = 0; wv < wpr; ++wv) sum += slot[lane * kWarps + wv];
+                    if (y) y[row] = sum;
+                    for (uint32_t d = 0; d < n_peer; ++d) op.y_peer[d][row] = sum;
+                    if (XCH && y_pairs) {
+                        const uint64_t pair = ((uint64_t)gen << 32) | __float_as_uint(sum);
+                        const size_t at = (size_t)row * stride;
+                        st_relaxed_sys_u64(y_pairs + at, pair);
+                        for (uint32_t d = 0; d < n_pair_peer; ++d) st_relaxed_sys_u64(op.y_pairs_peer[d] + at, pair);
+                    }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(red_empty(b));
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(red_empty(b));
         }
-        if (XCH && p.y_pairs && lane == 0) {
-            // The last block to retire publishes the new generation to later kernels of this GPU.
-            if (atomicAdd(p.y_hdr + 1, 1u) == gridDim.x - 1) {
-                *(volatile uint32_t*)p.y_hdr = gen;
-                *(volatile uint32_t*)(p.y_hdr + 1) = 0;
+        if (XCH && p.n_vec > 0 && lane == 0) {
+            // The last block to retire publishes the new generations to later kernels of this GPU.
+            if (atomicAdd(p.vec_hdr[0] + 1, 1u) == gridDim.x - 1) {
+                for (uint32_t v = 0; v < p.n_vec; ++v)
+                    *(volatile uint32_t*)p.vec_hdr[v] = *(volatile uint32_t*)p.vec_hdr[v] + p.vec_writes[v];
+                *(volatile uint32_t*)(p.vec_hdr[0] + 1) = 0;
             }
         }
         return;
@@ -191,19 +233,27 @@ gemv_stream_kernel(const StreamParams p) {
         if (tid == kConsumers) {
             const uint64_t policy = policy_evict_first();
             uint32_t k = 0;
-            for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
-                const uint32_t s = k % p.stages, use = k / p.stages;
-                if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1, abort_flag)) report(p.status, 11);
-                const uint32_t tr = min((uint32_t)TR, p.nrows - t * TR);
-                const uint64_t first = p.row0 + (uint64_t)t * TR;
-                const uint32_t qbytes = tr * row_bytes;
-                const uint64_t soff = first * p.nb * 2;
-                const uint64_t salign = soff & ~(uint64_t)15;
-                const uint32_t sbytes = (uint32_t)(((soff - salign) + (uint64_t)tr * p.nb * 2 + 15) & ~(uint64_t)15);
-                const uint32_t dst = smem_addr(smem + (size_t)s * p.stage_bytes);
-                mbar_arrive_expect_tx(full(s), qbytes + sbytes);
-                bulk_g2s_hint(dst, p.quants + first * row_bytes, qbytes, full(s), policy);
-                bulk_g2s_hint(dst + p.q_stage_bytes, p.scales + salign, sbytes, full(s), policy);
+            for (uint32_t o = 0; o < p.n_ops; ++o) {
+                const OpParams& op = ops[o];
+                const uint32_t nrows = op.nrows;
+                const uint32_t tiles = (nrows + TR - 1) / TR;
+                const uint8_t* const quants = op.quants;
+                const uint8_t* const scales = op.scales;
+                const uint64_t row0 = op.row0;
+                for (uint32_t t = first_tile(o, tiles); t < tiles; t += gridDim.x, ++k) {
+                    const uint32_t s = k % p.stages, use = k / p.stages;
+                    if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1, abort_flag)) report(p.status, 11);
+                    const uint32_t tr = min((uint32_t)TR, nrows - t * TR);
+                    const uint64_t first = row0 + (uint64_t)t * TR;
+                    const uint32_t qbytes = tr * row_bytes;
+                    const uint64_t soff = first * p.nb * 2;
+                    const uint64_t salign = soff & ~(uint64_t)15;
+                    const uint32_t sbytes = (uint32_t)(((soff - salign) + (uint64_t)tr * p.nb * 2 + 15) & ~(uint64_t)15);
+                    const uint32_t dst = smem_addr(smem + (size_t)s * p.stage_bytes);
+                    mbar_arrive_expect_tx(full(s), qbytes + sbytes);
+                    bulk_g2s_hint(dst, quants + first * row_bytes, qbytes, full(s), policy);
+                    bulk_g2s_hint(dst + p.q_stage_bytes, scales + salign, sbytes, full(s), policy);
+                }
             }
             // Do not leave while copies into this CTA's shared memory are still in flight:
             // wait until the consumers have released the last use of every stage.
@@ -225,159 +275,174 @@ gemv_stream_kernel(const StreamParams p) {
     // warp is already streaming weights, which no kernel writes).
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const uint32_t x_gen = XCH && p.x_pairs ? *(volatile const uint32_t*)p.x_hdr : 0;
-
-    // x -> three byte planes per chunk, kept in registers.
+    // x -> three byte planes per chunk, kept in registers for one GEMV of the list.
     uint32_t DA[CPT][DR], DB[CPT][DR], DC[CPT][DR];
     float sxs[CPT];
     int initA[CPT], initB[CPT], initC[CPT];
-    uint32_t chunk[CPT];
-#pragma unroll
-    for (int j = 0; j < CPT; ++j) {
-        const uint32_t c = tc + j * p.tpr;
-        const bool valid = active && c < p.nchunks;
-        chunk[j] = valid ? c : 0;
-        float xv[W];
-        if (XCH && valid && p.x_pairs) {
-            // Flagged x: two pairs per 16-byte load; anything that does not carry this vector's
-            // generation yet is still on its way from a peer and is read again (bounded).
-            const uint64_t* src = p.x_pairs + (size_t)c * W;
-            const long long start = clock64();
-            bool ok = false;
-            while (!ok) {
-                ok = true;
-#pragma unroll
-                for (int i = 0; i < W / 2; ++i) {
-                    uint64_t a, b;
-                    ld_volatile_v2_u64(src + 2 * i, a, b);
-                    ok = ok && (uint32_t)(a >> 32) == x_gen && (uint32_t)(b >> 32) == x_gen;
-                    xv[2 * i] = __uint_as_float((uint32_t)a);
-                    xv[2 * i + 1] = __uint_as_float((uint32_t)b);
-                }
-                if (!ok && (*abort_flag != 0u || clock64() - start > kWaitCycles)) break;
-            }
-            if (!ok) {
-                if (*abort_flag == 0u) report(p.status, 16);
-                *abort_flag = 1u;
-            }
-        } else if (valid) {
-            const float* src = p.x + (size_t)c * W;
-            if (p.x_vec) {
-#pragma unroll
-                for (int i = 0; i < W / 4; ++i) {
-                    const float4 v = __ldg(reinterpret_cast<const float4*>(src) + i);
-                    xv[4 * i + 0] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < W; ++i) xv[i] = __ldg(src + i);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < W; ++i) xv[i] = 0.0f;
-        }
-        float amax = 0.0f;
-#pragma unroll
-        for (int i = 0; i < W; ++i) amax = fmaxf(amax, fabsf(xv[i]));
-        // |x * inv| <= 8388606.5 before rounding, so X stays within 24 signed bits without a clamp.
-        const float inv = amax > 0.0f ? 8388606.0f / amax : 0.0f;
-        sxs[j] = valid ? amax / 8388606.0f : 0.0f;
-        int sa = 0, sb = 0, sc = 0;
-#pragma unroll
-        for (int r = 0; r < DR; ++r) {
-            const uint32_t X0 = (uint32_t)__float2int_rn(xv[4 * r + 0] * inv);
-            const uint32_t X1 = (uint32_t)__float2int_rn(xv[4 * r + 1] * inv);
-            const uint32_t X2 = (uint32_t)__float2int_rn(xv[4 * r + 2] * inv);
-            const uint32_t X3 = (uint32_t)__float2int_rn(xv[4 * r + 3] * inv);
-            // byte n of each X gathered into one register: n = 2 signed high, 1 middle, 0 low
-            DA[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0062), __byte_perm(X2, X3, 0x0062), 0x5410);
-            DB[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0051), __byte_perm(X2, X3, 0x0051), 0x5410);
-            DC[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0040), __byte_perm(X2, X3, 0x0040), 0x5410);
-            sa = dp4a_ss(0x01010101u, DA[j][r], sa);
-            sb = dp4a_su(0x01010101u, DB[j][r], sb);
-            sc = dp4a_su(0x01010101u, DC[j][r], sc);
-        }
-        initA[j] = QT == 1 ? -8 * sa : 0;
-        initB[j] = QT == 1 ? -8 * sb : 0;
-        initC[j] = QT == 1 ? -8 * sc : 0;
-    }
+    const float* held_x = nullptr;  // plain x the registers hold; GEMVs of a list often share it
 
     uint32_t k = 0;
-    for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
-        const uint32_t s = k % p.stages;
-        if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 13);
-        const uint8_t* sq = smem + (size_t)s * p.stage_bytes;
-        const uint64_t soff = (p.row0 + (uint64_t)t * TR) * p.nb * 2;
-        const uint8_t* ss = sq + p.q_stage_bytes + (uint32_t)(soff & 15);
-
-        float acc[NR];
-#pragma unroll
-        for (int i = 0; i < NR; ++i) acc[i] = 0.0f;
-
-        if (active) {
+    for (uint32_t o = 0; o < p.n_ops; ++o) {
+        const OpParams& op = ops[o];
+        const uint32_t tiles = (op.nrows + TR - 1) / TR;
+        uint32_t t = first_tile(o, tiles);
+        if (t >= tiles) continue;
+        const uint64_t* const x_pairs = XCH && op.x_vec >= 0 ? op.x_pairs : nullptr;
+        const float* const x = op.x;
+        if (x_pairs || x != held_x) {
+            held_x = x_pairs ? nullptr : x;
+            const uint32_t x_gen = x_pairs ? *(volatile const uint32_t*)p.vec_hdr[op.x_vec] + op.x_gen_add : 0;
+            const uint32_t x_aligned = op.x_aligned;
 #pragma unroll
             for (int j = 0; j < CPT; ++j) {
-                const uint32_t c = chunk[j];
-                const uint32_t blk = QT == 1 ? c : (c >> 1);
-                // All shared-memory reads of the tile first, so that the integer chains of the
-                // NR rows can overlap.
-                uint4 q[NR];
-                uint16_t dh[NR];
+                const uint32_t c = tc + j * p.tpr;
+                const bool valid = active && c < p.nchunks;
+                float xv[W];
+                if (XCH && valid && x_pairs) {
+                    // Flagged x: two pairs per 16-byte load; anything that does not carry this vector's
+                    // generation yet is still on its way (from a peer, or from another block of this
+                    // grid) and is read again (bounded).
+                    const uint64_t* src = x_pairs + (size_t)c * W;
+                    const long long start = clock64();
+                    bool ok = false;
+                    while (!ok) {
+                        ok = true;
 #pragma unroll
-                for (int i = 0; i < NR; ++i) {
-                    const uint32_t r = rp + i * RP;  // row inside the tile
-                    q[i] = *reinterpret_cast<const uint4*>(sq + ((size_t)r * p.nchunks + c) * 16);
-                    dh[i] = *reinterpret_cast<const uint16_t*>(ss + ((size_t)r * p.nb + blk) * 2);
-                }
+                        for (int i = 0; i < W / 2; ++i) {
+                            uint64_t a, b;
+                            ld_volatile_v2_u64(src + 2 * i, a, b);
+                            ok = ok && (uint32_t)(a >> 32) == x_gen && (uint32_t)(b >> 32) == x_gen;
+                            xv[2 * i] = __uint_as_float((uint32_t)a);
+                            xv[2 * i + 1] = __uint_as_float((uint32_t)b);
+                        }
+                        if (!ok && (*abort_flag != 0u || clock64() - start > kWaitCycles)) break;
+                    }
+                    if (!ok) {
+                        if (*abort_flag == 0u) report(p.status, 16);
+                        *abort_flag = 1u;
+                    }
+                } else if (valid) {
+                    const float* src = x + (size_t)c * W;
+                    if (x_aligned) {
 #pragma unroll
-                for (int i = 0; i < NR; ++i) {
-                    const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
-                    int sa = initA[j], sb = initB[j], sc = initC[j];
-                    if (QT == 1) {
-#pragma unroll
-                        for (int m = 0; m < 4; ++m) {
-                            const uint32_t lo = w[m] & 0x0F0F0F0Fu, hi = (w[m] >> 4) & 0x0F0F0F0Fu;
-                            sa = dp4a_ss(lo, DA[j][m], sa);
-                            sb = dp4a_su(lo, DB[j][m], sb);
-                            sc = dp4a_su(lo, DC[j][m], sc);
-                            sa = dp4a_ss(hi, DA[j][4 + m], sa);
-                            sb = dp4a_su(hi, DB[j][4 + m], sb);
-                            sc = dp4a_su(hi, DC[j][4 + m], sc);
+                        for (int i = 0; i < W / 4; ++i) {
+                            const float4 v = __ldg(reinterpret_cast<const float4*>(src) + i);
+                            xv[4 * i + 0] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
                         }
                     } else {
 #pragma unroll
-                        for (int m = 0; m < 4; ++m) {
-                            sa = dp4a_ss(w[m], DA[j][m], sa);
-                            sb = dp4a_su(w[m], DB[j][m], sb);
-                            sc = dp4a_su(w[m], DC[j][m], sc);
-                        }
+                        for (int i = 0; i < W; ++i) xv[i] = __ldg(src + i);
                     }
-                    // sum q X = 65536 sa + 256 sb + sc; |256 sb + sc| < 2^31 for both formats.
-                    const float tsum = fmaf((float)sa, 65536.0f, (float)(sb * 256 + sc));
-                    const float d = __half2float(__ushort_as_half(dh[i]));
-                    acc[i] = fmaf(d * sxs[j], tsum, acc[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < W; ++i) xv[i] = 0.0f;
+                }
+                float amax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < W; ++i) amax = fmaxf(amax, fabsf(xv[i]));
+                // |x * inv| <= 8388606.5 before rounding, so X stays within 24 signed bits without a clamp.
+                const float inv = amax > 0.0f ? 8388606.0f / amax : 0.0f;
+                sxs[j] = valid ? amax / 8388606.0f : 0.0f;
+                int sa = 0, sb = 0, sc = 0;
+#pragma unroll
+                for (int r = 0; r < DR; ++r) {
+                    const uint32_t X0 = (uint32_t)__float2int_rn(xv[4 * r + 0] * inv);
+                    const uint32_t X1 = (uint32_t)__float2int_rn(xv[4 * r + 1] * inv);
+                    const uint32_t X2 = (uint32_t)__float2int_rn(xv[4 * r + 2] * inv);
+                    const uint32_t X3 = (uint32_t)__float2int_rn(xv[4 * r + 3] * inv);
+                    // byte n of each X gathered into one register: n = 2 signed high, 1 middle, 0 low
+                    DA[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0062), __byte_perm(X2, X3, 0x0062), 0x5410);
+                    DB[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0051), __byte_perm(X2, X3, 0x0051), 0x5410);
+                    DC[j][r] = __byte_perm(__byte_perm(X0, X1, 0x0040), __byte_perm(X2, X3, 0x0040), 0x5410);
+                    sa = dp4a_ss(0x01010101u, DA[j][r], sa);
+                    sb = dp4a_su(0x01010101u, DB[j][r], sb);
+                    sc = dp4a_su(0x01010101u, DC[j][r], sc);
+                }
+                initA[j] = QT == 1 ? -8 * sa : 0;
+                initB[j] = QT == 1 ? -8 * sb : 0;
+                initC[j] = QT == 1 ? -8 * sc : 0;
+            }
+        }
+
+        const uint64_t row0 = op.row0;
+        for (; t < tiles; t += gridDim.x, ++k) {
+            const uint32_t s = k % p.stages;
+            if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 13);
+            const uint8_t* sq = smem + (size_t)s * p.stage_bytes;
+            const uint64_t soff = (row0 + (uint64_t)t * TR) * p.nb * 2;
+            const uint8_t* ss = sq + p.q_stage_bytes + (uint32_t)(soff & 15);
+
+            float acc[NR];
+#pragma unroll
+            for (int i = 0; i < NR; ++i) acc[i] = 0.0f;
+
+            if (active) {
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    // a chunk position past the row's end reads chunk 0 with sx = 0
+                    const uint32_t cj = tc + j * p.tpr;
+                    const uint32_t c = cj < p.nchunks ? cj : 0;
+                    const uint32_t blk = QT == 1 ? c : (c >> 1);
+                    // All shared-memory reads of the tile first, so that the integer chains of the
+                    // NR rows can overlap.
+                    uint4 q[NR];
+                    uint16_t dh[NR];
+#pragma unroll
+                    for (int i = 0; i < NR; ++i) {
+                        const uint32_t r = rp + i * RP;  // row inside the tile
+                        q[i] = *reinterpret_cast<const uint4*>(sq + ((size_t)r * p.nchunks + c) * 16);
+                        dh[i] = *reinterpret_cast<const uint16_t*>(ss + ((size_t)r * p.nb + blk) * 2);
+                    }
+#pragma unroll
+                    for (int i = 0; i < NR; ++i) {
+                        const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+                        int sa = initA[j], sb = initB[j], sc = initC[j];
+                        if (QT == 1) {
+#pragma unroll
+                            for (int m = 0; m < 4; ++m) {
+                                const uint32_t lo = w[m] & 0x0F0F0F0Fu, hi = (w[m] >> 4) & 0x0F0F0F0Fu;
+                                sa = dp4a_ss(lo, DA[j][m], sa);
+                                sb = dp4a_su(lo, DB[j][m], sb);
+                                sc = dp4a_su(lo, DC[j][m], sc);
+                                sa = dp4a_ss(hi, DA[j][4 + m], sa);
+                                sb = dp4a_su(hi, DB[j][4 + m], sb);
+                                sc = dp4a_su(hi, DC[j][4 + m], sc);
+                            }
+                        } else {
+#pragma unroll
+                            for (int m = 0; m < 4; ++m) {
+                                sa = dp4a_ss(w[m], DA[j][m], sa);
+                                sb = dp4a_su(w[m], DB[j][m], sb);
+                                sc = dp4a_su(w[m], DC[j][m], sc);
+                            }
+                        }
+                        // sum q X = 65536 sa + 256 sb + sc; |256 sb + sc| < 2^31 for both formats.
+                        const float tsum = fmaf((float)sa, 65536.0f, (float)(sb * 256 + sc));
+                        const float d = __half2float(__ushort_as_half(dh[i]));
+                        acc[i] = fmaf(d * sxs[j], tsum, acc[i]);
+                    }
                 }
             }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty(s));  // this warp has finished reading the stage
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty(s));  // this warp has finished reading the stage
 
-        const float total = transposed_reduce<NR>(acc, lane);
-        const uint32_t b = k % kRedBufs;
-        if (k >= kRedBufs && !mbar_wait(red_empty(b), ((k / kRedBufs) - 1) & 1, abort_flag)) report(p.status, 15);
-        float* slot = red + (size_t)b * TR * kWarps;
-        if (active) {
-            // lanes whose low bits are zero hold one row each
-            constexpr uint32_t low_mask = NR == 8 ? 3u : NR == 4 ? 7u : NR == 2 ? 15u : 31u;
-            if ((lane & low_mask) == 0) {
-                const uint32_t i = NR == 8 ? (((lane >> 4) & 1u) * 4 + ((lane >> 3) & 1u) * 2 + ((lane >> 2) & 1u))
-                                 : NR == 4 ? (((lane >> 4) & 1u) * 2 + ((lane >> 3) & 1u))
-                                 : NR == 2 ? ((lane >> 4) & 1u) : 0u;
-                slot[(rp + i * RP) * kWarps + (warp - rp * wpr)] = total;
+            const float total = transposed_reduce<NR>(acc, lane);
+            const uint32_t b = k % kRedBufs;
+            if (k >= kRedBufs && !mbar_wait(red_empty(b), ((k / kRedBufs) - 1) & 1, abort_flag)) report(p.status, 15);
+            float* slot = red + (size_t)b * TR * kWarps;
+            if (active) {
+                // lanes whose low bits are zero hold one row each
+                constexpr uint32_t low_mask = NR == 8 ? 3u : NR == 4 ? 7u : NR == 2 ? 15u : 31u;
+                if ((lane & low_mask) == 0) {
+                    const uint32_t i = NR == 8 ? (((lane >> 4) & 1u) * 4 + ((lane >> 3) & 1u) * 2 + ((lane >> 2) & 1u))
+                                     : NR == 4 ? (((lane >> 4) & 1u) * 2 + ((lane >> 3) & 1u))
+                                     : NR == 2 ? ((lane >> 4) & 1u) : 0u;
+                    slot[(rp + i * RP) * kWarps + (warp - rp * wpr)] = total;
+                }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(red_full(b));
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(red_full(b));
     }
 }
 
@@ -425,7 +490,99 @@ vx_status launch_tr(vx_context* ctx, int qtype, uint32_t tr, int cpt, int rp, co
     return qtype == VX_Q4_0 ? launch_qt<1, 4, XCH>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 4, XCH>(ctx, cpt, rp, p, grid, smem);
 }
 
+// How one row shape maps onto the kernel.
+struct StreamConfig {
+    uint32_t tr, tpr, stages, stage_bytes, q_stage;
+    int cpt, rp;
+    int64_t per_sm;
+    size_t smem;
+};
+
+// false: the row is too long for the shared-memory ring or the register-resident x.
+bool choose_config(vx_context* ctx, uint32_t nchunks, uint32_t nb, uint32_t max_tiles_hint_rows, bool flagged,
+                   StreamConfig* c) {
+    using vx::option;
+    c->tr = option(ctx, "gemv.tile_rows", 8) == 4 ? 4 : 8;
+    if (nchunks > 4 * kConsumers) return false;
+    c->cpt = nchunks <= kConsumers ? 1 : nchunks <= 2 * kConsumers ? 2 : 4;
+    uint32_t tpr = ((nchunks + c->cpt - 1) / c->cpt + 31) / 32 * 32;
+    c->tpr = std::min<uint32_t>(tpr, kConsumers);
+    c->rp = 1;
+    if (c->cpt == 1) {
+        const uint32_t fit = kConsumers / c->tpr;  // 1..8
+        c->rp = fit >= 4 ? 4 : fit >= 2 ? 2 : 1;
+    }
+    c->q_stage = c->tr * nchunks * 16;
+    const uint32_t s_stage = (c->tr * nb * 2 + 32 + 15) / 16 * 16;
+    c->stage_bytes = (c->q_stage + s_stage + 127) / 128 * 128;
+    const size_t fixed = kRedBufs * c->tr * kWarps * sizeof(float) + (2 * 16 + 2 * kRedBufs + 1) * sizeof(uint64_t);
+    const uint32_t tiles = (max_tiles_hint_rows + c->tr - 1) / c->tr;
+    // Measured on B200: two CTAs per SM pay off once every CTA slot streams many tiles; short
+    // launches do better with one CTA per SM, which also balances their few tiles better.  The
+    // ring stays at two stages by default so that a CTA takes well under half of the SM's
+    // shared memory: the next kernel of a dependent-launch chain can then become resident and
+    // prefetch its first tiles while this one is still running.
+    int64_t per_sm = option(ctx, "gemv.ctas_per_sm", 0);
+    if (per_sm <= 0) per_sm = tiles >= 16u * (uint32_t)ctx->sm_count ? 2 : 1;
+    if (flagged) per_sm = 1;  // the flagged kernel's registers allow one CTA per SM
+    per_sm = std::min<int64_t>(per_sm, 4);
+    const size_t budget = (size_t)(200 * 1024) / (size_t)per_sm - fixed;
+    int64_t want_stages = option(ctx, "gemv.stages", 0);
+    if (want_stages <= 0) want_stages = 2;
+    uint32_t stages = (uint32_t)std::min<size_t>(16, budget / c->stage_bytes);
+    stages = std::min<uint32_t>(stages, (uint32_t)want_stages);
+    if (stages < 2) {
+        // a long row: give one CTA the whole SM
+        per_sm = 1;
+        stages = (uint32_t)std::min<size_t>(2, ((size_t)(227 * 1024) - 1024 - fixed) / c->stage_bytes);
+        if (stages < 2) return false;
+    }
+    c->stages = stages;
+    c->per_sm = per_sm;
+    c->smem = (size_t)stages * c->stage_bytes + fixed;
+    return true;
+}
+
+void fill_common(StreamParams* p, const StreamConfig& c, uint32_t nchunks, uint32_t nb, vx_context* ctx) {
+    p->nchunks = nchunks;
+    p->nb = nb;
+    p->tpr = c.tpr;
+    p->stages = c.stages;
+    p->stage_bytes = c.stage_bytes;
+    p->q_stage_bytes = c.q_stage;
+    p->status = ctx->d_status;
+}
+
+void fill_plain_op(OpParams* o, const vx_qweights* w, size_t row0, uint32_t nrows, const float* x, float* y,
+                   float* const* y_peer, uint32_t n_peer) {
+    *o = OpParams{};
+    o->quants = w->d_quants;
+    o->scales = reinterpret_cast<const uint8_t*>(w->d_scales);
+    o->row0 = row0;
+    o->nrows = nrows;
+    o->x = x;
+    o->x_aligned = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 ? 1u : 0u;
+    o->y = y;
+    o->n_peer = std::min<uint32_t>(n_peer, vx::kMaxPeers);
+    for (uint32_t d = 0; d < o->n_peer; ++d) o->y_peer[d] = y_peer[d];
+    o->x_vec = -1;
+    o->y_vec = -1;
+    o->y_pair_stride = 1;
+}
+
 }  // namespace
+
+// A list of GEMVs prepared for one launch.
+struct vx_gemv_batch {
+    int device = 0;
+    int qtype = 0;
+    bool flagged = false;
+    StreamConfig cfg{};
+    StreamParams params{};
+    dim3 grid;
+    OpParams* d_ops = nullptr;
+    size_t n_ops = 0;
+};
 
 namespace vx {
 
@@ -434,87 +591,48 @@ namespace vx {
 vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
                              const float* x, float* y, float* const* y_peer, uint32_t n_peer,
                              const Exchange* xch, bool* eligible) {
-    const uint32_t TR = option(ctx, "gemv.tile_rows", 8) == 4 ? 4 : 8;
     *eligible = false;
     const uint32_t nb = (uint32_t)w->blocks_per_row;
     const uint32_t nchunks = (uint32_t)(w->quant_row_bytes / 16);
-    if (nchunks > 4 * kConsumers) return VX_OK;
-    const int cpt = nchunks <= kConsumers ? 1 : nchunks <= 2 * kConsumers ? 2 : 4;
-    uint32_t tpr = ((nchunks + cpt - 1) / cpt + 31) / 32 * 32;
-    tpr = std::min<uint32_t>(tpr, kConsumers);
-    int rp = 1;
-    if (cpt == 1) {
-        const uint32_t fit = kConsumers / tpr;  // 1..8
-        rp = fit >= 4 ? 4 : fit >= 2 ? 2 : 1;
+    const bool flagged = xch && (xch->x_vec || xch->y_vec);
+    StreamConfig c;
+    if (!choose_config(ctx, nchunks, nb, nrows, flagged, &c)) return VX_OK;
+
+    StreamParams p{};
+    fill_common(&p, c, nchunks, nb, ctx);
+    p.n_ops = 1;
+    OpParams& o = p.op0;
+    fill_plain_op(&o, w, row0, nrows, x, y, y_peer, n_peer);
+    if (flagged) {
+        // vector table: the written vector first (its header carries the retire counter)
+        if (xch->y_vec) {
+            o.y_vec = (int32_t)p.n_vec;
+            p.vec_hdr[p.n_vec] = static_cast<uint32_t*>(xch->y_vec);
+            p.vec_writes[p.n_vec++] = 1;
+            o.y_gen_add = 1;
+            auto pairs = [&](void* base) {
+                return reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(base) + kExchangeHeader) + xch->y_row0;
+            };
+            o.y_pairs = pairs(xch->y_vec);
+            o.y_pair_stride = (uint32_t)xch->y_stride;
+            o.n_pair_peer = std::min<uint32_t>(xch->n_peers, kMaxPeers);
+            for (uint32_t d = 0; d < o.n_pair_peer; ++d) o.y_pairs_peer[d] = pairs(xch->peer_y_vec[d]);
+        }
+        if (xch->x_vec) {
+            // reading and writing one vector in the same GEMV is refused by the caller
+            o.x_vec = (int32_t)p.n_vec;
+            p.vec_hdr[p.n_vec] = const_cast<uint32_t*>(static_cast<const uint32_t*>(xch->x_vec));
+            p.vec_writes[p.n_vec++] = 0;
+            o.x_gen_add = 0;
+            o.x_pairs = reinterpret_cast<const uint64_t*>(static_cast<const uint8_t*>(xch->x_vec) + kExchangeHeader);
+        }
     }
 
-    const uint32_t q_stage = TR * nchunks * 16;
-    const uint32_t s_stage = (TR * nb * 2 + 32 + 15) / 16 * 16;
-    const uint32_t stage_bytes = (q_stage + s_stage + 127) / 128 * 128;
-    const size_t fixed = kRedBufs * TR * kWarps * sizeof(float) + (2 * 16 + 2 * kRedBufs + 1) * sizeof(uint64_t);
-    const uint32_t tiles = (nrows + TR - 1) / TR;
-    // Measured on B200: two CTAs per SM pay off once every CTA slot streams many tiles; short
-    // launches do better with one CTA per SM, which also balances their few tiles better.  The
-    // ring stays at two stages by default so that a CTA takes well under half of the SM's
-    // shared memory: the next kernel of a dependent-launch chain can then become resident and
-    // prefetch its first tiles while this one is still running.
-    int64_t per_sm = option(ctx, "gemv.ctas_per_sm", 0);
-    if (per_sm <= 0) per_sm = tiles >= 16u * (uint32_t)ctx->sm_count ? 2 : 1;
-    if (xch && (xch->x_vec || xch->y_vec)) per_sm = 1;  // the flagged kernel's registers allow one CTA per SM
-    per_sm = std::min<int64_t>(per_sm, 4);
-    const size_t budget = (size_t)(200 * 1024) / (size_t)per_sm - fixed;
-    int64_t want_stages = option(ctx, "gemv.stages", 0);
-    if (want_stages <= 0) want_stages = 2;
-    uint32_t stages = (uint32_t)std::min<size_t>(16, budget / stage_bytes);
-    stages = std::min<uint32_t>(stages, (uint32_t)want_stages);
-    if (stages < 2) {
-        // a long row: give one CTA the whole SM
-        per_sm = 1;
-        stages = (uint32_t)std::min<size_t>(2, ((size_t)(227 * 1024) - 1024 - fixed) / stage_bytes);
-        if (stages < 2) return VX_OK;
-    }
-
-    StreamParams p;
-    p.quants = w->d_quants;
-    p.scales = reinterpret_cast<const uint8_t*>(w->d_scales);
-    p.nchunks = nchunks;
-    p.nb = nb;
-    p.row0 = row0;
-    p.nrows = nrows;
-    p.x = x;
-    p.y = y;
-    p.x_pairs = xch && xch->x_vec ? reinterpret_cast<const uint64_t*>(static_cast<const uint8_t*>(xch->x_vec) + kExchangeHeader) : nullptr;
-    p.x_hdr = xch ? static_cast<const uint32_t*>(xch->x_vec) : nullptr;
-    p.y_pairs = nullptr;
-    p.y_hdr = nullptr;
-    p.n_pair_peer = 0;
-    p.y_pair_stride = xch ? (uint32_t)xch->y_stride : 1;
-    for (uint32_t d = 0; d < (uint32_t)kMaxPeers; ++d) p.y_pairs_peer[d] = nullptr;
-    if (xch && xch->y_vec) {
-        auto pairs = [&](void* base) {
-            return reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(base) + kExchangeHeader) + xch->y_row0;
-        };
-        p.y_pairs = pairs(xch->y_vec);
-        p.y_hdr = static_cast<uint32_t*>(xch->y_vec);
-        p.n_pair_peer = std::min<uint32_t>(xch->n_peers, kMaxPeers);
-        for (uint32_t d = 0; d < p.n_pair_peer; ++d) p.y_pairs_peer[d] = pairs(xch->peer_y_vec[d]);
-    }
-    p.n_peer = std::min<uint32_t>(n_peer, kMaxPeers);
-    for (uint32_t d = 0; d < (uint32_t)kMaxPeers; ++d) p.y_peer[d] = d < p.n_peer ? y_peer[d] : nullptr;
-    p.tpr = tpr;
-    p.stages = stages;
-    p.stage_bytes = stage_bytes;
-    p.q_stage_bytes = q_stage;
-    p.x_vec = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 ? 1u : 0u;
-    p.status = ctx->d_status;
-
-    const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * per_sm);
+    const uint32_t tiles = (nrows + c.tr - 1) / c.tr;
+    const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * c.per_sm);
     dim3 grid(std::min(tiles, slots));
-    const size_t smem = (size_t)stages * stage_bytes + fixed;
-    // The flagged kernel needs more registers than two CTAs per SM leave it.
-    const bool flagged = p.x_pairs || p.y_pairs;
-    const vx_status st = flagged ? launch_tr<true>(ctx, w->type, TR, cpt, rp, p, grid, smem)
-                                 : launch_tr<false>(ctx, w->type, TR, cpt, rp, p, grid, smem);
+    const vx_status st = flagged ? launch_tr<true>(ctx, w->type, c.tr, c.cpt, c.rp, p, grid, c.smem)
+                                 : launch_tr<false>(ctx, w->type, c.tr, c.cpt, c.rp, p, grid, c.smem);
     if (st != VX_OK) return st;
     ctx->launches++;
     ctx->status_dirty = true;
@@ -523,3 +641,133 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
 }
 
 }  // namespace vx
+
+extern "C" {
+
+vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_ops, vx_gemv_batch** out) {
+    using vx::fail;
+    VX_REQUIRE(ctx && ops && out && n_ops >= 1, VX_ERR_INVALID_ARGUMENT, "vx_gemv_batch_create: null or empty argument");
+    *out = nullptr;
+    VX_REQUIRE(n_ops <= 4096, VX_ERR_INVALID_ARGUMENT, "at most 4096 GEMVs in a list (%zu given)", n_ops);
+    const vx_qweights* w0 = ops[0].w;
+    VX_REQUIRE(w0, VX_ERR_INVALID_ARGUMENT, "GEMV 0 has no weights");
+    std::unique_ptr<vx_gemv_batch> b(new vx_gemv_batch());
+    b->device = ctx->device;
+    b->qtype = w0->type;
+    b->n_ops = n_ops;
+    std::vector<OpParams> host(n_ops);
+    StreamParams& p = b->params;
+    uint32_t max_rows = 0;
+    auto vec_index = [&](const void* hdr) -> int32_t {
+        for (uint32_t v = 0; v < p.n_vec; ++v)
+            if (p.vec_hdr[v] == hdr) return (int32_t)v;
+        if (p.n_vec == (uint32_t)kMaxVecs) return -1;
+        p.vec_hdr[p.n_vec] = const_cast<uint32_t*>(static_cast<const uint32_t*>(hdr));
+        p.vec_writes[p.n_vec] = 0;
+        return (int32_t)p.n_vec++;
+    };
+    // Written vectors first, so that entry 0 (whose header carries the retire counter) is one this list owns.
+    for (size_t i = 0; i < n_ops; ++i)
+        if (ops[i].y_xvec) VX_REQUIRE(vec_index(ops[i].y_xvec) >= 0, VX_ERR_UNSUPPORTED, "more than %d exchange vectors", kMaxVecs);
+    for (size_t i = 0; i < n_ops; ++i) {
+        const vx_gemv_op& g = ops[i];
+        VX_REQUIRE(g.w, VX_ERR_INVALID_ARGUMENT, "GEMV %zu has no weights", i);
+        VX_REQUIRE(g.w->device == ctx->device, VX_ERR_INVALID_ARGUMENT, "weights of GEMV %zu live on device %d", i, g.w->device);
+        VX_REQUIRE(g.w->type == w0->type && g.w->cols == w0->cols, VX_ERR_UNSUPPORTED,
+                   "GEMV %zu: a list holds one quantisation type and one column count", i);
+        VX_REQUIRE(g.row0 <= g.w->rows && g.nrows <= g.w->rows - g.row0 && g.nrows >= 1 && g.nrows <= 0xFFFFFFFFull,
+                   VX_ERR_OUT_OF_BOUNDS, "GEMV %zu: rows [%zu, %zu) outside a matrix of %zu rows", i, g.row0,
+                   g.row0 + g.nrows, g.w->rows);
+        VX_REQUIRE(g.x_xvec || g.x, VX_ERR_INVALID_ARGUMENT, "GEMV %zu has no x", i);
+        VX_REQUIRE(g.y || g.y_xvec, VX_ERR_INVALID_ARGUMENT, "GEMV %zu has no y", i);
+        VX_REQUIRE(g.n_peers <= (size_t)vx::kMaxPeers && (g.n_peers == 0 || (g.y_xvec && g.peer_y_xvec)),
+                   VX_ERR_INVALID_ARGUMENT, "GEMV %zu: peers need exchange vectors (at most %d)", i, vx::kMaxPeers);
+        VX_REQUIRE(!g.y_xvec || g.x_xvec != g.y_xvec, VX_ERR_INVALID_ARGUMENT, "GEMV %zu reads the vector it writes", i);
+        VX_REQUIRE((reinterpret_cast<uintptr_t>(g.x_xvec) & 15u) == 0 && (reinterpret_cast<uintptr_t>(g.y_xvec) & 15u) == 0,
+                   VX_ERR_INVALID_ARGUMENT, "GEMV %zu: exchange vectors are 16-byte aligned", i);
+        OpParams& o = host[i];
+        fill_plain_op(&o, g.w, g.row0, (uint32_t)g.nrows, g.x_xvec ? nullptr : g.x, g.y, nullptr, 0);
+        if (g.x_xvec) {
+            const int32_t v = vec_index(g.x_xvec);
+            VX_REQUIRE(v >= 0, VX_ERR_UNSUPPORTED, "more than %d exchange vectors", kMaxVecs);
+            o.x_vec = v;
+            o.x_gen_add = p.vec_writes[v];  // writes by the GEMVs before this one
+            o.x_pairs = reinterpret_cast<const uint64_t*>(static_cast<const uint8_t*>(g.x_xvec) + vx::kExchangeHeader);
+            b->flagged = true;
+        }
+        if (g.y_xvec) {
+            const int32_t v = vec_index(g.y_xvec);
+            o.y_vec = v;
+            o.y_gen_add = ++p.vec_writes[v];
+            VX_REQUIRE(g.y_stride >= 1 && g.y_stride <= 0xFFFFu, VX_ERR_INVALID_ARGUMENT, "GEMV %zu: element stride %zu", i, g.y_stride);
+            auto pairs = [&](void* base) {
+                return reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(base) + vx::kExchangeHeader) + g.y_row0;
+            };
+            o.y_pairs = pairs(g.y_xvec);
+            o.y_pair_stride = (uint32_t)g.y_stride;
+            o.n_pair_peer = (uint32_t)g.n_peers;
+            for (size_t d = 0; d < g.n_peers; ++d) {
+                VX_REQUIRE(g.peer_y_xvec[d] && (reinterpret_cast<uintptr_t>(g.peer_y_xvec[d]) & 15u) == 0,
+                           VX_ERR_INVALID_ARGUMENT, "GEMV %zu: exchange vector of peer %zu is null or misaligned", i, d);
+                o.y_pairs_peer[d] = pairs(g.peer_y_xvec[d]);
+            }
+            b->flagged = true;
+        }
+        max_rows = std::max<uint32_t>(max_rows, (uint32_t)g.nrows);
+    }
+    const uint32_t nb = (uint32_t)w0->blocks_per_row;
+    const uint32_t nchunks = (uint32_t)(w0->quant_row_bytes / 16);
+    // A list streams like one long GEMV: size the launch for the sum of its rows.
+    uint64_t total_rows = 0;
+    for (size_t i = 0; i < n_ops; ++i) total_rows += ops[i].nrows;
+    VX_REQUIRE(choose_config(ctx, nchunks, nb, (uint32_t)std::min<uint64_t>(total_rows, 0xFFFFFFFFull), b->flagged, &b->cfg),
+               VX_ERR_UNSUPPORTED, "rows of %zu columns do not fit the streaming kernel", w0->cols);
+    fill_common(&p, b->cfg, nchunks, nb, ctx);
+    p.n_ops = (uint32_t)n_ops;
+    const uint32_t tiles = (max_rows + b->cfg.tr - 1) / b->cfg.tr;
+    const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * b->cfg.per_sm);
+    b->grid = dim3(std::min(tiles, slots));
+    vx::DeviceGuard guard(ctx->device);
+    if (n_ops == 1) {
+        p.op0 = host[0];
+    } else {
+        VX_CUDA(cudaMalloc(&b->d_ops, n_ops * sizeof(OpParams)));
+        const cudaError_t e = cudaMemcpy(b->d_ops, host.data(), n_ops * sizeof(OpParams), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            cudaFree(b->d_ops);
+            return fail(VX_ERR_CUDA, "uploading the GEMV list: %s", cudaGetErrorString(e));
+        }
+        p.ops = b->d_ops;
+    }
+    *out = b.release();
+    return VX_OK;
+}
+
+vx_status vx_gemv_batch_launch(vx_context* ctx, const vx_gemv_batch* b) {
+    using vx::fail;
+    VX_REQUIRE(ctx && b, VX_ERR_INVALID_ARGUMENT, "vx_gemv_batch_launch: null argument");
+    VX_REQUIRE(b->device == ctx->device, VX_ERR_INVALID_ARGUMENT, "the list was made for device %d", b->device);
+    vx::DeviceGuard guard(ctx->device);
+    StreamParams p = b->params;
+    p.status = ctx->d_status;
+    const StreamConfig& c = b->cfg;
+    const vx_status st = b->flagged ? launch_tr<true>(ctx, b->qtype, c.tr, c.cpt, c.rp, p, b->grid, c.smem)
+                                    : launch_tr<false>(ctx, b->qtype, c.tr, c.cpt, c.rp, p, b->grid, c.smem);
+    if (st != VX_OK) return st;
+    ctx->launches++;
+    ctx->status_dirty = true;
+    return VX_OK;
+}
+
+vx_status vx_gemv_batch_free(vx_context* ctx, vx_gemv_batch* b) {
+    using vx::fail;
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_gemv_batch_free: null context");
+    if (!b) return VX_OK;
+    vx::DeviceGuard guard(ctx->device);
+    VX_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (b->d_ops) cudaFree(b->d_ops);
+    delete b;
+    return VX_OK;
+}
+
+}  // extern "C"

@@ -258,6 +258,56 @@ class Gemv:
         _lib.check(_lib.load().vx_gemv_q_rows(backend._ctx, w._h, row0, nrows, xp, xs, yp, ys, batch))
 
 
+class GemvBatch:
+    """A fixed list of GEMVs run by ONE persistent launch (vx_gemv_batch): one weight stream, one prologue.
+
+    Each entry is a dict: w (QuantizedMatrix), and optionally row0, nrows, x (plain device pointer), x_xvec
+    (exchange vector to read x from), y (plain rows), y_xvec (exchange vector to write), peers (the same
+    vector on the peer GPUs), y_row0, y_stride.  Entries may depend on each other only through exchange
+    vectors.  Pointers are captured at construction."""
+
+    def __init__(self, backend: Backend, entries):
+        lib = _lib.load()
+        n = len(entries)
+        arr = (_lib.VxGemvOp * n)()
+        self._keep = []
+        for i, e in enumerate(entries):
+            w = e["w"]
+            row0 = e.get("row0", 0)
+            nrows = e.get("nrows")
+            peers = list(e.get("peers") or [])
+            pa = (C.c_void_p * max(1, len(peers)))(*peers)
+            self._keep.append((w, pa))
+            arr[i].w = w._h
+            arr[i].row0 = row0
+            arr[i].nrows = w.rows - row0 if nrows is None else nrows
+            arr[i].x_xvec = e.get("x_xvec") or None
+            arr[i].x = e.get("x") or None
+            arr[i].y = e.get("y") or None
+            arr[i].y_xvec = e.get("y_xvec") or None
+            arr[i].peer_y_xvec = pa
+            arr[i].n_peers = len(peers)
+            arr[i].y_row0 = e.get("y_row0", 0)
+            arr[i].y_stride = e.get("y_stride", 1)
+        h = C.c_void_p()
+        _lib.check(lib.vx_gemv_batch_create(backend._ctx, arr, n, C.byref(h)))
+        self.backend, self._h, self.n = backend, h, n
+
+    def launch(self) -> None:
+        _lib.check(_lib.load().vx_gemv_batch_launch(self.backend._ctx, self._h))
+
+    def free(self) -> None:
+        if self._h and self.backend._ctx:
+            _lib.check(_lib.load().vx_gemv_batch_free(self.backend._ctx, self._h))
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 def _ptr_len(t):
     """Device pointer (with view offset) and remaining length of a Tensor / view / buffer / raw int."""
     if isinstance(t, int):

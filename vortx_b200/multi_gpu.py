@@ -139,6 +139,23 @@ class PeerScatterGemv:
                                                self.vectors[y_vec].local.ptr, self._vec_peers[y_vec],
                                                len(self._others), self.row0, self.world if self.cyclic else 1))
 
+    def chain_batch(self, weights_list, x_ptr: int):
+        """The whole chain as ONE persistent launch per GPU (GemvBatch): link 0 reads the plain x, link l reads
+        exchange vector (l - 1) % 2 and writes l % 2.  Returns the batch; after `launch()`, `unpack((len - 1) % 2, ...)`
+        ends the chain."""
+        from .linalg import GemvBatch
+        entries = []
+        for l, w in enumerate(weights_list):
+            e = {"w": w, "nrows": self.nrows, "y_xvec": self.vectors[l % 2].local.ptr,
+                 "peers": [self.vectors[l % 2].ptrs[r] for r in self._others],
+                 "y_row0": self.row0, "y_stride": self.world if self.cyclic else 1}
+            if l == 0:
+                e["x"] = x_ptr
+            else:
+                e["x_xvec"] = self.vectors[(l - 1) % 2].local.ptr
+            entries.append(e)
+        return GemvBatch(self.backend, entries)
+
     def unpack(self, vec: int, out_ptr: int, n: Optional[int] = None) -> None:
         """Exchange vector -> plain f32 at out_ptr, waiting on the device for the pairs still under way."""
         from . import _lib
