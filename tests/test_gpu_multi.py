@@ -213,3 +213,64 @@ def test_peer_scatter_and_nccl_gemv_on_two_gpus(tmp_path, oracle):
             assert np.abs(peer - y64).max() / np.abs(y64).max() <= 1e-4
             assert (np.abs(peer - y64) <= 2e-6 * absdot).all()
             assert np.array_equal(nccl[0].view(np.uint32), peer[0].view(np.uint32))   # same kernel, same rows
+
+
+def _gemm_worker(rank, world, port, out_dir):
+    """Column-sharded TF32 GEMM: peer-store epilogue + barrier kernel, and the NCCL all-gather + re-layout form."""
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import vortx_b200 as vb
+    from vortx_b200.multi_gpu import ShardedGemm
+    be = vb.Backend(rank)
+    stream = torch.cuda.ExternalStream(be.stream)
+    results = {}
+    for m, n, k in GEMM_CASES:
+        rng = np.random.Generator(np.random.Philox(m + n + k))
+        a = rng.random((m, k), dtype=np.float32) * 2 - 1
+        b = rng.random((k, n), dtype=np.float32) * 2 - 1
+        ad, bd = be.init_buffer(a.ravel()), be.init_buffer(b.ravel())   # B whole on every rank; each uses its columns
+        g = ShardedGemm(be, m, n, k)
+        for form in ("peer", "nccl"):
+            for rep in range(2):
+                with torch.cuda.stream(stream):
+                    if form == "peer":
+                        g.dispatch_peer(ad.ptr, bd.ptr + g.col0 * 4, n)
+                    else:
+                        g.dispatch_nccl(ad.ptr, bd.ptr + g.col0 * 4, n)
+            be.synchronize()
+            c = np.empty(m * n, np.float32)
+            be.slow_read_buffer(g.c.local, c.view(np.uint8))
+            results[f"{form}_{m}_{n}_{k}"] = c.reshape(m, n)
+            dist.barrier()
+        g.close()
+    np.savez(os.path.join(out_dir, f"gemm{rank}.npz"), **results)
+    dist.barrier()
+    be.close()
+    os._exit(0)
+
+
+GEMM_CASES = [(512, 512, 256), (300, 1024, 200), (1024, 2048, 1024)]
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_column_sharded_tf32_gemm_on_two_gpus(tmp_path):
+    world = 2
+    _run_ranks(_gemm_worker, world, str(tmp_path))
+    got = [np.load(tmp_path / f"gemm{r}.npz") for r in range(world)]
+    for m, n, k in GEMM_CASES:
+        rng = np.random.Generator(np.random.Philox(m + n + k))
+        a = rng.random((m, k), dtype=np.float32) * 2 - 1
+        b = rng.random((k, n), dtype=np.float32) * 2 - 1
+        want = a.astype(np.float64) @ b.astype(np.float64)
+        key = f"{m}_{n}_{k}"
+        for r in range(world):
+            peer, nccl = got[r][f"peer_{key}"], got[r][f"nccl_{key}"]
+            rel = np.linalg.norm(peer - want) / np.linalg.norm(want)
+            assert rel <= 5e-3, (key, r, rel)                       # TF32 inputs, f32 accumulate
+            assert np.array_equal(peer.view(np.uint32), nccl.view(np.uint32))          # same kernel, same tiles
+            assert np.array_equal(peer.view(np.uint32), got[0][f"peer_{key}"].view(np.uint32))   # one C everywhere

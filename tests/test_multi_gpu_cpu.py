@@ -69,3 +69,59 @@ def test_sharded_gemv_gathers_the_full_product(tmp_path, world, rows, batch):
         got = np.load(tmp_path / f"y{r}.npy")
         # each row's sum is computed by exactly one rank with the oracle's own order: bit-identical
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), r
+
+
+# ------------------------------------------------------------------ column-sharded GEMM ----
+
+from vortx_b200.multi_gpu import col_shard, panel_relayout_shape  # noqa: E402
+
+
+def test_col_shard_partitions_in_whole_blocks():
+    for cols in (32, 64, 1024, 8192, 1000, 96 + 5):
+        for world in (1, 2, 3, 4, 8):
+            spans = [col_shard(cols, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and sum(n for _, n in spans) == cols
+            for (a0, an), (b0, _) in zip(spans, spans[1:]):
+                assert a0 + an == b0
+            assert all(c0 % 32 == 0 for c0, _ in spans)
+            assert all(n % 32 == 0 for _, n in spans[:-1])
+    assert col_shard(8192, 8, 5) == (5 * 1024, 1024)
+
+
+def _gemm_worker(rank, world, port, m, n, k, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.Generator(np.random.Philox(7))
+        a = rng.random((m, k), dtype=np.float32) * 2 - 1
+        b = rng.random((k, n), dtype=np.float32) * 2 - 1
+        col0, ncols = col_shard(n, world, rank)
+        # the per-rank panel through the oracle's restatement of the reference GEMM
+        panel = np.zeros((m, ncols), np.float32)
+        o.gemm_dispatch(panel, a, np.ascontiguousarray(b[:, col0:col0 + ncols]),
+                        o.shape_contiguous(1, 1, m, ncols), o.shape_contiguous(1, 1, m, k),
+                        o.shape_contiguous(1, 1, k, ncols))
+        stack = torch.empty(world * m * ncols)      # rank-major: [world][m][ncols]
+        dist.all_gather_into_tensor(stack, torch.from_numpy(panel).reshape(-1))
+        sizes, strides = panel_relayout_shape(m, world, ncols)
+        c = o.contiguous(stack.numpy().ravel(), o.Shape(*sizes, *strides))
+        np.save(os.path.join(out_dir, f"c{rank}.npy"), c.reshape(m, n))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,m,n,k", [(2, 48, 128, 40), (4, 33, 256, 64)])
+def test_column_sharded_gemm_relayout_gives_the_unsharded_product(tmp_path, world, m, n, k):
+    """All-gather of rank-major panels + the strided gather (panel_relayout_shape) equals the unsharded GEMM,
+    bit for bit: every element is computed by exactly one rank in the reference's own order."""
+    mp.spawn(_gemm_worker, args=(world, _free_port(), m, n, k, str(tmp_path)), nprocs=world, join=True)
+    rng = np.random.Generator(np.random.Philox(7))
+    a = rng.random((m, k), dtype=np.float32) * 2 - 1
+    b = rng.random((k, n), dtype=np.float32) * 2 - 1
+    want = np.zeros((m, n), np.float32)
+    o.gemm_dispatch(want, a, b, o.shape_contiguous(1, 1, m, n), o.shape_contiguous(1, 1, m, k),
+                    o.shape_contiguous(1, 1, k, n))
+    for r in range(world):
+        got = np.load(tmp_path / f"c{r}.npy")
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), r

@@ -121,6 +121,7 @@ SIGNATURES = {
     "vx_gemv_batch_create": (C.c_int32, [_P, _P, C.c_size_t, C.POINTER(_P)]),
     "vx_gemv_batch_launch": (C.c_int32, [_P, _P]),
     "vx_gemv_batch_free": (C.c_int32, [_P, _P]),
+    "vx_gemm_tf32_scatter": (C.c_int32, [_P, _P, _P, _P, C.POINTER(VxShapes3), C.POINTER(_P), C.c_size_t]),
     "vx_peer_barrier": (C.c_int32, [_P, C.POINTER(_P), C.c_size_t, C.c_size_t]),
     "vx_reduce": (C.c_int32, [_P, C.c_int, C.c_int, C.c_int, _P, C.POINTER(VxShape), C.c_uint64, _P]),
     "vx_reduce_static": (C.c_int32, [C.c_int32, _P, C.c_int, C.c_int, _P, C.POINTER(VxShape), _P]),

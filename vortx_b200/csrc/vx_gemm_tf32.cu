@@ -64,8 +64,19 @@ struct Tf32Params {
     uint32_t tiles_m, tiles_n;
     uint32_t raster;  // tiles of M walked together before moving along N
     uint32_t out_vec; // rows of out are 16-byte aligned
+    // Column-sharded use: every tile is also stored at the same position of these buffers (the
+    // full-width C of each peer GPU, mapped into this process).  Plain stores over NVLink.
+    uint32_t n_peer;
+    float* out_peer[vx::kMaxPeers];
     vx::DeviceStatus* status;
 };
+
+// Per epilogue warp: a 32 x 32 block of C turned from "one row per lane" (how tensor memory
+// hands it out) into rows of 128 contiguous bytes, so that stores to a peer leave as full
+// 128-byte segments instead of 16-byte pieces.  Rows padded to 36 floats: 16-byte aligned and
+// conflict-free for 128-bit accesses.
+constexpr int kXposeStride = 36;
+constexpr uint32_t kXposeBytes = 4 * 32 * kXposeStride * 4;  // four epilogue warps
 
 struct SharedTail {
     uint64_t full[kMaxStages];
@@ -102,7 +113,7 @@ constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1
 template <int HALVES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const Tf32Params p) {
+                 const __grid_constant__ Tf32Params p) {
     using C = Cfg<HALVES>;
     constexpr int kStages = C::kStages, kAccStages = C::kAccStages;
     constexpr uint32_t kStageBytes = C::kStageBytes, kABytes = C::kABytes;
@@ -111,6 +122,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // The ring must start on a 1024-byte boundary (128-byte swizzle repeats every 8 rows).
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     SharedTail* tail = reinterpret_cast<SharedTail*>(smem + kStages * kStageBytes);
+    float* xpose_all = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256);  // used with peers only
     volatile uint32_t* abort_flag = &tail->abort_flag;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -226,8 +238,31 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     uint32_t v[32];
                     tmem_ld_32x32(taddr + c * 32, v);
                     tmem_ld_wait();
-                    if (row < p.m) {
-                        const uint32_t col = col0 + c * 32;
+                    const uint32_t col = col0 + c * 32;
+                    if (p.n_peer > 0) {
+                        // (the host only takes this path with 16-byte aligned rows and n % 32 == 0)
+                        float* xp = xpose_all + quad * 32 * kXposeStride;
+                        float4* mine = reinterpret_cast<float4*>(xp + lane * kXposeStride);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            mine[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        __syncwarp();
+                        const uint32_t row_base = tm * C::BM + h * BMMA + quad * 32;
+                        if (col < p.n) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint32_t r = j * 4 + (lane >> 3);
+                                if (row_base + r < p.m) {
+                                    const float4 val = *reinterpret_cast<const float4*>(xp + r * kXposeStride + 4 * (lane & 7));
+                                    const size_t at = (size_t)(row_base + r) * p.ldc + col + 4 * (lane & 7);
+                                    *reinterpret_cast<float4*>(p.out + at) = val;
+                                    for (uint32_t d = 0; d < p.n_peer; ++d) *reinterpret_cast<float4*>(p.out_peer[d] + at) = val;
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    } else if (row < p.m) {
                         if (p.out_vec && col + 32 <= p.n) {
                             float4* d4 = reinterpret_cast<float4*>(dst_row + c * 32);
 #pragma unroll
@@ -297,7 +332,8 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 template <int HALVES>
 vx_status launch_tiles(vx_context* ctx, const CUtensorMap& map_a, const CUtensorMap& map_b, Tf32Params p) {
     using C = Cfg<HALVES>;
-    const size_t smem = (size_t)C::kStages * C::kStageBytes + sizeof(SharedTail) + 1024;
+    const size_t smem = (size_t)C::kStages * C::kStageBytes + 256 + kXposeBytes + 1024;
+    static_assert(sizeof(SharedTail) <= 256, "barriers and the transposition buffers share the tail");
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63]) {
         VX_CUDA(cudaFuncSetAttribute(gemm_tf32_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -317,8 +353,14 @@ vx_status launch_tiles(vx_context* ctx, const CUtensorMap& map_a, const CUtensor
 namespace vx {
 
 vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const float* rhs,
-                           const vx_shapes3& s, bool* eligible) {
+                           const vx_shapes3& s, bool* eligible, float* const* out_peer, uint32_t n_peer) {
     *eligible = false;
+    if (n_peer > 0) {
+        // The peer path stores whole 32-column blocks as 16-byte pieces.
+        if (s.out.n != 1 || s.out.c != 1 || s.out.w % 32 != 0 || !aligned16(out) || s.out.h_stride % 4 != 0) return VX_OK;
+        for (uint32_t d = 0; d < n_peer; ++d)
+            if (!aligned16(out_peer[d])) return VX_OK;
+    }
     const uint32_t m = s.out.h, n = s.out.w, k = s.lhs.w;
     // What TMA can describe: unit stride along the rows, 16-byte aligned bases and row pitches.
     if (m == 0 || n == 0 || k == 0) return VX_OK;
@@ -361,6 +403,8 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
             p.raster = (uint32_t)std::max<int64_t>(1, option(ctx, "gemm.tf32.raster", halves == 2 ? 2 : 8));
             p.out_vec = (aligned16(c) && s.out.h_stride % 4 == 0) ? 1u : 0u;
             p.status = ctx->d_status;
+            p.n_peer = std::min<uint32_t>(n_peer, kMaxPeers);
+            for (uint32_t d = 0; d < (uint32_t)kMaxPeers; ++d) p.out_peer[d] = d < p.n_peer ? out_peer[d] : nullptr;
             vx_status st = halves == 2 ? launch_tiles<2>(ctx, map_a, map_b, p) : launch_tiles<1>(ctx, map_a, map_b, p);
             if (st != VX_OK) return st;
             ctx->launches++;

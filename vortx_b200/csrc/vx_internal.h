@@ -99,13 +99,17 @@ vx_status launch_gemm_simt_exact(vx_context* ctx, float* out, const float* lhs, 
 
 // tcgen05 kernel (vx_gemm_tf32.cu).  *eligible = false when the operands cannot be
 // described to TMA (strides, alignment, batch); nothing is launched then.
+// out_peer / n_peer: further full-width C buffers (peer GPUs') that receive every tile at the same
+// position, or null / 0; with peers the launch also requires one matrix, n % 32 == 0 and 16-byte
+// aligned rows.
+constexpr int kMaxPeers = 7;
 vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const float* rhs,
-                           const vx_shapes3& s, bool* eligible);
+                           const vx_shapes3& s, bool* eligible, float* const* out_peer = nullptr,
+                           uint32_t n_peer = 0);
 
 // Streaming GEMV (vx_gemv_stream.cu), one vector.  *eligible = false when the row shape does
 // not fit its shared-memory ring or register-resident x; nothing is launched then.
 // y_peer / n_peer: further buffers that receive every row as well (peer GPUs' y), or null / 0.
-constexpr int kMaxPeers = 7;
 // Arrival flags of the cross-GPU barrier: flags[r] is rank r's array of `world` counters (its
 // own memory for r == this rank, a mapped peer pointer otherwise).
 struct PeerFlags {

@@ -183,6 +183,26 @@ vx_status vx_xvec_unpack(vx_context* ctx, const void* xvec, size_t n, float* out
     return VX_OK;
 }
 
+vx_status vx_gemm_tf32_scatter(vx_context* ctx, float* out, const float* lhs, const float* rhs,
+                               const vx_shapes3* shapes, float* const* peer_out, size_t n_peers) {
+    VX_REQUIRE(ctx && out && lhs && rhs && shapes, VX_ERR_INVALID_ARGUMENT, "vx_gemm_tf32_scatter: null argument");
+    VX_REQUIRE(n_peers <= (size_t)vx::kMaxPeers && (peer_out || n_peers == 0), VX_ERR_INVALID_ARGUMENT,
+               "at most %d peers", vx::kMaxPeers);
+    for (size_t i = 0; i < n_peers; ++i)
+        VX_REQUIRE(peer_out[i], VX_ERR_INVALID_ARGUMENT, "peer buffer %zu is null", i);
+    const vx_shapes3& s = *shapes;
+    VX_REQUIRE(s.out.h == s.lhs.h && s.out.w == s.rhs.w && s.lhs.w == s.rhs.h, VX_ERR_SHAPE,
+               "out %ux%u, lhs %ux%u, rhs %ux%u do not form a product", s.out.h, s.out.w, s.lhs.h, s.lhs.w, s.rhs.h, s.rhs.w);
+    vx::DeviceGuard guard(ctx->device);
+    bool eligible = false;
+    vx_status st = vx::launch_gemm_tf32(ctx, out, lhs, rhs, s, &eligible, peer_out, (uint32_t)n_peers);
+    if (st != VX_OK) return st;
+    VX_REQUIRE(eligible, VX_ERR_UNSUPPORTED,
+               "the panel must be one matrix with unit column strides, 16-byte aligned rows and a width that is a multiple of 32");
+    ctx->last_gemm_kernel = 3;
+    return VX_OK;
+}
+
 vx_status vx_peer_barrier(vx_context* ctx, uint32_t* const* flags, size_t world, size_t rank) {
     VX_REQUIRE(ctx && flags, VX_ERR_INVALID_ARGUMENT, "vx_peer_barrier: null argument");
     VX_REQUIRE(world >= 1 && world <= (size_t)vx::kMaxPeers + 1 && rank < world, VX_ERR_INVALID_ARGUMENT,

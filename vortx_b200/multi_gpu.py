@@ -31,6 +31,26 @@ def shard_blocks(blocks: np.ndarray, rows: int, cols: int, block_bytes: int, wor
     return blocks[row0 * per_row:(row0 + n) * per_row]
 
 
+def col_shard(cols: int, world: int, rank: int, multiple: int = 32) -> Tuple[int, int]:
+    """Contiguous panels of whole `multiple`-column blocks, balanced like row_shard; the last panel also takes
+    the columns beyond the last whole block."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside a world of {world}")
+    blocks = cols // multiple
+    b0, nb = row_shard(blocks, world, rank)
+    col0, ncols = b0 * multiple, nb * multiple
+    if rank == world - 1:
+        ncols = cols - col0
+    return col0, ncols
+
+
+def panel_relayout_shape(m: int, world: int, ncols: int):
+    """(sizes, strides) in elements of the 4-D view that reads a rank-major stack of C panels
+    [world][m][ncols] in the order of the row-major C [m][world * ncols]: element (i, r, j) of the result is
+    element (r, i, j) of the stack."""
+    return (1, m, world, ncols), (world * m * ncols, ncols, m * ncols, 1)
+
+
 class PeerBuffers:
     """One device buffer per rank, each mapped into every other rank's process with CUDA IPC.
 
@@ -173,6 +193,84 @@ class PeerScatterGemv:
         self.flags.close()
         for v in self.vectors:
             v.close()
+
+
+class ShardedGemm:
+    """C[m, n] = A[m, k] B[k, n] (f32 in, TF32 tensor cores, f32 accumulate) with B and C split by columns
+    across the ranks; A is replicated.  The full C ends up on every GPU, either way:
+
+    * `dispatch_peer`: the kernel's epilogue stores every tile into each peer's C as well (NVLink stores,
+      row stride n), then the arrival barrier kernel.
+    * `dispatch_nccl`: the panel goes into a rank-major stack, NCCL all-gathers the stack, and a strided
+      gather kernel (vortx's Contiguous) lays it out as row-major C."""
+
+    def __init__(self, backend, m: int, n: int, k: int, group=None):
+        import ctypes as C
+        import torch.distributed as dist
+        self.backend, self.m, self.n, self.k, self.group = backend, m, n, k, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 GPUs of one node")
+        self.col0, self.ncols = col_shard(n, self.world, self.rank)
+        self.c = PeerBuffers(backend, m * n * 4, group)
+        self.flags = PeerBuffers(backend, 64 * 4, group)
+        self._others = [r for r in range(self.world) if r != self.rank]
+        self._flags_all = (C.c_void_p * self.world)(*self.flags.ptrs)
+        self._peer_c = (C.c_void_p * max(1, len(self._others)))(*[self.c.ptrs[r] + self.col0 * 4 for r in self._others])
+        self._stack = None
+        dist.barrier(group=group)
+
+    def _shapes(self, out_stride: int, b_stride: int):
+        from . import _lib
+        sh = _lib.VxShapes3()
+        for s, (h, w, hs) in ((sh.out, (self.m, self.ncols, out_stride)), (sh.lhs, (self.m, self.k, self.k)),
+                              (sh.rhs, (self.k, self.ncols, b_stride))):
+            s.n = s.c = 1
+            s.h, s.w = h, w
+            s.n_stride = s.c_stride = h * hs
+            s.h_stride, s.w_stride = hs, 1
+        return sh
+
+    def dispatch_peer(self, a_ptr: int, b_panel_ptr: int, b_stride: int) -> None:
+        """a_ptr: A, row-major contiguous.  b_panel_ptr: this rank's columns of B (first element), rows
+        b_stride elements apart.  After the call, stream-ordered, self.c.local holds the whole C."""
+        import ctypes as C
+        from . import _lib
+        sh = self._shapes(self.n, b_stride)
+        _lib.check(_lib.load().vx_gemm_tf32_scatter(self.backend._ctx, self.c.local.ptr + self.col0 * 4, a_ptr,
+                                                    b_panel_ptr, C.byref(sh), self._peer_c, len(self._others)))
+        _lib.check(_lib.load().vx_peer_barrier(self.backend._ctx, self._flags_all, self.world, self.rank))
+
+    def dispatch_nccl(self, a_ptr: int, b_panel_ptr: int, b_stride: int) -> None:
+        """Same result through NCCL; needs equal panels.  The caller's current torch stream must be the
+        backend's stream."""
+        import ctypes as C
+        import torch
+        from . import _lib
+        if self.n % self.world or (self.n // self.world) % 32:
+            raise ValueError("the collective form takes equal panels of whole 32-column blocks")
+        lib = _lib.load()
+        if self._stack is None:
+            self._stack = torch.empty(self.world, self.m, self.ncols, device="cuda", dtype=torch.float32)
+        mine = self._stack[self.rank]
+        sh = self._shapes(self.ncols, b_stride)
+        _lib.check(lib.vx_gemm_f32(self.backend._ctx, _lib.VX_GEMM_TF32, mine.data_ptr(), a_ptr, b_panel_ptr,
+                                   C.byref(sh), 0, 0, 0))
+        self.dist_all_gather(mine)
+        sizes, strides = panel_relayout_shape(self.m, self.world, self.ncols)
+        shape = _lib.VxShape(*sizes, *strides)
+        _lib.check(lib.vx_contiguous(self.backend._ctx, self.c.local.ptr, self.m * self.n, self._stack.data_ptr(),
+                                     C.byref(shape), self._stack.numel(), 0))
+
+    def dist_all_gather(self, mine) -> None:
+        import torch.distributed as dist
+        dist.all_gather_into_tensor(self._stack, mine, group=self.group)
+
+    def close(self) -> None:
+        self.backend.synchronize()
+        self.c.close()
+        self.flags.close()
 
 
 class ShardedGemv:
