@@ -326,24 +326,31 @@ def run_ours(args):
     achieved = list_bytes / (launch_us * 1e-6) / 1e9
 
     note("kernel-only timing done")
-    # End to end through the public API with host buffers: per GEMV, x from pinned host memory,
-    # y back to the host.
-    x_pin = torch.from_numpy(x_host).pin_memory()
-    y_pin = torch.empty(ROWS, dtype=torch.float32).pin_memory()
-    x_stage = torch.empty(COLS, device=dev, dtype=torch.float32)
+    # End to end through the public API with host buffers: the step's 32 x vectors go up from pinned host
+    # memory in one copy, the step runs (each product reads its own x), and the 32 y vectors come back in one
+    # copy.  N > 1: every rank uploads x and reads back the whole y of every product, gathered on the device
+    # (peer stores from the epilogue + the barrier kernel, or NCCL).
+    xs_pin = torch.from_numpy(np.tile(x_host, (LAYERS, 1))).pin_memory()
+    ys_pin = torch.empty(LAYERS, ROWS, dtype=torch.float32).pin_memory()
+    xs_dev = torch.empty(LAYERS, COLS, device=dev, dtype=torch.float32)
+    e2e_batch = vb.GemvBatch(be, [{"w": layers[l], "x": xs_dev[l].data_ptr(), "y": y_full[l].data_ptr() + row0 * 4}
+                                  for l in range(LAYERS)])
 
     def step_e2e():
-        for l in range(LAYERS):
-            _lib.check(lib.vx_upload(be._ctx, x_stage.data_ptr(), x_pin.data_ptr(), COLS * 4))
-            if n > 1 and args.exchange.startswith("peer"):
-                scatter.dispatch(layers[l], x_stage.data_ptr(), l)   # y is read back at once: barrier form
-                src = scatter.y_ptr(l)
-            else:
-                gemv(l, x_stage.data_ptr())
-                if n > 1:
-                    dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
-                src = y_full[l].data_ptr()
-            _lib.check(lib.vx_download(be._ctx, y_pin.data_ptr(), src, ROWS * 4))
+        _lib.check(lib.vx_upload(be._ctx, xs_dev.data_ptr(), xs_pin.data_ptr(), LAYERS * COLS * 4))
+        if n == 1:
+            e2e_batch.launch()
+            src = y_full.data_ptr()
+        elif args.exchange.startswith("peer"):
+            for l in range(LAYERS):
+                scatter.dispatch(layers[l], xs_dev[l].data_ptr(), l)
+            src = scatter.y_ptr(0)
+        else:
+            e2e_batch.launch()
+            for l in range(LAYERS):
+                dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
+            src = y_full.data_ptr()
+        _lib.check(lib.vx_download(be._ctx, ys_pin.data_ptr(), src, LAYERS * ROWS * 4))
 
     for _ in range(2):
         step_e2e()
@@ -386,6 +393,8 @@ def run_ours(args):
             other_ms = float(t.item()) / args.steps
             extra[f"exchange_{other}"] = {"ms_per_step": other_ms, "GB/s": bytes_per_step / (other_ms * 1e-3) / 1e9}
         extra["kernels_only"] = {"us_per_list_launch": launch_us, "GB/s_per_gpu": achieved}
+        note("exchange variants timed")
+        extra["gemm_tf32_8192_col_sharded"] = sharded_gemm_numbers(be, torch, dist, stream, n, rank, barrier)
     cpu = None
     if rank == 0 and n == 1:
         extra = side_configs(be, lib, torch, stream)
@@ -433,6 +442,49 @@ def run_ours(args):
         os._exit(0)
 
 
+def sharded_gemm_numbers(be, torch, dist, stream, world, rank, barrier):
+    """C = A B at 8192^3 with B and C split by columns over the ranks (A replicated), the full C on every GPU:
+    panel compute alone, the peer-store epilogue + barrier kernel, and NCCL all-gather + re-layout.  Device time
+    of `iters` back-to-back products, max over ranks; TFLOP/s counts the whole product's flops."""
+    from vortx_b200.multi_gpu import ShardedGemm
+    import ctypes as C
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    dim, iters = 8192, 5
+    g = ShardedGemm(be, dim, dim, dim)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.rand(dim, dim, device="cuda", generator=gen) * 2 - 1
+    b = torch.rand(dim, g.ncols, device="cuda", generator=gen) * 2 - 1       # this rank's columns of B
+    local_c = torch.empty(dim, dim, device="cuda")
+    sh = g._shapes(dim, g.ncols)
+
+    def compute_only():
+        _lib.check(lib.vx_gemm_f32(be._ctx, _lib.VX_GEMM_TF32, local_c.data_ptr() + g.col0 * 4, a.data_ptr(), b.data_ptr(),
+                                   C.byref(sh), 0, 0, 0))
+
+    forms = {"compute_only": compute_only,
+             "peer_stores": lambda: g.dispatch_peer(a.data_ptr(), b.data_ptr(), g.ncols),
+             "nccl_all_gather": lambda: g.dispatch_nccl(a.data_ptr(), b.data_ptr(), g.ncols)}
+    out = {"m=n=k": dim, "columns_per_gpu": g.ncols, "iters": iters}
+    flops = 2.0 * dim ** 3
+    for name, fn in forms.items():
+        for _ in range(2):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item()) / iters
+        out[name] = {"ms": ms, "TFLOP/s": flops / (ms * 1e-3) / 1e12}
+    g.close()
+    return out
+
+
 def side_configs(be, lib, torch, stream):
     """The other benchmark configurations, each timed briefly (graph replay, rotating weight copies)."""
     import vortx_b200 as vb
@@ -473,6 +525,13 @@ def side_configs(be, lib, torch, stream):
             us = time_graph(fn, copies)
             byts = gemv_bytes(rows, cols, 1, b, qb)
             out[f"{name}_b{b}"] = {"us": us, "GB/s": byts / us / 1e3, "frac_of_measured_hbm": byts / us / 1e3 / peak}
+            if b == 1:
+                # the same products as one list launch over the rotating weight copies
+                batch = vb.GemvBatch(be, [{"w": w, "x": x.data_ptr(), "y": y.data_ptr()} for w in ws])
+                us = time_graph(batch.launch, copies)
+                out[f"{name}_b1_list_of_{copies}"] = {"us_per_gemv": us, "GB/s": byts / us / 1e3,
+                                                      "frac_of_measured_hbm": byts / us / 1e3 / peak}
+                batch.free()
         for w in ws:
             w.free()
 

@@ -54,7 +54,7 @@ def test_dequant_bit_exact(backend, oracle, qt, rows, cols):
 @pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
 @pytest.mark.parametrize("rows,cols,batch", [(1, 32, 1), (7, 96, 1), (33, 1056, 2), (257, 2048, 1),
-                                             (64, 256, 4), (130, 512, 8), (96, 4096, 3)])
+                                             (64, 256, 4), (130, 512, 8), (96, 4096, 3), (40, 512, 11)])
 def test_gemv_small(backend, oracle, qt, rows, cols, batch, variant):
     backend.set_option("gemv.variant", variant)
     w = synth.normal_matrix(rows, cols, seed=11 * rows + cols)

@@ -44,6 +44,7 @@ constexpr int kWarps = kConsumers / 32;
 constexpr int kRedBufs = 4;                // partial-sum buffers between consumers and the epilogue warp
 
 constexpr int kMaxVecs = 8;
+constexpr int kInlineOps = 8;  // GEMVs of a list that travel in the kernel parameters
 
 // One GEMV of the list.
 struct OpParams {
@@ -86,13 +87,13 @@ struct StreamParams {
     uint32_t stages;
     uint32_t stage_bytes;
     uint32_t q_stage_bytes;  // TR * row bytes: where the scales start inside a stage
-    uint32_t n_ops;          // 1: op0; more: ops[] in device memory
+    uint32_t n_ops;          // up to kInlineOps: inline_ops; more: ops[] in device memory
     uint32_t n_vec;
     const OpParams* ops;
     uint32_t* vec_hdr[kMaxVecs];   // headers of the exchange vectors the list touches (own memory)
     uint32_t vec_writes[kMaxVecs]; // how often the list writes each of them
     vx::DeviceStatus* status;
-    OpParams op0;
+    OpParams inline_ops[kInlineOps];
 };
 
 __device__ __forceinline__ void report(vx::DeviceStatus* st, uint32_t code) {
@@ -173,7 +174,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     }
     __syncthreads();
 
-    const OpParams* const ops = p.n_ops > 1 ? p.ops : &p.op0;
+    const OpParams* const ops = p.ops ? p.ops : p.inline_ops;
     const uint32_t row_bytes = p.nchunks * 16;
     const uint32_t wpr = p.tpr >> 5;  // warps per row group
 
@@ -315,7 +316,10 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                             xv[2 * i] = __uint_as_float((uint32_t)a);
                             xv[2 * i + 1] = __uint_as_float((uint32_t)b);
                         }
-                        if (!ok && (*abort_flag != 0u || clock64() - start > kWaitCycles)) break;
+                        if (!ok) {
+                            if (*abort_flag != 0u || clock64() - start > kWaitCycles) break;
+                            __nanosleep(40);  // leave the L2 ports to the stores that are on their way
+                        }
                     }
                     if (!ok) {
                         if (*abort_flag == 0u) report(p.status, 16);
@@ -586,23 +590,28 @@ struct vx_gemv_batch {
 
 namespace vx {
 
-// One vector (batch 1).  *eligible = false (nothing launched) when the row is too long for
-// the shared-memory ring or the register-resident x.
+// `batch` vectors (at most kInlineOps; more than one only without peers or exchange) in one launch:
+// a list whose entries share the weights, so that the later vectors find them in L2 when the
+// matrix fits there.  *eligible = false (nothing launched) when the row is too long for the
+// shared-memory ring or the register-resident x.
 vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
                              const float* x, float* y, float* const* y_peer, uint32_t n_peer,
-                             const Exchange* xch, bool* eligible) {
+                             const Exchange* xch, bool* eligible, uint32_t batch, size_t x_stride,
+                             size_t y_stride) {
     *eligible = false;
     const uint32_t nb = (uint32_t)w->blocks_per_row;
     const uint32_t nchunks = (uint32_t)(w->quant_row_bytes / 16);
     const bool flagged = xch && (xch->x_vec || xch->y_vec);
     StreamConfig c;
-    if (!choose_config(ctx, nchunks, nb, nrows, flagged, &c)) return VX_OK;
+    if (batch < 1 || batch > (uint32_t)kInlineOps || (batch > 1 && (flagged || n_peer))) return VX_OK;
+    if (!choose_config(ctx, nchunks, nb, nrows * batch, flagged, &c)) return VX_OK;
 
     StreamParams p{};
     fill_common(&p, c, nchunks, nb, ctx);
-    p.n_ops = 1;
-    OpParams& o = p.op0;
-    fill_plain_op(&o, w, row0, nrows, x, y, y_peer, n_peer);
+    p.n_ops = batch;
+    OpParams& o = p.inline_ops[0];
+    for (uint32_t v = 0; v < batch; ++v)
+        fill_plain_op(&p.inline_ops[v], w, row0, nrows, x + v * x_stride, y + v * y_stride, y_peer, n_peer);
     if (flagged) {
         // vector table: the written vector first (its header carries the retire counter)
         if (xch->y_vec) {
@@ -728,8 +737,8 @@ vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_
     const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * b->cfg.per_sm);
     b->grid = dim3(std::min(tiles, slots));
     vx::DeviceGuard guard(ctx->device);
-    if (n_ops == 1) {
-        p.op0 = host[0];
+    if (n_ops <= (size_t)kInlineOps) {
+        for (size_t i = 0; i < n_ops; ++i) p.inline_ops[i] = host[i];
     } else {
         VX_CUDA(cudaMalloc(&b->d_ops, n_ops * sizeof(OpParams)));
         const cudaError_t e = cudaMemcpy(b->d_ops, host.data(), n_ops * sizeof(OpParams), cudaMemcpyHostToDevice);

@@ -130,6 +130,7 @@ struct Exchange {
 };
 vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows,
                              const float* x, float* y, float* const* y_peer, uint32_t n_peer,
-                             const Exchange* xch, bool* eligible);
+                             const Exchange* xch, bool* eligible, uint32_t batch = 1, size_t x_stride = 0,
+                             size_t y_stride = 0);
 
 }  // namespace vx

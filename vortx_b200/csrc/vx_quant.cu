@@ -576,17 +576,21 @@ vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t row0, siz
                w->cols, nrows);
     vx::DeviceGuard guard(ctx->device);
 
-    // Default: the TMA-fed streaming kernel, one launch per vector (weights of the later
-    // vectors come out of L2 when the matrix fits there).  "gemv.variant" 0 / 1 select the
-    // register-staged kernels below, which also take over when a row does not fit the ring.
+    // Default: the TMA-fed streaming kernel, up to eight vectors per launch (a list whose entries
+    // share the weights: the later vectors find them in L2 when the matrix fits there).
+    // "gemv.variant" 0 / 1 select the register-staged kernels below, which also take over when a
+    // row does not fit the ring.
     if (vx::option(ctx, "gemv.variant", 2) == 2) {
         size_t v = 0;
-        for (; v < batch; ++v) {
+        while (v < batch) {
+            const uint32_t take = (uint32_t)std::min<size_t>(8, batch - v);
             bool eligible = false;
             vx_status st = vx::launch_gemv_stream(ctx, w, row0, (uint32_t)nrows, x + v * x_stride,
-                                                  y + v * y_stride, nullptr, 0, nullptr, &eligible);
+                                                  y + v * y_stride, nullptr, 0, nullptr, &eligible, take, x_stride,
+                                                  y_stride);
             if (st != VX_OK) return st;
             if (!eligible) break;
+            v += take;
         }
         if (v == batch) return VX_OK;
         x += v * x_stride;
