@@ -137,7 +137,7 @@ __device__ __forceinline__ uint32_t first_tile(uint32_t op, uint32_t tiles) {
 // XCH: reads a flagged x and / or writes flagged pairs (the cross-GPU exchange); a template
 // switch so that the plain kernel keeps its register count (two CTAs per SM need <= 102).
 template <int QT, int CPT, int RP, int TR, bool XCH>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, (XCH && CPT == 1) ? 2 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int W = QT == 1 ? 32 : 16;
     constexpr int DR = W / 4;   // registers per digit plane per chunk
@@ -528,7 +528,7 @@ bool choose_config(vx_context* ctx, uint32_t nchunks, uint32_t nb, uint32_t max_
     // prefetch its first tiles while this one is still running.
     int64_t per_sm = option(ctx, "gemv.ctas_per_sm", 0);
     if (per_sm <= 0) per_sm = tiles >= 16u * (uint32_t)ctx->sm_count ? 2 : 1;
-    if (flagged) per_sm = 1;  // the flagged kernel's registers allow one CTA per SM
+    if (flagged && (c->cpt != 1 || option(ctx, "gemv.flagged_ctas_per_sm", 1) < 2)) per_sm = 1;
     per_sm = std::min<int64_t>(per_sm, 4);
     const size_t budget = (size_t)(200 * 1024) / (size_t)per_sm - fixed;
     int64_t want_stages = option(ctx, "gemv.stages", 0);
