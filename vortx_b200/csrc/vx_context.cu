@@ -33,7 +33,6 @@ static const char* const kKnownOptions[] = {
     "gemv.rows_per_warp", // rows a warp carries at once
     "gemv.block_threads", // CTA size of the GEMV kernels
     "gemv.ctas_per_sm",   // persistent grid = SMs x this
-    "gemv.flagged_ctas_per_sm",  // 2 lets the flagged (exchange) kernel run two CTAs per SM; default 1
     "gemm.simt.force_generic",  // 1: always take the generic-stride SIMT kernel
     "gemm.tf32.stages",   // TMA pipeline depth
     "gemm.tf32.raster",   // tile rasterisation group height

@@ -38,9 +38,7 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kConsumers = 256;
-constexpr int kThreads = kConsumers + 64;  // + producer warp + epilogue warp
-constexpr int kWarps = kConsumers / 32;
+constexpr int kConsumers = 256;            // consumer threads of a CTA (8 warps)
 constexpr int kRedBufs = 4;                // partial-sum buffers between consumers and the epilogue warp
 
 constexpr int kMaxVecs = 8;
@@ -136,9 +134,14 @@ __device__ __forceinline__ uint32_t first_tile(uint32_t op, uint32_t tiles) {
 // CPT: chunk positions per thread.  RP: row groups working side by side.  TR: rows per tile.
 // XCH: reads a flagged x and / or writes flagged pairs (the cross-GPU exchange); a template
 // switch so that the plain kernel keeps its register count (two CTAs per SM need <= 102).
-template <int QT, int CPT, int RP, int TR, bool XCH>
-__global__ void __launch_bounds__(kThreads, (XCH && CPT == 1) ? 2 : 1)
+// NCW: consumer warps, 8 everywhere.  (The plain kernel gets 16 warps per SM from two CTAs.  A flagged
+// CTA of 16 consumer warps, x held twice, measured slower than 8: 17.9 against 15.2 us per chained
+// 14336 x 8192 product.)
+template <int QT, int CPT, int RP, int TR, bool XCH, int NCW>
+__global__ void __launch_bounds__(NCW * 32 + 64, 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+    constexpr int kWarps = NCW;
+    constexpr int kConsumers = NCW * 32;  // then one producer warp and one epilogue warp
     constexpr int W = QT == 1 ? 32 : 16;
     constexpr int DR = W / 4;   // registers per digit plane per chunk
     constexpr int NR = TR / RP; // rows per thread per tile
@@ -308,13 +311,22 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                     bool ok = false;
                     while (!ok) {
                         ok = true;
+                        // 16 values (eight 16-byte loads) at a time: the temporaries of the loads are what
+                        // sets the kernel's register count
 #pragma unroll
-                        for (int i = 0; i < W / 2; ++i) {
-                            uint64_t a, b;
-                            ld_volatile_v2_u64(src + 2 * i, a, b);
-                            ok = ok && (uint32_t)(a >> 32) == x_gen && (uint32_t)(b >> 32) == x_gen;
-                            xv[2 * i] = __uint_as_float((uint32_t)a);
-                            xv[2 * i + 1] = __uint_as_float((uint32_t)b);
+                        for (int h = 0; h < W / 16; ++h) {
+                            uint64_t v[16];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) ld_volatile_v2_u64(src + 16 * h + 2 * i, v[2 * i], v[2 * i + 1]);
+                            uint32_t good = 1;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                good &= (uint32_t)(v[i] >> 32) == x_gen ? 1u : 0u;
+                                xv[16 * h + i] = __uint_as_float((uint32_t)v[i]);
+                            }
+                            // pins this group's values before the next group's loads are issued
+                            asm volatile("" : "+r"(good) : "f"(xv[16 * h]), "f"(xv[16 * h + 5]), "f"(xv[16 * h + 10]), "f"(xv[16 * h + 15]));
+                            ok = ok && good != 0;
                         }
                         if (!ok) {
                             if (*abort_flag != 0u || clock64() - start > kWaitCycles) break;
@@ -450,9 +462,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     }
 }
 
-template <int QT, int CPT, int RP, int TR, bool XCH>
+template <int QT, int CPT, int RP, int TR, bool XCH, int NCW = 8>
 vx_status launch_one(vx_context* ctx, const StreamParams& p, dim3 grid, size_t smem) {
-    auto kernel = gemv_stream_kernel<QT, CPT, RP, TR, XCH>;
+    auto kernel = gemv_stream_kernel<QT, CPT, RP, TR, XCH, NCW>;
     // Raise the dynamic shared-memory limit once per device and kernel instance.
     static size_t granted[64] = {};
     const int dev = ctx->device & 63;
@@ -462,7 +474,7 @@ vx_status launch_one(vx_context* ctx, const StreamParams& p, dim3 grid, size_t s
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(NCW * 32 + 64);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -475,7 +487,8 @@ vx_status launch_one(vx_context* ctx, const StreamParams& p, dim3 grid, size_t s
 }
 
 template <int QT, int TR, bool XCH>
-vx_status launch_qt(vx_context* ctx, int cpt, int rp, const StreamParams& p, dim3 grid, size_t smem) {
+vx_status launch_qt(vx_context* ctx, int cpt, int rp, int ncw, const StreamParams& p, dim3 grid, size_t smem) {
+    (void)ncw;
     if (cpt == 1) {
         switch (rp) {
             case 1: return launch_one<QT, 1, 1, TR, XCH>(ctx, p, grid, smem);
@@ -487,20 +500,23 @@ vx_status launch_qt(vx_context* ctx, int cpt, int rp, const StreamParams& p, dim
     return launch_one<QT, 4, 1, TR, XCH>(ctx, p, grid, smem);
 }
 
-template <bool XCH>
-vx_status launch_tr(vx_context* ctx, int qtype, uint32_t tr, int cpt, int rp, const StreamParams& p, dim3 grid, size_t smem) {
-    if (tr == 8)
-        return qtype == VX_Q4_0 ? launch_qt<1, 8, XCH>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 8, XCH>(ctx, cpt, rp, p, grid, smem);
-    return qtype == VX_Q4_0 ? launch_qt<1, 4, XCH>(ctx, cpt, rp, p, grid, smem) : launch_qt<0, 4, XCH>(ctx, cpt, rp, p, grid, smem);
-}
-
 // How one row shape maps onto the kernel.
 struct StreamConfig {
     uint32_t tr, tpr, stages, stage_bytes, q_stage;
-    int cpt, rp;
+    int cpt, rp, ncw;
     int64_t per_sm;
     size_t smem;
 };
+
+template <bool XCH>
+vx_status launch_tr(vx_context* ctx, int qtype, const StreamConfig& c, const StreamParams& p, dim3 grid) {
+    if (c.tr == 8)
+        return qtype == VX_Q4_0 ? launch_qt<1, 8, XCH>(ctx, c.cpt, c.rp, c.ncw, p, grid, c.smem)
+                                : launch_qt<0, 8, XCH>(ctx, c.cpt, c.rp, c.ncw, p, grid, c.smem);
+    return qtype == VX_Q4_0 ? launch_qt<1, 4, XCH>(ctx, c.cpt, c.rp, c.ncw, p, grid, c.smem)
+                            : launch_qt<0, 4, XCH>(ctx, c.cpt, c.rp, c.ncw, p, grid, c.smem);
+}
+
 
 // false: the row is too long for the shared-memory ring or the register-resident x.
 bool choose_config(vx_context* ctx, uint32_t nchunks, uint32_t nb, uint32_t max_tiles_hint_rows, bool flagged,
@@ -512,14 +528,15 @@ bool choose_config(vx_context* ctx, uint32_t nchunks, uint32_t nb, uint32_t max_
     uint32_t tpr = ((nchunks + c->cpt - 1) / c->cpt + 31) / 32 * 32;
     c->tpr = std::min<uint32_t>(tpr, kConsumers);
     c->rp = 1;
+    c->ncw = 8;
     if (c->cpt == 1) {
-        const uint32_t fit = kConsumers / c->tpr;  // 1..8
+        const uint32_t fit = (uint32_t)c->ncw * 32 / c->tpr;  // 1..16
         c->rp = fit >= 4 ? 4 : fit >= 2 ? 2 : 1;
     }
     c->q_stage = c->tr * nchunks * 16;
     const uint32_t s_stage = (c->tr * nb * 2 + 32 + 15) / 16 * 16;
     c->stage_bytes = (c->q_stage + s_stage + 127) / 128 * 128;
-    const size_t fixed = kRedBufs * c->tr * kWarps * sizeof(float) + (2 * 16 + 2 * kRedBufs + 1) * sizeof(uint64_t);
+    const size_t fixed = kRedBufs * c->tr * c->ncw * sizeof(float) + (2 * 16 + 2 * kRedBufs + 1) * sizeof(uint64_t);
     const uint32_t tiles = (max_tiles_hint_rows + c->tr - 1) / c->tr;
     // Measured on B200: two CTAs per SM pay off once every CTA slot streams many tiles; short
     // launches do better with one CTA per SM, which also balances their few tiles better.  The
@@ -528,7 +545,9 @@ bool choose_config(vx_context* ctx, uint32_t nchunks, uint32_t nb, uint32_t max_
     // prefetch its first tiles while this one is still running.
     int64_t per_sm = option(ctx, "gemv.ctas_per_sm", 0);
     if (per_sm <= 0) per_sm = tiles >= 16u * (uint32_t)ctx->sm_count ? 2 : 1;
-    if (flagged && (c->cpt != 1 || option(ctx, "gemv.flagged_ctas_per_sm", 1) < 2)) per_sm = 1;
+    // The flagged kernel needs 128 registers: one CTA per SM.  (Capped at 102 for two CTAs per SM it spills
+    // in the main loop and a chained product measured 20.8 us instead of 15.3 us.)
+    if (flagged) per_sm = 1;
     per_sm = std::min<int64_t>(per_sm, 4);
     const size_t budget = (size_t)(200 * 1024) / (size_t)per_sm - fixed;
     int64_t want_stages = option(ctx, "gemv.stages", 0);
@@ -640,8 +659,7 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
     const uint32_t tiles = (nrows + c.tr - 1) / c.tr;
     const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * c.per_sm);
     dim3 grid(std::min(tiles, slots));
-    const vx_status st = flagged ? launch_tr<true>(ctx, w->type, c.tr, c.cpt, c.rp, p, grid, c.smem)
-                                 : launch_tr<false>(ctx, w->type, c.tr, c.cpt, c.rp, p, grid, c.smem);
+    const vx_status st = flagged ? launch_tr<true>(ctx, w->type, c, p, grid) : launch_tr<false>(ctx, w->type, c, p, grid);
     if (st != VX_OK) return st;
     ctx->launches++;
     ctx->status_dirty = true;
@@ -760,8 +778,7 @@ vx_status vx_gemv_batch_launch(vx_context* ctx, const vx_gemv_batch* b) {
     StreamParams p = b->params;
     p.status = ctx->d_status;
     const StreamConfig& c = b->cfg;
-    const vx_status st = b->flagged ? launch_tr<true>(ctx, b->qtype, c.tr, c.cpt, c.rp, p, b->grid, c.smem)
-                                    : launch_tr<false>(ctx, b->qtype, c.tr, c.cpt, c.rp, p, b->grid, c.smem);
+    const vx_status st = b->flagged ? launch_tr<true>(ctx, b->qtype, c, p, b->grid) : launch_tr<false>(ctx, b->qtype, c, p, b->grid);
     if (st != VX_OK) return st;
     ctx->launches++;
     ctx->status_dirty = true;
