@@ -329,12 +329,14 @@ def run_ours(args):
     # End to end through the public API with host buffers: the step's 32 x vectors go up from pinned host
     # memory in one copy, the step runs (each product reads its own x), and the 32 y vectors come back in one
     # copy.  N > 1: every rank uploads x and reads back the whole y of every product, gathered on the device
-    # (peer stores from the epilogue + the barrier kernel, or NCCL).
+    # (one list launch whose epilogue stores the rows on every GPU + one barrier kernel; or NCCL).
     xs_pin = torch.from_numpy(np.tile(x_host, (LAYERS, 1))).pin_memory()
     ys_pin = torch.empty(LAYERS, ROWS, dtype=torch.float32).pin_memory()
     xs_dev = torch.empty(LAYERS, COLS, device=dev, dtype=torch.float32)
     e2e_batch = vb.GemvBatch(be, [{"w": layers[l], "x": xs_dev[l].data_ptr(), "y": y_full[l].data_ptr() + row0 * 4}
                                   for l in range(LAYERS)])
+
+    e2e_scatter = scatter.scatter_batch(layers, [xs_dev[l].data_ptr() for l in range(LAYERS)]) if n > 1 else None
 
     def step_e2e():
         _lib.check(lib.vx_upload(be._ctx, xs_dev.data_ptr(), xs_pin.data_ptr(), LAYERS * COLS * 4))
@@ -342,8 +344,8 @@ def run_ours(args):
             e2e_batch.launch()
             src = y_full.data_ptr()
         elif args.exchange.startswith("peer"):
-            for l in range(LAYERS):
-                scatter.dispatch(layers[l], xs_dev[l].data_ptr(), l)
+            e2e_scatter.launch()      # rows of all 32 products stored here and on every peer ...
+            scatter.finish()          # ... and one arrival barrier for the step
             src = scatter.y_ptr(0)
         else:
             e2e_batch.launch()

@@ -215,6 +215,9 @@ typedef struct {
     void* const* peer_y_xvec;   /* the same vector of every peer (n_peers entries)  */
     size_t n_peers;
     size_t y_row0, y_stride;    /* row r goes to element y_row0 + r * y_stride      */
+    float* const* peer_y;       /* plain rows also stored here (n_peer_y buffers, as for
+                                   vx_gemv_q_rows_scatter), or NULL                 */
+    size_t n_peer_y;
 } vx_gemv_op;
 VX_API vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_ops,
                                       vx_gemv_batch** out);

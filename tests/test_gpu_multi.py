@@ -56,6 +56,20 @@ def _worker(rank, world, port, out_dir):
         be.slow_read_buffer(g.y.local, y.view(np.uint8))
         results[f"{name}_peer"] = y.reshape(slots, rows)
         dist.barrier()
+        # the same products as one list launch with plain peer rows and a single barrier
+        lib = vb.load()
+        vb._lib.check(lib.vx_memset(be._ctx, g.y.local.ptr, 0xFF, slots * rows * 4))
+        be.synchronize()
+        dist.barrier()
+        batch = g.scatter_batch([qm] * slots, [xd.ptr + s * cols * 4 for s in range(slots)])
+        batch.launch()
+        g.finish()
+        be.synchronize()
+        y2 = np.empty(slots * rows, np.float32)
+        be.slow_read_buffer(g.y.local, y2.view(np.uint8))
+        results[f"{name}_peer_list"] = y2.reshape(slots, rows)
+        batch.free()
+        dist.barrier()
         g.close()
         # NCCL form through torch tensors on the same stream
         sg = ShardedGemv.for_backend(be, qt, mine, rows, cols)
@@ -213,6 +227,7 @@ def test_peer_scatter_and_nccl_gemv_on_two_gpus(tmp_path, oracle):
             assert np.abs(peer - y64).max() / np.abs(y64).max() <= 1e-4
             assert (np.abs(peer - y64) <= 2e-6 * absdot).all()
             assert np.array_equal(nccl[0].view(np.uint32), peer[0].view(np.uint32))   # same kernel, same rows
+            assert np.array_equal(got[f"{name}_peer_list"].view(np.uint32), peer.view(np.uint32))
 
 
 def _gemm_worker(rank, world, port, out_dir):

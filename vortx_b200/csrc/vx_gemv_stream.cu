@@ -713,7 +713,11 @@ vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_
         VX_REQUIRE((reinterpret_cast<uintptr_t>(g.x_xvec) & 15u) == 0 && (reinterpret_cast<uintptr_t>(g.y_xvec) & 15u) == 0,
                    VX_ERR_INVALID_ARGUMENT, "GEMV %zu: exchange vectors are 16-byte aligned", i);
         OpParams& o = host[i];
-        fill_plain_op(&o, g.w, g.row0, (uint32_t)g.nrows, g.x_xvec ? nullptr : g.x, g.y, nullptr, 0);
+        VX_REQUIRE(g.n_peer_y <= (size_t)vx::kMaxPeers && (g.n_peer_y == 0 || (g.peer_y && g.y)), VX_ERR_INVALID_ARGUMENT,
+                   "GEMV %zu: plain peer rows need y and at most %d buffers", i, vx::kMaxPeers);
+        for (size_t d = 0; d < g.n_peer_y; ++d)
+            VX_REQUIRE(g.peer_y[d], VX_ERR_INVALID_ARGUMENT, "GEMV %zu: peer buffer %zu is null", i, d);
+        fill_plain_op(&o, g.w, g.row0, (uint32_t)g.nrows, g.x_xvec ? nullptr : g.x, g.y, g.peer_y, (uint32_t)g.n_peer_y);
         if (g.x_xvec) {
             const int32_t v = vec_index(g.x_xvec);
             VX_REQUIRE(v >= 0, VX_ERR_UNSUPPORTED, "more than %d exchange vectors", kMaxVecs);

@@ -263,7 +263,7 @@ class GemvBatch:
 
     Each entry is a dict: w (QuantizedMatrix), and optionally row0, nrows, x (plain device pointer), x_xvec
     (exchange vector to read x from), y (plain rows), y_xvec (exchange vector to write), peers (the same
-    vector on the peer GPUs), y_row0, y_stride.  Entries may depend on each other only through exchange
+    vector on the peer GPUs), y_row0, y_stride, peer_y (peer buffers that receive the plain rows as well).  Entries may depend on each other only through exchange
     vectors.  Pointers are captured at construction."""
 
     def __init__(self, backend: Backend, entries):
@@ -277,7 +277,11 @@ class GemvBatch:
             nrows = e.get("nrows")
             peers = list(e.get("peers") or [])
             pa = (C.c_void_p * max(1, len(peers)))(*peers)
-            self._keep.append((w, pa))
+            plain = list(e.get("peer_y") or [])
+            pp = (C.c_void_p * max(1, len(plain)))(*plain)
+            self._keep.append((w, pa, pp))
+            arr[i].peer_y = pp
+            arr[i].n_peer_y = len(plain)
             arr[i].w = w._h
             arr[i].row0 = row0
             arr[i].nrows = w.rows - row0 if nrows is None else nrows

@@ -159,6 +159,19 @@ class PeerScatterGemv:
                                                self.vectors[y_vec].local.ptr, self._vec_peers[y_vec],
                                                len(self._others), self.row0, self.world if self.cyclic else 1))
 
+    def scatter_batch(self, weights_list, x_ptrs):
+        """Independent products as ONE persistent launch per GPU: product l reads the plain x_ptrs[l] and stores
+        its rows into y[l] here and on every peer.  After `launch()`, one `finish()` completes all of them."""
+        from .linalg import GemvBatch
+        if self.cyclic:
+            raise ValueError("plain peer rows take contiguous slabs")
+        entries = []
+        for l, w in enumerate(weights_list):
+            off = (l * self.rows + self.row0) * 4
+            entries.append({"w": w, "nrows": self.nrows, "x": x_ptrs[l], "y": self.y.local.ptr + off,
+                            "peer_y": [self.y.ptrs[r] + off for r in self._others]})
+        return GemvBatch(self.backend, entries)
+
     def chain_batch(self, weights_list, x_ptr: int):
         """The whole chain as ONE persistent launch per GPU (GemvBatch): link 0 reads the plain x, link l reads
         exchange vector (l - 1) % 2 and writes l % 2.  Returns the batch; after `launch()`, `unpack((len - 1) % 2, ...)`
