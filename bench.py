@@ -464,8 +464,14 @@ def sharded_gemm_numbers(be, torch, dist, stream, world, rank, barrier):
         _lib.check(lib.vx_gemm_f32(be._ctx, _lib.VX_GEMM_TF32, local_c.data_ptr() + g.col0 * 4, a.data_ptr(), b.data_ptr(),
                                    C.byref(sh), 0, 0, 0))
 
+    def peer_tile128():
+        be.set_option("gemm.tf32.tile_m", 128)      # two accumulator stages: the peer stores run under the next tile's MMAs
+        g.dispatch_peer(a.data_ptr(), b.data_ptr(), g.ncols)
+        be.set_option("gemm.tf32.tile_m", 0)
+
     forms = {"compute_only": compute_only,
              "peer_stores": lambda: g.dispatch_peer(a.data_ptr(), b.data_ptr(), g.ncols),
+             "peer_stores_tile128": peer_tile128,
              "nccl_all_gather": lambda: g.dispatch_nccl(a.data_ptr(), b.data_ptr(), g.ncols)}
     out = {"m=n=k": dim, "columns_per_gpu": g.ncols, "iters": iters}
     flops = 2.0 * dim ** 3
