@@ -225,11 +225,12 @@ VX_API vx_status vx_gemv_batch_launch(vx_context* ctx, const vx_gemv_batch* batc
 VX_API vx_status vx_gemv_batch_free(vx_context* ctx, vx_gemv_batch* batch);
 /* Column-sharded GEMM: this rank's panel of C = A * B (out, lhs, rhs and shapes as for vx_gemm_f32
  * with VX_GEMM_TF32; out already advanced to the panel's first column, its row stride the full
- * width of C) computed by the tensor-core kernel, whose epilogue stores every tile at the same
- * position of each peer's C as well (128-byte segments over NVLink; nothing is loaded from a
- * peer).  vx_peer_barrier afterwards tells every rank that all panels have landed.  One matrix,
- * unit column strides, 16-byte aligned rows and a panel width that is a multiple of 32; anything
- * else is VX_ERR_UNSUPPORTED (no fallback here, the caller picks the collective form). */
+ * width of C) computed by the tensor-core kernel, whose epilogue sends every 32 x 32 block of the
+ * panel with tiled TMA stores to this GPU's C and to the same position of each peer's C (whole
+ * 128-byte rows over NVLink, asynchronous to the tensor cores; nothing is loaded from a peer).
+ * vx_peer_barrier afterwards tells every rank that all panels have landed.  One matrix, unit column
+ * strides, 16-byte aligned bases and row pitches; anything else is VX_ERR_UNSUPPORTED (no fallback
+ * here, the caller picks the collective form). */
 VX_API vx_status vx_gemm_tf32_scatter(vx_context* ctx, float* out, const float* lhs, const float* rhs,
                                       const vx_shapes3* shapes, float* const* peer_out, size_t n_peers);
 /* flags[r] (r < world <= 8) is rank r's sync block of 64 u32, zero-initialised: its own for

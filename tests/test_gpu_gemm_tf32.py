@@ -103,3 +103,39 @@ def test_tf32_4096_against_simt(backend, tile_m):
     assert kern == "tcgen05_tf32"
     ref, _ = _gemm(backend, "dispatch_tiled", A, B)
     assert _rel_fro(got, ref) <= TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 200), (129, 72, 40), (1024, 2048, 512)])
+def test_tf32_scatter_epilogue_writes_every_destination(backend, m, n, k):
+    """vx_gemm_tf32_scatter with two further buffers of the SAME GPU standing in for peers: the epilogue's tiled TMA
+    stores must put the bits of the plain tensor-core GEMM into all three, clipped at ragged edges, and nothing
+    outside the panel (the panel sits inside a wider C)."""
+    import ctypes as C
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.Generator(np.random.Philox(m * 7 + n))
+    a = rng.random((m, k), dtype=np.float32) * 2 - 1
+    b = rng.random((k, n), dtype=np.float32) * 2 - 1
+    ad, bd = backend.init_buffer(a.ravel()), backend.init_buffer(b.ravel())
+    ldc, col0 = n + 24, 8                                    # panel inside a wider C: 16-byte aligned pitch and base
+    canary = np.full(m * ldc, np.float32(-7.5))
+    outs = [backend.init_buffer(canary) for _ in range(3)]
+    ref = backend.init_buffer(canary)
+    sh = _lib.VxShapes3()
+    for s, (h, w, hs) in ((sh.out, (m, n, ldc)), (sh.lhs, (m, k, k)), (sh.rhs, (k, n, n))):
+        s.n = s.c = 1
+        s.h, s.w = h, w
+        s.n_stride = s.c_stride = h * hs
+        s.h_stride, s.w_stride = hs, 1
+    _lib.check(lib.vx_gemm_f32(backend._ctx, _lib.VX_GEMM_TF32, ref.ptr + col0 * 4, ad.ptr, bd.ptr, C.byref(sh), 0, 0, 0))
+    assert vb.Gemm.last_kernel(backend) == "tcgen05_tf32"
+    peers = (C.c_void_p * 2)(outs[1].ptr + col0 * 4, outs[2].ptr + col0 * 4)
+    _lib.check(lib.vx_gemm_tf32_scatter(backend._ctx, outs[0].ptr + col0 * 4, ad.ptr, bd.ptr, C.byref(sh), peers, 2))
+    want = np.empty(m * ldc, np.float32)
+    backend.slow_read_buffer(ref, want)
+    w2 = want.reshape(m, ldc)
+    assert (w2[:, :col0] == -7.5).all() and (w2[:, col0 + n:] == -7.5).all()
+    for o in outs:
+        got = np.empty(m * ldc, np.float32)
+        backend.slow_read_buffer(o, got)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

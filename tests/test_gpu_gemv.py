@@ -128,8 +128,6 @@ def test_exchange_chain_on_one_gpu_matches_plain_chain(backend, qt, n):
     peers: a chain of square products ends on the same bits as the same chain through plain vectors."""
     from vortx_b200 import _lib
     lib = _lib.load()
-    if qt == vb.Q8_0 and n > 8192:
-        pytest.skip("a Q8_0 row of 16384 columns does not fit the streaming kernel's shared-memory ring")
     links = 5
     w = synth.normal_matrix(n, n, seed=n + 5) * np.float32(50.0 / np.sqrt(n))
     blocks = vb.quantize(qt, w)
@@ -173,8 +171,6 @@ def test_exchange_chain_on_one_gpu_matches_plain_chain(backend, qt, n):
 def test_batch_of_independent_gemvs_matches_single_launches(backend, qt, rows, cols, count):
     """One persistent launch over a list of products (different weights, row counts and x) gives the bits the
     products give when launched one by one."""
-    if qt == vb.Q8_0 and cols > 8192:
-        pytest.skip("a Q8_0 row of 16384 columns does not fit the streaming kernel's shared-memory ring")
     ws, entries, singles = [], [], []
     xs = synth.normal_vectors(2, cols, seed=cols)
     xd = backend.init_buffer(xs.ravel())
@@ -235,3 +231,14 @@ def test_batch_chain_through_exchange_vectors_on_one_gpu(backend, qt, n):
         backend.slow_read_buffer(out, got)
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     batch.free()
+
+
+@pytest.mark.parametrize("qt,rows,cols", [(vb.Q4_0, 40, 28672), (vb.Q4_0, 19, 32768), (vb.Q8_0, 33, 14336),
+                                          (vb.Q8_0, 12, 16384)])
+def test_gemv_long_rows(backend, oracle, qt, rows, cols):
+    """Rows too long for two 8-row stages stream in tiles of 4 rows (the down-projection shape, 28672 columns)."""
+    w = synth.normal_matrix(rows, cols, seed=rows + cols)
+    x = synth.normal_vectors(2, cols, seed=rows)
+    blocks = oracle.quantize(qt, w)
+    y64, absdot = oracle.gemv_f64(qt, blocks, rows, cols, x)
+    _check(_run(backend, qt, blocks, rows, cols, x), y64, absdot)

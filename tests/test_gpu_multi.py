@@ -250,7 +250,8 @@ def _gemm_worker(rank, world, port, out_dir):
         b = rng.random((k, n), dtype=np.float32) * 2 - 1
         ad, bd = be.init_buffer(a.ravel()), be.init_buffer(b.ravel())   # B whole on every rank; each uses its columns
         g = ShardedGemm(be, m, n, k)
-        for form in ("peer", "nccl"):
+        even = n % world == 0 and (n // world) % 32 == 0
+        for form in ("peer", "nccl") if even else ("peer",):
             for rep in range(2):
                 with torch.cuda.stream(stream):
                     if form == "peer":
@@ -269,7 +270,7 @@ def _gemm_worker(rank, world, port, out_dir):
     os._exit(0)
 
 
-GEMM_CASES = [(512, 512, 256), (300, 1024, 200), (1024, 2048, 1024)]
+GEMM_CASES = [(512, 512, 256), (300, 1024, 200), (1024, 2048, 1024), (200, 1000, 96), (129, 72, 40)]
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
@@ -284,8 +285,9 @@ def test_column_sharded_tf32_gemm_on_two_gpus(tmp_path):
         want = a.astype(np.float64) @ b.astype(np.float64)
         key = f"{m}_{n}_{k}"
         for r in range(world):
-            peer, nccl = got[r][f"peer_{key}"], got[r][f"nccl_{key}"]
+            peer = got[r][f"peer_{key}"]
             rel = np.linalg.norm(peer - want) / np.linalg.norm(want)
             assert rel <= 5e-3, (key, r, rel)                       # TF32 inputs, f32 accumulate
-            assert np.array_equal(peer.view(np.uint32), nccl.view(np.uint32))          # same kernel, same tiles
+            if f"nccl_{key}" in got[r]:                             # equal panels only
+                assert np.array_equal(peer.view(np.uint32), got[r][f"nccl_{key}"].view(np.uint32))   # same kernel, same tiles
             assert np.array_equal(peer.view(np.uint32), got[0][f"peer_{key}"].view(np.uint32))   # one C everywhere

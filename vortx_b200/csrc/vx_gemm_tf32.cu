@@ -71,12 +71,15 @@ struct Tf32Params {
     vx::DeviceStatus* status;
 };
 
-// Per epilogue warp: a 32 x 32 block of C turned from "one row per lane" (how tensor memory
-// hands it out) into rows of 128 contiguous bytes, so that stores to a peer leave as full
-// 128-byte segments instead of 16-byte pieces.  Rows padded to 36 floats: 16-byte aligned and
-// conflict-free for 128-bit accesses.
-constexpr int kXposeStride = 36;
-constexpr uint32_t kXposeBytes = 4 * 32 * kXposeStride * 4;  // four epilogue warps
+// With peers, each epilogue warp stages a 32 x 32 block of C (one row per lane, as tensor memory hands it
+// out) in shared memory in the 128-byte-swizzled box layout and one lane sends it with tiled TMA stores to
+// this GPU's C and to every peer's: the copies run asynchronously (the warp goes on to the next block, two
+// staging buffers per warp) and leave as whole 128-byte rows over NVLink.
+constexpr uint32_t kStageBoxBytes = 32 * 32 * 4;                 // 4 KB
+constexpr uint32_t kXposeBytes = 4 * 2 * kStageBoxBytes;         // four epilogue warps, two buffers each
+struct PeerMaps {
+    CUtensorMap c[vx::kMaxPeers + 1];  // [0] this GPU's panel of C, then the peers'
+};
 
 struct SharedTail {
     uint64_t full[kMaxStages];
@@ -113,7 +116,7 @@ constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1
 template <int HALVES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ Tf32Params p) {
+                 const __grid_constant__ Tf32Params p, const __grid_constant__ PeerMaps maps_c) {
     using C = Cfg<HALVES>;
     constexpr int kStages = C::kStages, kAccStages = C::kAccStages;
     constexpr uint32_t kStageBytes = C::kStageBytes, kABytes = C::kABytes;
@@ -122,7 +125,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // The ring must start on a 1024-byte boundary (128-byte swizzle repeats every 8 rows).
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     SharedTail* tail = reinterpret_cast<SharedTail*>(smem + kStages * kStageBytes);
-    float* xpose_all = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256);  // used with peers only
+    uint8_t* stage_all = smem + kStages * kStageBytes + 1024;  // used with peers only; 1024-byte aligned
     volatile uint32_t* abort_flag = &tail->abort_flag;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -219,7 +222,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else {
         // --------------------------------------------------------------------- epilogue ----
         const uint32_t quad = warp & 3;  // a warp may only touch tensor-memory lanes 32*(warp%4) ..
-        uint32_t tile_it = 0;
+        uint32_t tile_it = 0, chunk_it = 0;
         for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_it) {
             uint32_t tm, tn;
             tile_coords(p, t, tm, tn);
@@ -240,28 +243,31 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     tmem_ld_wait();
                     const uint32_t col = col0 + c * 32;
                     if (p.n_peer > 0) {
-                        // (the host only takes this path with 16-byte aligned rows and n % 32 == 0)
-                        float* xp = xpose_all + quad * 32 * kXposeStride;
-                        float4* mine = reinterpret_cast<float4*>(xp + lane * kXposeStride);
+                        // (the host only takes this path when TMA can describe every C: 16-byte aligned bases and
+                        // row pitches)
+                        const uint32_t use = chunk_it++;
+                        uint8_t* box = stage_all + (quad * 2 + (use & 1)) * kStageBoxBytes;
+                        // the copies that last read this buffer (two blocks ago) must have read it
+                        if (lane == 0) bulk_wait_group_read<1>();
+                        __syncwarp();
+                        // 128-byte swizzle: 16-byte unit j of row r sits at position j ^ (r & 7)
+                        uint8_t* mine = box + lane * 128;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            mine[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                            *reinterpret_cast<float4*>(mine + ((j ^ (lane & 7)) << 4)) =
+                                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                            __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        fence_proxy_async_smem();
                         __syncwarp();
                         const uint32_t row_base = tm * C::BM + h * BMMA + quad * 32;
-                        if (col < p.n) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const uint32_t r = j * 4 + (lane >> 3);
-                                if (row_base + r < p.m) {
-                                    const float4 val = *reinterpret_cast<const float4*>(xp + r * kXposeStride + 4 * (lane & 7));
-                                    const size_t at = (size_t)(row_base + r) * p.ldc + col + 4 * (lane & 7);
-                                    *reinterpret_cast<float4*>(p.out + at) = val;
-                                    for (uint32_t d = 0; d < p.n_peer; ++d) *reinterpret_cast<float4*>(p.out_peer[d] + at) = val;
-                                }
+                        if (lane == 0) {
+                            if (row_base < p.m && col < p.n) {
+                                const uint32_t src = smem_addr(box);
+                                for (uint32_t d = 0; d <= p.n_peer; ++d)
+                                    tma_store_2d(&maps_c.c[d], (int32_t)col, (int32_t)row_base, src);
                             }
+                            bulk_commit_group();
                         }
-                        __syncwarp();
                     } else if (row < p.m) {
                         if (p.out_vec && col + 32 <= p.n) {
                             float4* d4 = reinterpret_cast<float4*>(dst_row + c * 32);
@@ -281,6 +287,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_addr(&tail->acc_empty[as]));
         }
+        // every TMA store of this warp has been performed before the block leaves
+        if (p.n_peer > 0 && lane == 0) bulk_wait_group<0>();
     }
 
     tc_fence_before_sync();
@@ -330,10 +338,11 @@ bool make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t oute
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <int HALVES>
-vx_status launch_tiles(vx_context* ctx, const CUtensorMap& map_a, const CUtensorMap& map_b, Tf32Params p) {
+vx_status launch_tiles(vx_context* ctx, const CUtensorMap& map_a, const CUtensorMap& map_b, Tf32Params p,
+                       const PeerMaps& maps_c) {
     using C = Cfg<HALVES>;
-    const size_t smem = (size_t)C::kStages * C::kStageBytes + 256 + kXposeBytes + 1024;
-    static_assert(sizeof(SharedTail) <= 256, "barriers and the transposition buffers share the tail");
+    const size_t smem = (size_t)C::kStages * C::kStageBytes + 1024 + kXposeBytes + 1024;
+    static_assert(sizeof(SharedTail) <= 1024, "barriers sit in the first KB after the ring, the staging boxes after it");
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63]) {
         VX_CUDA(cudaFuncSetAttribute(gemm_tf32_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -343,7 +352,7 @@ vx_status launch_tiles(vx_context* ctx, const CUtensorMap& map_a, const CUtensor
     p.tiles_n = (p.n + BN - 1) / BN;
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     dim3 grid(std::min<uint32_t>(tiles, (uint32_t)ctx->sm_count));
-    gemm_tf32_kernel<HALVES><<<grid, kThreads, smem, ctx->stream>>>(map_a, map_b, p);
+    gemm_tf32_kernel<HALVES><<<grid, kThreads, smem, ctx->stream>>>(map_a, map_b, p, maps_c);
     VX_CUDA(cudaGetLastError());
     return VX_OK;
 }
@@ -356,8 +365,8 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
                            const vx_shapes3& s, bool* eligible, float* const* out_peer, uint32_t n_peer) {
     *eligible = false;
     if (n_peer > 0) {
-        // The peer path stores whole 32-column blocks as 16-byte pieces.
-        if (s.out.n != 1 || s.out.c != 1 || s.out.w % 32 != 0 || !aligned16(out) || s.out.h_stride % 4 != 0) return VX_OK;
+        // The peer path sends 32 x 32 blocks with tiled TMA stores: every C must be describable.
+        if (s.out.n != 1 || s.out.c != 1 || !aligned16(out) || s.out.h_stride % 4 != 0 || s.out.h_stride < s.out.w) return VX_OK;
         for (uint32_t d = 0; d < n_peer; ++d)
             if (!aligned16(out_peer[d])) return VX_OK;
     }
@@ -405,7 +414,19 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
             p.status = ctx->d_status;
             p.n_peer = std::min<uint32_t>(n_peer, kMaxPeers);
             for (uint32_t d = 0; d < (uint32_t)kMaxPeers; ++d) p.out_peer[d] = d < p.n_peer ? out_peer[d] : nullptr;
-            vx_status st = halves == 2 ? launch_tiles<2>(ctx, map_a, map_b, p) : launch_tiles<1>(ctx, map_a, map_b, p);
+            PeerMaps maps_c;
+            memset(&maps_c, 0, sizeof(maps_c));
+            if (p.n_peer > 0) {
+                // One map per destination: the panel (n columns wide, rows ldc apart), 32 x 32 boxes in the
+                // 128-byte-swizzled layout the epilogue stages.
+                for (uint32_t d = 0; d <= p.n_peer; ++d) {
+                    float* dst = d == 0 ? c : out_peer[d - 1];
+                    if (!make_map(&maps_c.c[d], dst, n, m, s.out.h_stride, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+                        return fail(VX_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled refused the C panel of destination %u", d);
+                }
+            }
+            vx_status st = halves == 2 ? launch_tiles<2>(ctx, map_a, map_b, p, maps_c)
+                                       : launch_tiles<1>(ctx, map_a, map_b, p, maps_c);
             if (st != VX_OK) return st;
             ctx->launches++;
             ctx->status_dirty = true;

@@ -6,8 +6,8 @@
 //     completion counted on one mbarrier per stage.  Bytes in flight are set by the ring,
 //     not by registers or occupancy.
 //   * Every consumer thread owns the same 16-byte chunk position(s) of every row (32 Q4_0
-//     weights or 16 Q8_0 weights) and keeps the matching slice of x in registers for the whole
-//     kernel, so x is read from memory once per CTA and never touches shared memory.
+//     weights or 16 Q8_0 weights) and keeps the matching slice of x in registers for a whole
+//     product, so x is read from memory once per CTA and product and never touches shared memory.
 //   * x is held as fixed point: per chunk, x_i = sx * X_i with |X_i| < 2^23, and X_i split into
 //     three byte planes (signed high, unsigned middle and low).  A chunk-row product is then
 //     6 (Q4_0: 24, Q8_0: 12) dp4a on the raw quants — exact integer arithmetic — followed by
@@ -519,10 +519,10 @@ vx_status launch_tr(vx_context* ctx, int qtype, const StreamConfig& c, const Str
 
 
 // false: the row is too long for the shared-memory ring or the register-resident x.
-bool choose_config(vx_context* ctx, uint32_t nchunks, uint32_t nb, uint32_t max_tiles_hint_rows, bool flagged,
-                   StreamConfig* c) {
+bool choose_config_tr(vx_context* ctx, uint32_t tile_rows, uint32_t nchunks, uint32_t nb, uint32_t max_tiles_hint_rows,
+                      bool flagged, StreamConfig* c) {
     using vx::option;
-    c->tr = option(ctx, "gemv.tile_rows", 8) == 4 ? 4 : 8;
+    c->tr = tile_rows;
     if (nchunks > 4 * kConsumers) return false;
     c->cpt = nchunks <= kConsumers ? 1 : nchunks <= 2 * kConsumers ? 2 : 4;
     uint32_t tpr = ((nchunks + c->cpt - 1) / c->cpt + 31) / 32 * 32;
@@ -564,6 +564,15 @@ bool choose_config(vx_context* ctx, uint32_t nchunks, uint32_t nb, uint32_t max_
     c->per_sm = per_sm;
     c->smem = (size_t)stages * c->stage_bytes + fixed;
     return true;
+}
+
+// Tiles of 8 rows (or what "gemv.tile_rows" asks for); rows too long for two stages of those (beyond about
+// 28 000 Q4_0 / 14 000 Q8_0 weights) take tiles of 4 rows.
+bool choose_config(vx_context* ctx, uint32_t nchunks, uint32_t nb, uint32_t max_tiles_hint_rows, bool flagged,
+                   StreamConfig* c) {
+    const uint32_t first = vx::option(ctx, "gemv.tile_rows", 8) == 4 ? 4 : 8;
+    if (choose_config_tr(ctx, first, nchunks, nb, max_tiles_hint_rows, flagged, c)) return true;
+    return first == 8 && choose_config_tr(ctx, 4, nchunks, nb, max_tiles_hint_rows, flagged, c);
 }
 
 void fill_common(StreamParams* p, const StreamConfig& c, uint32_t nchunks, uint32_t nb, vx_context* ctx) {

@@ -198,7 +198,7 @@ vx_status vx_gemm_tf32_scatter(vx_context* ctx, float* out, const float* lhs, co
     vx_status st = vx::launch_gemm_tf32(ctx, out, lhs, rhs, s, &eligible, peer_out, (uint32_t)n_peers);
     if (st != VX_OK) return st;
     VX_REQUIRE(eligible, VX_ERR_UNSUPPORTED,
-               "the panel must be one matrix with unit column strides, 16-byte aligned rows and a width that is a multiple of 32");
+               "the panel must be one matrix with unit column strides and 16-byte aligned bases and row pitches");
     ctx->last_gemm_kernel = 3;
     return VX_OK;
 }

@@ -91,6 +91,28 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int3
         "l"(tmap), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+// Tiled TMA store, shared memory -> global memory (also a peer GPU's, through its mapped address), tracked by
+// the issuing thread's bulk async-group.  Elements of the box that fall outside the tensor are not written.
+// x and y must not be negative.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, int32_t x, int32_t y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap), "r"(x),
+                 "r"(y), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's groups still have to READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until at most N of this thread's groups are still incomplete (writes performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Orders this thread's earlier shared-memory writes (generic proxy) before later TMA reads (async proxy).
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int32_t x, int32_t y, int32_t z,
                                             uint32_t bar) {
     asm volatile(
