@@ -555,6 +555,7 @@ def side_configs(be, lib, torch, stream):
 
     # f32 GEMM 1024^3, exact SIMT path (and the TF32 path at 8192^3 when the device has room).
     for name, mode, dim in (("gemm_f32_simt_exact_1024", _lib.VX_GEMM_SIMT_EXACT, 1024),
+                            ("gemm_tf32_4096", _lib.VX_GEMM_TF32, 4096),
                             ("gemm_tf32_8192", _lib.VX_GEMM_TF32, 8192)):
         A = torch.rand(dim, dim, device="cuda") * 2 - 1
         B = torch.rand(dim, dim, device="cuda") * 2 - 1
@@ -582,6 +583,11 @@ def side_configs(be, lib, torch, stream):
             fn()
             be.synchronize()
         out[name]["reference_protocol_ms"] = (time.perf_counter() - t0) * 1e3 / 10
+        if mode == _lib.VX_GEMM_TF32:
+            be.set_option("gemm.tf32.tma_store", 0)     # the epilogue warps store C themselves
+            us = time_graph(fn, 1, reps=3)
+            be.set_option("gemm.tf32.tma_store", 1)
+            out[name]["plain_store_epilogue"] = {"us": us, "TFLOP/s": 2 * dim ** 3 / us / 1e6}
     return out
 
 

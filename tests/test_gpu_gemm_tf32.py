@@ -139,3 +139,33 @@ def test_tf32_scatter_epilogue_writes_every_destination(backend, m, n, k):
         got = np.empty(m * ldc, np.float32)
         backend.slow_read_buffer(o, got)
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_tf32_round_to_nearest_on_load_is_no_worse_than_truncation(backend):
+    """With "gemm.tf32.round_nearest" (default) the TMA copies round A and B to TF32 to nearest; without it the
+    tensor core drops the low mantissa bits.  Both sit inside the 5e-3 bar; rounding must not be the worse one."""
+    import ctypes as C
+    lib = _lib.load()
+    n = 1024
+    rng = np.random.Generator(np.random.Philox(99))
+    a = rng.random((n, n), dtype=np.float32) * 2 - 1
+    b = rng.random((n, n), dtype=np.float32) * 2 - 1
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    ad, bd, cd = backend.init_buffer(a.ravel()), backend.init_buffer(b.ravel()), backend.uninit_buffer(n * n)
+    sh = _lib.VxShapes3()
+    for s in (sh.out, sh.lhs, sh.rhs):
+        s.n = s.c = 1
+        s.h = s.w = n
+        s.n_stride = s.c_stride = n * n
+        s.h_stride, s.w_stride = n, 1
+    err = {}
+    for rn in (0, 1):
+        backend.set_option("gemm.tf32.round_nearest", rn)
+        _lib.check(lib.vx_gemm_f32(backend._ctx, _lib.VX_GEMM_TF32, cd.ptr, ad.ptr, bd.ptr, C.byref(sh), 0, 0, 0))
+        got = np.empty(n * n, np.float32)
+        backend.slow_read_buffer(cd, got)
+        err[rn] = np.linalg.norm(got.reshape(n, n) - want) / np.linalg.norm(want)
+    backend.set_option("gemm.tf32.round_nearest", 1)
+    print("relative Frobenius error: truncation", err[0], "round to nearest", err[1])
+    assert err[0] <= 5e-3 and err[1] <= 5e-3
+    assert err[1] <= err[0] * 1.05

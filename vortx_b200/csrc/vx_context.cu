@@ -36,6 +36,8 @@ static const char* const kKnownOptions[] = {
     "gemm.simt.force_generic",  // 1: always take the generic-stride SIMT kernel
     "gemm.tf32.stages",   // TMA pipeline depth
     "gemm.tf32.raster",   // tile rasterisation group height
+    "gemm.tf32.tma_store",  // 1 (default): the epilogue hands C blocks to tiled TMA stores; 0: plain stores
+    "gemm.tf32.round_nearest",  // 1 (default): TMA rounds A and B to TF32 to nearest on load; 0: the tensor core truncates
     "gemm.tf32.tile_m",   // 128 or 256 forces the tile height of the TF32 kernel (0 = by problem size)
     "bounds_check",       // 1 (default): refuse layouts that reach beyond the stated capacity
 };

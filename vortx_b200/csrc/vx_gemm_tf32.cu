@@ -67,6 +67,7 @@ struct Tf32Params {
     // Column-sharded use: every tile is also stored at the same position of these buffers (the
     // full-width C of each peer GPU, mapped into this process).  Plain stores over NVLink.
     uint32_t n_peer;
+    uint32_t tma_store;  // the epilogue sends blocks with tiled TMA stores (always with peers)
     float* out_peer[vx::kMaxPeers];
     vx::DeviceStatus* status;
 };
@@ -242,7 +243,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     tmem_ld_32x32(taddr + c * 32, v);
                     tmem_ld_wait();
                     const uint32_t col = col0 + c * 32;
-                    if (p.n_peer > 0) {
+                    if (p.tma_store) {
                         // (the host only takes this path when TMA can describe every C: 16-byte aligned bases and
                         // row pitches)
                         const uint32_t use = chunk_it++;
@@ -288,7 +289,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (lane == 0) mbar_arrive(smem_addr(&tail->acc_empty[as]));
         }
         // every TMA store of this warp has been performed before the block leaves
-        if (p.n_peer > 0 && lane == 0) bulk_wait_group<0>();
+        if (p.tma_store && lane == 0) bulk_wait_group<0>();
     }
 
     tc_fence_before_sync();
@@ -322,15 +323,18 @@ EncodeFn encode_fn() {
 
 // 2-D f32 tensor map: inner dimension `inner` (unit stride), outer dimension `outer` with
 // `stride_elems` between rows; box inner_box x outer_box; zero fill out of bounds.
+// `round_tf32`: the copy engine rounds each f32 to TF32 (to nearest) on its way into shared memory; the tensor
+// core otherwise just drops the low 13 mantissa bits.
 bool make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t stride_elems,
-              uint32_t inner_box, uint32_t outer_box, CUtensorMapSwizzle swizzle) {
+              uint32_t inner_box, uint32_t outer_box, CUtensorMapSwizzle swizzle, bool round_tf32 = false) {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {stride_elems * sizeof(float)};
     const cuuint32_t box[2] = {inner_box, outer_box};
     const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
+    return fn(map, round_tf32 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+              const_cast<float*>(base), dims, strides, box, elem,
               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -397,8 +401,9 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
             const float* b = rhs + (size_t)bn * s.rhs.n_stride + (size_t)bc * s.rhs.c_stride;
             float* c = out + (size_t)bn * s.out.n_stride + (size_t)bc * s.out.c_stride;
             CUtensorMap map_a, map_b;
-            if (!make_map(&map_a, a, k, m, s.lhs.h_stride, BK, BMMA * halves, CU_TENSOR_MAP_SWIZZLE_128B) ||
-                !make_map(&map_b, b, n, k, s.rhs.h_stride, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) {
+            const bool rn = option(ctx, "gemm.tf32.round_nearest", 1) != 0;
+            if (!make_map(&map_a, a, k, m, s.lhs.h_stride, BK, BMMA * halves, CU_TENSOR_MAP_SWIZZLE_128B, rn) ||
+                !make_map(&map_b, b, n, k, s.rhs.h_stride, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, rn)) {
                 if (bn == 0 && bc == 0) return VX_OK;  // nothing launched yet: let the caller fall back
                 return fail(VX_ERR_CUDA, "cuTensorMapEncodeTiled refused a batch matrix after the first");
             }
@@ -416,13 +421,23 @@ vx_status launch_gemm_tf32(vx_context* ctx, float* out, const float* lhs, const 
             for (uint32_t d = 0; d < (uint32_t)kMaxPeers; ++d) p.out_peer[d] = d < p.n_peer ? out_peer[d] : nullptr;
             PeerMaps maps_c;
             memset(&maps_c, 0, sizeof(maps_c));
-            if (p.n_peer > 0) {
-                // One map per destination: the panel (n columns wide, rows ldc apart), 32 x 32 boxes in the
-                // 128-byte-swizzled layout the epilogue stages.
+            // One map per destination: the panel (n columns wide, rows ldc apart), 32 x 32 boxes in the
+            // 128-byte-swizzled layout the epilogue stages.  Without peers the TMA epilogue is a choice
+            // ("gemm.tf32.tma_store", default on when C can be described): the warps hand their blocks to the
+            // copy engine instead of storing them themselves.
+            p.tma_store = 0;
+            const bool describable = aligned16(c) && s.out.h_stride % 4 == 0 && s.out.h_stride >= n;
+            if (p.n_peer > 0 || (describable && option(ctx, "gemm.tf32.tma_store", 1) != 0)) {
+                p.tma_store = 1;
                 for (uint32_t d = 0; d <= p.n_peer; ++d) {
                     float* dst = d == 0 ? c : out_peer[d - 1];
-                    if (!make_map(&maps_c.c[d], dst, n, m, s.out.h_stride, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+                    if (!make_map(&maps_c.c[d], dst, n, m, s.out.h_stride, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+                        if (p.n_peer == 0) {
+                            p.tma_store = 0;
+                            break;
+                        }
                         return fail(VX_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled refused the C panel of destination %u", d);
+                    }
                 }
             }
             vx_status st = halves == 2 ? launch_tiles<2>(ctx, map_a, map_b, p, maps_c)
