@@ -135,6 +135,11 @@ VX_API vx_status vx_dequantize_host(vx_qtype t, const void* blocks, size_t rows,
 /* Upload a host block stream; rows x cols logical weights. */
 VX_API vx_status vx_qweights_upload(vx_context* ctx, vx_qtype t, const void* blocks, size_t rows,
                                     size_t cols, vx_qweights** out);
+/* The same weights quantised ON the device from an f32 matrix that is already there (rows row_stride
+ * elements apart), straight into the planar layout: no host pass, no upload.  Bit-identical to
+ * vx_quantize + vx_qweights_upload of the same values.  Stream-ordered. */
+VX_API vx_status vx_qweights_from_device(vx_context* ctx, vx_qtype t, const float* w_device, size_t rows,
+                                         size_t cols, size_t row_stride, vx_qweights** out);
 VX_API vx_status vx_qweights_free(vx_context* ctx, vx_qweights* w);
 VX_API vx_status vx_qweights_info(const vx_qweights* w, int32_t* qtype, size_t* rows, size_t* cols,
                                   size_t* device_bytes);

@@ -242,3 +242,40 @@ def test_gemv_long_rows(backend, oracle, qt, rows, cols):
     blocks = oracle.quantize(qt, w)
     y64, absdot = oracle.gemv_f64(qt, blocks, rows, cols, x)
     _check(_run(backend, qt, blocks, rows, cols, x), y64, absdot)
+
+
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("rows,cols,pad", [(1, 32, 0), (37, 96, 0), (300, 1056, 32), (64, 4096, 0), (129, 2048, 5)])
+def test_device_quantiser_matches_host_quantiser(backend, oracle, qt, rows, cols, pad):
+    """vx_qweights_from_device gives the very weights vx_quantize + upload give: dequantised planes and GEMV
+    outputs are bit-identical.  Ties, zero blocks, extreme magnitudes and unaligned row strides included."""
+    w = synth.normal_matrix(rows, cols, seed=3 * rows + cols).copy()
+    w[0, :32] = 0.0                                   # a zero block: neutral quants
+    if cols >= 64:
+        w[0, 32:64] = np.float32(0.5)                 # all equal: the first element fixes the scale
+        w[0, 40] = np.float32(-0.5)                   # same magnitude later on: must not take over
+    w[rows - 1, :8] = np.float32([1e-30, -1e-30, 65000.0, -3e4, 7.0, -7.0, 3.5, -3.5])
+    stride = cols + pad
+    padded = np.zeros((rows, stride), np.float32)
+    padded[:, :cols] = w
+    wd = backend.init_buffer(padded.ravel())
+    on_dev = vb.QuantizedMatrix.from_device_f32(backend, qt, wd.ptr, rows, cols, stride)
+    on_host = vb.QuantizedMatrix(backend, qt, oracle.quantize(qt, w), rows, cols)
+    outs = []
+    for qm in (on_dev, on_host):
+        buf = backend.uninit_buffer(rows * cols)
+        qm.dequantize(buf)
+        got = np.empty(rows * cols, np.float32)
+        backend.slow_read_buffer(buf, got)
+        outs.append(got)
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    x = synth.normal_vectors(1, cols, seed=9)
+    xd = backend.init_buffer(x.ravel())
+    ys = []
+    for qm in (on_dev, on_host):
+        yd = backend.init_buffer(np.full(rows, np.nan, np.float32))
+        vb.Gemv().dispatch(backend, None, yd, qm, xd)
+        y = np.empty(rows, np.float32)
+        backend.slow_read_buffer(yd, y)
+        ys.append(y)
+    assert np.array_equal(ys[0].view(np.uint32), ys[1].view(np.uint32))

@@ -104,6 +104,7 @@ SIGNATURES = {
     "vx_quantize": (C.c_int32, [C.c_int, _P, C.c_size_t, C.c_size_t, _P]),
     "vx_dequantize_host": (C.c_int32, [C.c_int, _P, C.c_size_t, C.c_size_t, _P]),
     "vx_qweights_upload": (C.c_int32, [_P, C.c_int, _P, C.c_size_t, C.c_size_t, C.POINTER(_P)]),
+    "vx_qweights_from_device": (C.c_int32, [_P, C.c_int, _P, C.c_size_t, C.c_size_t, C.c_size_t, C.POINTER(_P)]),
     "vx_qweights_free": (C.c_int32, [_P, _P]),
     "vx_qweights_info": (C.c_int32, [_P, C.POINTER(C.c_int32), C.POINTER(C.c_size_t),
                                      C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),

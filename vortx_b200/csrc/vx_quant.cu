@@ -20,6 +20,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <memory>
 #include <cmath>
 #include <cstring>
 #include <new>
@@ -389,6 +390,73 @@ vx_status launch_batch(vx_context* ctx, const vx_qweights* w, size_t row0, uint3
 
 }  // namespace
 
+// Device quantiser: one thread per block of 32 weights, the same arithmetic as the host quantiser below
+// (IEEE division, f16 scale rounded to nearest even before the quants are formed, round half away from zero),
+// writing the planar layout directly.  `row_stride` is the distance between rows of w in elements.
+template <int QT>
+__global__ void quantize_planar_kernel(const float* __restrict__ w, size_t rows, size_t nb, size_t row_stride,
+                                       uint8_t* __restrict__ quants, uint16_t* __restrict__ scales) {
+    const size_t total = rows * nb;
+    for (size_t blk = (size_t)blockIdx.x * blockDim.x + threadIdx.x; blk < total; blk += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = blk / nb, b = blk % nb;
+        const float* src = w + r * row_stride + b * QK;
+        float v[QK];
+        if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+#pragma unroll
+            for (int i = 0; i < QK / 4; ++i) {
+                const float4 f = __ldg(reinterpret_cast<const float4*>(src) + i);
+                v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < QK; ++i) v[i] = __ldg(src + i);
+        }
+        // The element of largest magnitude (first one on ties) fixes the scale.
+        float amax = 0.0f, signed_max = 0.0f;
+#pragma unroll
+        for (int i = 0; i < QK; ++i) {
+            const float a = fabsf(v[i]);
+            if (a > amax) {
+                amax = a;
+                signed_max = v[i];
+            }
+        }
+        const __half dh = __float2half_rn(QT == 0 ? __fdiv_rn(amax, 127.0f) : __fdiv_rn(signed_max, 7.0f));
+        const float d = __half2float(dh);
+        scales[blk] = __half_as_ushort(dh);
+        if (QT == 0) {
+            uint32_t packed[QK / 4];
+#pragma unroll
+            for (int i = 0; i < QK; ++i) {
+                float q = d != 0.0f ? roundf(__fdiv_rn(v[i], d)) : 0.0f;   // roundf: half away from zero
+                q = fminf(127.0f, fmaxf(-127.0f, q));
+                const uint32_t byte = (uint32_t)(int)q & 0xFFu;
+                if (i % 4 == 0) packed[i / 4] = 0;
+                packed[i / 4] |= byte << (8 * (i % 4));
+            }
+            uint4* dst = reinterpret_cast<uint4*>(quants + blk * 32);
+            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+            uint32_t q[QK];
+#pragma unroll
+            for (int i = 0; i < QK; ++i) {
+                float t = d != 0.0f ? roundf(__fdiv_rn(v[i], d)) + 8.0f : 8.0f;
+                t = fminf(15.0f, fmaxf(0.0f, t));
+                q[i] = (uint32_t)(int)t;
+            }
+            uint32_t packed[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                packed[k] = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) packed[k] |= (q[4 * k + j] | (q[4 * k + j + 16] << 4)) << (8 * j);
+            }
+            *reinterpret_cast<uint4*>(quants + blk * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+    }
+}
+
 extern "C" {
 
 size_t vx_qblock_bytes(vx_qtype t) { return (t == VX_Q8_0 || t == VX_Q4_0) ? block_bytes(t) : 0; }
@@ -521,6 +589,58 @@ vx_status vx_qweights_upload(vx_context* ctx, vx_qtype t, const void* blocks, si
     w->d_quants = w->d_base;
     w->d_scales = reinterpret_cast<uint16_t*>(w->d_base + qplane);
     *out = w;
+    return VX_OK;
+}
+
+vx_status vx_qweights_from_device(vx_context* ctx, vx_qtype t, const float* w_device, size_t rows, size_t cols,
+                                  size_t row_stride, vx_qweights** out) {
+    VX_REQUIRE(ctx && out, VX_ERR_INVALID_ARGUMENT, "vx_qweights_from_device: null argument");
+    *out = nullptr;
+    VX_REQUIRE(t == VX_Q8_0 || t == VX_Q4_0, VX_ERR_INVALID_ARGUMENT, "unknown quantised type %d", (int)t);
+    VX_REQUIRE(cols % QK == 0 && cols > 0 && rows > 0, VX_ERR_INVALID_ARGUMENT,
+               "rows (%zu) and cols (%zu) must be positive and cols a multiple of 32", rows, cols);
+    VX_REQUIRE(w_device && row_stride >= cols, VX_ERR_INVALID_ARGUMENT, "null weights or rows %zu elements apart", row_stride);
+    VX_REQUIRE(rows <= 0xFFFFFFFFull && cols / QK <= 0x03FFFFFFull, VX_ERR_UNSUPPORTED, "matrix too large");
+    vx::DeviceGuard guard(ctx->device);
+    std::unique_ptr<vx_qweights> w(new (std::nothrow) vx_qweights());
+    VX_REQUIRE(w, VX_ERR_OUT_OF_MEMORY, "host allocation failed");
+    w->type = t;
+    w->rows = rows;
+    w->cols = cols;
+    w->blocks_per_row = cols / QK;
+    w->quant_row_bytes = w->blocks_per_row * quant_bytes(t);
+    w->device = ctx->device;
+    const size_t nblocks = rows * w->blocks_per_row;
+    const size_t qplane = round_up(nblocks * quant_bytes(t), 256);
+    const size_t splane = round_up(nblocks * 2, 256);
+    w->device_bytes = qplane + splane;
+    cudaError_t e = cudaMalloc(&w->d_base, w->device_bytes);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(VX_ERR_OUT_OF_MEMORY, "allocating %zu bytes of quantised weights failed: %s", w->device_bytes,
+                    cudaGetErrorString(e));
+    }
+    w->d_quants = w->d_base;
+    w->d_scales = reinterpret_cast<uint16_t*>(w->d_base + qplane);
+    // the padding behind each plane is read by whole-tile copies: keep it defined
+    e = cudaMemsetAsync(w->d_base, 0, w->device_bytes, ctx->stream);
+    if (e == cudaSuccess) {
+        const unsigned threads = 128;
+        const unsigned blocks = (unsigned)std::min<size_t>((nblocks + threads - 1) / threads, (size_t)ctx->sm_count * 16);
+        if (t == VX_Q8_0)
+            quantize_planar_kernel<0><<<blocks, threads, 0, ctx->stream>>>(w_device, rows, w->blocks_per_row, row_stride,
+                                                                        w->d_quants, w->d_scales);
+        else
+            quantize_planar_kernel<1><<<blocks, threads, 0, ctx->stream>>>(w_device, rows, w->blocks_per_row, row_stride,
+                                                                        w->d_quants, w->d_scales);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        cudaFree(w->d_base);
+        return fail(VX_ERR_CUDA, "device quantisation failed: %s", cudaGetErrorString(e));
+    }
+    ctx->launches++;
+    *out = w.release();
     return VX_OK;
 }
 

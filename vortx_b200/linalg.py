@@ -216,6 +216,18 @@ class QuantizedMatrix:
     def from_f32(cls, backend: Backend, qtype: int, w: np.ndarray) -> "QuantizedMatrix":
         return cls(backend, qtype, quantize(qtype, w), w.shape[0], w.shape[1])
 
+    @classmethod
+    def from_device_f32(cls, backend: Backend, qtype: int, w_ptr: int, rows: int, cols: int,
+                        row_stride: Optional[int] = None) -> "QuantizedMatrix":
+        """Quantises an f32 matrix that already lives on the device (vx_qweights_from_device)."""
+        h = C.c_void_p()
+        _lib.check(_lib.load().vx_qweights_from_device(backend._ctx, qtype, w_ptr, rows, cols,
+                                                       cols if row_stride is None else row_stride, C.byref(h)))
+        self = cls.__new__(cls)
+        self.backend, self.qtype, self.rows, self.cols = backend, qtype, rows, cols
+        self._h = h
+        return self
+
     def stream_bytes(self) -> int:
         return self.rows * (self.cols // 32) * _lib.load().vx_qblock_bytes(self.qtype)
 
