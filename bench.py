@@ -210,18 +210,21 @@ def run_ours(args):
     y_full = torch.zeros(LAYERS, ROWS, device=dev, dtype=torch.float32)  # one y per layer
 
     # N > 1: how the rows of y reach every GPU.
-    #   "peer" (default): the step is a CHAIN.  Rows are dealt out in turn (rank r owns rows r, r + N, ...);
-    #       the GEMV's epilogue stores each row as a {value, generation} pair into an exchange vector on
-    #       every GPU over NVLink, and the next GEMV takes its x from the first COLS elements of that vector
-    #       (rows of every rank), re-reading pairs that have not arrived yet while its weights already stream.
-    #       GEMV 0 of a step reads the plain x; the step ends by unpacking the last vector to plain f32.
+    #   "peer" (default): the step is a CHAIN in one persistent launch per GPU.  Each rank owns a contiguous slab
+    #       of rows; the GEMV's epilogue stores each row as a {value, generation} pair into an exchange vector on
+    #       every GPU over NVLink (a tile's rows leave as one contiguous store), and the next GEMV takes its x from
+    #       the head of every rank's slab in that vector (COLS / N elements each: rows of every rank), re-reading
+    #       pairs that have not arrived yet while its weights already stream.  GEMV 0 of a step reads the plain x;
+    #       the step ends by unpacking the last vector to plain f32.
+    #   "peer-launches": the same dependency with one launch per GEMV and rows dealt out in turn.
     #   "peer-barrier": plain peer stores from the epilogue + a one-warp barrier kernel after every GEMV.
     #   "nccl": all-gather after every GEMV.
     scatter = chain = None
     if n > 1:
         from vortx_b200.multi_gpu import PeerScatterGemv
         scatter = PeerScatterGemv(be, ROWS, COLS, LAYERS, vectors=0)
-        chain = PeerScatterGemv(be, ROWS, COLS, 1, vectors=2, cyclic=True)
+        chain = PeerScatterGemv(be, ROWS, COLS, 1, vectors=2, cyclic=True)      # "peer-launches": rows dealt out in turn
+        chain_w = PeerScatterGemv(be, ROWS, COLS, 1, vectors=2)                  # "peer": contiguous slabs, windowed x
 
     def gemv(layer: int, xptr: int):
         yptr = y_full[layer].data_ptr() + row0 * 4
@@ -233,7 +236,7 @@ def run_ours(args):
     # the kernel-only figure; chained through the exchange vectors for "peer".
     plain_batch = vb.GemvBatch(be, [{"w": layers[l], "x": x_dev.data_ptr(), "y": y_full[l].data_ptr() + row0 * 4}
                                     for l in range(LAYERS)])
-    chain_batch = chain.chain_batch(layers, x_dev.data_ptr()) if n > 1 else None
+    chain_batch = chain_w.chain_batch(layers, x_dev.data_ptr(), window=True) if n > 1 else None
 
     def step_device(exchange=args.exchange):
         if n == 1 and exchange != "separate":
@@ -241,7 +244,7 @@ def run_ours(args):
             return
         if n > 1 and exchange == "peer":
             chain_batch.launch()
-            chain.unpack((LAYERS - 1) % 2, chain.y_ptr(0))
+            chain_w.unpack((LAYERS - 1) % 2, chain_w.y_ptr(0))
             return
         if n > 1 and exchange == "peer-launches":      # the same chain, one launch per GEMV
             chain.dispatch_chained(layers[0], 0, x_ptr=x_dev.data_ptr())
@@ -396,10 +399,18 @@ def run_ours(args):
             extra[f"exchange_{other}"] = {"ms_per_step": other_ms, "GB/s": bytes_per_step / (other_ms * 1e-3) / 1e9}
         extra["kernels_only"] = {"us_per_list_launch": launch_us, "GB/s_per_gpu": achieved}
         note("exchange variants timed")
-        extra["gemm_tf32_8192_col_sharded"] = sharded_gemm_numbers(be, torch, dist, stream, n, rank, barrier)
+        # (the headline numbers above must not be lost to a failure in this side measurement: every rank
+        # runs the same code, so a library error raises on all of them alike)
+        try:
+            extra["gemm_tf32_8192_col_sharded"] = sharded_gemm_numbers(be, torch, dist, stream, n, rank, barrier)
+        except _lib.VortxError as e:
+            extra["gemm_tf32_8192_col_sharded"] = {"failed": str(e)}
     cpu = None
     if rank == 0 and n == 1:
-        extra = side_configs(be, lib, torch, stream)
+        try:
+            extra = side_configs(be, lib, torch, stream)
+        except _lib.VortxError as e:
+            extra = {"side_configs_failed": str(e)}
         try:
             gbs, dt, threads = cpu_gemv_rate(blocks, ROWS, steps=5, warmup=1)
             cpu = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",

@@ -279,3 +279,72 @@ def test_device_quantiser_matches_host_quantiser(backend, oracle, qt, rows, cols
         backend.slow_read_buffer(yd, y)
         ys.append(y)
     assert np.array_equal(ys[0].view(np.uint32), ys[1].view(np.uint32))
+
+
+def test_batch_rejects_what_it_cannot_run(backend):
+    """A list refuses mixed formats or column counts, entries without x or y, rows outside the matrix and an
+    entry that reads the vector it writes — with a status, before anything is launched."""
+    from vortx_b200 import _lib
+    w4 = vb.QuantizedMatrix.from_f32(backend, vb.Q4_0, synth.normal_matrix(16, 64, seed=1))
+    w8 = vb.QuantizedMatrix.from_f32(backend, vb.Q8_0, synth.normal_matrix(16, 64, seed=2))
+    wide = vb.QuantizedMatrix.from_f32(backend, vb.Q4_0, synth.normal_matrix(16, 128, seed=3))
+    x = backend.init_buffer(np.zeros(128, np.float32))
+    y = backend.uninit_buffer(64)
+    vec = backend.init_buffer(np.zeros(256 + 8 * 64, np.uint8))
+    before = backend.launch_count()
+    good = {"w": w4, "x": x.ptr, "y": y.ptr}
+    for bad, status in (([good, {"w": w8, "x": x.ptr, "y": y.ptr}], _lib.VX_ERR_UNSUPPORTED),
+                        ([good, {"w": wide, "x": x.ptr, "y": y.ptr}], _lib.VX_ERR_UNSUPPORTED),
+                        ([{"w": w4, "y": y.ptr}], _lib.VX_ERR_INVALID_ARGUMENT),
+                        ([{"w": w4, "x": x.ptr}], _lib.VX_ERR_INVALID_ARGUMENT),
+                        ([{"w": w4, "x": x.ptr, "y": y.ptr, "row0": 10, "nrows": 7}], _lib.VX_ERR_OUT_OF_BOUNDS),
+                        ([{"w": w4, "x_xvec": vec.ptr, "y_xvec": vec.ptr}], _lib.VX_ERR_INVALID_ARGUMENT)):
+        with pytest.raises(_lib.VortxError) as e:
+            vb.GemvBatch(backend, bad)
+        assert e.value.status == status, e.value
+    assert backend.launch_count() == before
+
+
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("rows,cols,segs", [(1024, 512, 2), (4096, 2048, 4), (3584, 1024, 8)])
+def test_batch_chain_with_windowed_x(backend, qt, rows, cols, segs):
+    """rows > cols: the next product's x is a window of the previous y — the first cols / segs elements of each of
+    `segs` equal slabs (what a row-sharded chain reads: the head of every rank's slab).  One list launch against
+    the same chain done with plain products and device copies."""
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    links = 4
+    w = synth.normal_matrix(rows, cols, seed=rows + 3) * np.float32(50.0 / np.sqrt(cols))
+    qm = vb.QuantizedMatrix.from_f32(backend, qt, w)
+    x0 = synth.normal_vectors(1, cols, seed=6)[0]
+    xd = backend.init_buffer(x0)
+    seg_len, seg_stride = cols // segs, rows // segs
+    # plain chain
+    y = backend.uninit_buffer(rows)
+    xn = backend.uninit_buffer(cols)
+    src = xd
+    for l in range(links):
+        vb.Gemv().dispatch(backend, None, y, qm, src)
+        for s in range(segs):
+            _lib.check(lib.vx_copy(backend._ctx, xn.ptr + s * seg_len * 4, y.ptr + s * seg_stride * 4, seg_len * 4))
+        src = xn
+    want = np.empty(rows, np.float32)
+    backend.slow_read_buffer(y, want)
+    # the same as one list
+    nbytes = lib.vx_xvec_bytes(rows)
+    vecs = [backend.uninit_buffer(nbytes, dtype=np.uint8) for _ in range(2)]
+    for v in vecs:
+        _lib.check(lib.vx_memset(backend._ctx, v.ptr, 0, nbytes))
+    entries = [{"w": qm, "x": xd.ptr, "y_xvec": vecs[0].ptr}]
+    for l in range(1, links):
+        entries.append({"w": qm, "x_xvec": vecs[(l - 1) % 2].ptr, "y_xvec": vecs[l % 2].ptr,
+                        "x_seg_len": seg_len, "x_seg_stride": seg_stride})
+    batch = vb.GemvBatch(backend, entries)
+    out = backend.uninit_buffer(rows)
+    got = np.empty(rows, np.float32)
+    for rep in range(2):
+        batch.launch()
+        _lib.check(lib.vx_xvec_unpack(backend._ctx, vecs[(links - 1) % 2].ptr, rows, out.ptr))
+        backend.slow_read_buffer(out, got)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    batch.free()

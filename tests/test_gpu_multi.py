@@ -148,6 +148,37 @@ def _chain_worker(rank, world, port, out_dir):
             batch.free()
             dist.barrier()
         g.close()
+    # rows > cols with contiguous slabs: x of the next link is the head of every rank's slab (a windowed read);
+    # against the same chain computed on this GPU alone from the whole matrix, with plain products and copies
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    rows, cols, wl = 4096, 2048, 5
+    w2 = synth.normal_matrix(rows, cols, seed=41) * np.float32(50.0 / 45.0)
+    blocks2 = vb.quantize(vb.Q4_0, w2)
+    g = PeerScatterGemv(be, rows, cols, 1)
+    mine = vb.QuantizedMatrix(be, vb.Q4_0, shard_blocks(blocks2, rows, cols, 18, world, rank), g.nrows, cols)
+    whole = vb.QuantizedMatrix(be, vb.Q4_0, blocks2, rows, cols)
+    seg_len, seg_stride = cols // world, rows // world
+    yp, xn = be.uninit_buffer(rows), be.uninit_buffer(cols)
+    src = xd.ptr
+    for l in range(wl):
+        vb.Gemv().dispatch(be, None, yp, whole, src)
+        for s_ in range(world):
+            _lib.check(lib.vx_copy(be._ctx, xn.ptr + s_ * seg_len * 4, yp.ptr + s_ * seg_stride * 4, seg_len * 4))
+        src = xn.ptr
+    want = np.empty(rows, np.float32)
+    be.slow_read_buffer(yp, want)
+    batch = g.chain_batch([mine] * wl, xd.ptr, window=True)
+    for rep in range(3):
+        batch.launch()
+        g.unpack((wl - 1) % 2, g.y_ptr(0))
+    be.synchronize()
+    got = np.empty(rows, np.float32)
+    be.slow_read_buffer(g.y.local, got.view(np.uint8))
+    results["window_want"], results["window_got"] = want, got
+    batch.free()
+    dist.barrier()
+    g.close()
     np.savez(os.path.join(out_dir, f"chain{rank}.npz"), **results)
     dist.barrier()
     be.close()
@@ -196,6 +227,9 @@ def test_chained_gemv_with_fused_exchange_on_two_gpus(tmp_path, oracle):
                 assert np.array_equal(got[r][f"pure{run}_{cyclic}"].view(np.uint32), ys[links - 1].view(np.uint32))
                 assert np.array_equal(got[r][f"batch{run}_{cyclic}"].view(np.uint32), ys[links - 1].view(np.uint32))
         assert not np.array_equal(got[0][f"run0_{cyclic}"], got[0][f"run1_{cyclic}"])
+    for r in range(world):
+        assert np.array_equal(got[r]["window_got"].view(np.uint32), got[r]["window_want"].view(np.uint32))
+        assert np.isfinite(got[r]["window_got"]).all() and np.abs(got[r]["window_got"]).max() > 0
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")

@@ -53,7 +53,8 @@ class VxGemvOp(C.Structure):
     _fields_ = [("w", C.c_void_p), ("row0", C.c_size_t), ("nrows", C.c_size_t), ("x_xvec", C.c_void_p),
                 ("x", C.c_void_p), ("y", C.c_void_p), ("y_xvec", C.c_void_p), ("peer_y_xvec", C.POINTER(C.c_void_p)),
                 ("n_peers", C.c_size_t), ("y_row0", C.c_size_t), ("y_stride", C.c_size_t),
-                ("peer_y", C.POINTER(C.c_void_p)), ("n_peer_y", C.c_size_t)]
+                ("peer_y", C.POINTER(C.c_void_p)), ("n_peer_y", C.c_size_t),
+                ("x_seg_len", C.c_size_t), ("x_seg_stride", C.c_size_t)]
 
 
 class VortxError(RuntimeError):

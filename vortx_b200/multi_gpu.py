@@ -172,11 +172,15 @@ class PeerScatterGemv:
                             "peer_y": [self.y.ptrs[r] + off for r in self._others]})
         return GemvBatch(self.backend, entries)
 
-    def chain_batch(self, weights_list, x_ptr: int):
+    def chain_batch(self, weights_list, x_ptr: int, window: bool = False):
         """The whole chain as ONE persistent launch per GPU (GemvBatch): link 0 reads the plain x, link l reads
         exchange vector (l - 1) % 2 and writes l % 2.  Returns the batch; after `launch()`, `unpack((len - 1) % 2, ...)`
-        ends the chain."""
+        ends the chain.  x of a link is the vector's first `cols` elements, or with `window` (contiguous slabs,
+        rows > cols) the first cols / world elements of every rank's slab: rows of every rank, and each tile's rows
+        still leave for a peer as one contiguous store."""
         from .linalg import GemvBatch
+        if window and (self.cyclic or self.cols % self.world or self.rows % self.world or (self.cols // self.world) % 32):
+            raise ValueError("the windowed chain takes equal contiguous slabs and cols / world a multiple of 32")
         entries = []
         for l, w in enumerate(weights_list):
             e = {"w": w, "nrows": self.nrows, "y_xvec": self.vectors[l % 2].local.ptr,
@@ -186,6 +190,8 @@ class PeerScatterGemv:
                 e["x"] = x_ptr
             else:
                 e["x_xvec"] = self.vectors[(l - 1) % 2].local.ptr
+                if window:
+                    e["x_seg_len"], e["x_seg_stride"] = self.cols // self.world, self.rows // self.world
             entries.append(e)
         return GemvBatch(self.backend, entries)
 
