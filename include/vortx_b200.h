@@ -223,10 +223,10 @@ typedef struct {
     float* const* peer_y;       /* plain rows also stored here (n_peer_y buffers, as for
                                    vx_gemv_q_rows_scatter), or NULL                 */
     size_t n_peer_y;
-    size_t x_seg_len, x_seg_stride; /* with x_xvec: x is x_seg_len consecutive elements out of every
-                                   x_seg_stride of the vector (the head of every rank's slab); 0, 0:
-                                   the vector's first cols elements.  x_seg_len divides cols and is a
-                                   multiple of 32                                   */
+    size_t x_seg_len, x_seg_stride, x_seg_first; /* with x_xvec: x is x_seg_len consecutive elements,
+                                   from element x_seg_first, out of every x_seg_stride of the vector (a
+                                   piece of every rank's slab); all 0: the vector's first cols elements.
+                                   x_seg_len divides cols and is a multiple of 32; first and stride even */
 } vx_gemv_op;
 VX_API vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_ops,
                                       vx_gemv_batch** out);

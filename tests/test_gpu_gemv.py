@@ -306,10 +306,11 @@ def test_batch_rejects_what_it_cannot_run(backend):
 
 
 @pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("at_end", [False, True])
 @pytest.mark.parametrize("rows,cols,segs", [(1024, 512, 2), (4096, 2048, 4), (3584, 1024, 8)])
-def test_batch_chain_with_windowed_x(backend, qt, rows, cols, segs):
+def test_batch_chain_with_windowed_x(backend, qt, rows, cols, segs, at_end):
     """rows > cols: the next product's x is a window of the previous y — the first cols / segs elements of each of
-    `segs` equal slabs (what a row-sharded chain reads: the head of every rank's slab).  One list launch against
+    `segs` equal slabs, or the last ones (what a row-sharded chain reads: a piece of every rank's slab).  One list launch against
     the same chain done with plain products and device copies."""
     from vortx_b200 import _lib
     lib = _lib.load()
@@ -319,6 +320,7 @@ def test_batch_chain_with_windowed_x(backend, qt, rows, cols, segs):
     x0 = synth.normal_vectors(1, cols, seed=6)[0]
     xd = backend.init_buffer(x0)
     seg_len, seg_stride = cols // segs, rows // segs
+    first = seg_stride - seg_len if at_end else 0
     # plain chain
     y = backend.uninit_buffer(rows)
     xn = backend.uninit_buffer(cols)
@@ -326,7 +328,7 @@ def test_batch_chain_with_windowed_x(backend, qt, rows, cols, segs):
     for l in range(links):
         vb.Gemv().dispatch(backend, None, y, qm, src)
         for s in range(segs):
-            _lib.check(lib.vx_copy(backend._ctx, xn.ptr + s * seg_len * 4, y.ptr + s * seg_stride * 4, seg_len * 4))
+            _lib.check(lib.vx_copy(backend._ctx, xn.ptr + s * seg_len * 4, y.ptr + (s * seg_stride + first) * 4, seg_len * 4))
         src = xn
     want = np.empty(rows, np.float32)
     backend.slow_read_buffer(y, want)
@@ -338,7 +340,7 @@ def test_batch_chain_with_windowed_x(backend, qt, rows, cols, segs):
     entries = [{"w": qm, "x": xd.ptr, "y_xvec": vecs[0].ptr}]
     for l in range(1, links):
         entries.append({"w": qm, "x_xvec": vecs[(l - 1) % 2].ptr, "y_xvec": vecs[l % 2].ptr,
-                        "x_seg_len": seg_len, "x_seg_stride": seg_stride})
+                        "x_seg_len": seg_len, "x_seg_stride": seg_stride, "x_seg_first": first})
     batch = vb.GemvBatch(backend, entries)
     out = backend.uninit_buffer(rows)
     got = np.empty(rows, np.float32)

@@ -148,7 +148,7 @@ def _chain_worker(rank, world, port, out_dir):
             batch.free()
             dist.barrier()
         g.close()
-    # rows > cols with contiguous slabs: x of the next link is the head of every rank's slab (a windowed read);
+    # rows > cols with contiguous slabs: x of the next link is the tail of every rank's slab (a windowed read);
     # against the same chain computed on this GPU alone from the whole matrix, with plain products and copies
     from vortx_b200 import _lib
     lib = _lib.load()
@@ -164,7 +164,8 @@ def _chain_worker(rank, world, port, out_dir):
     for l in range(wl):
         vb.Gemv().dispatch(be, None, yp, whole, src)
         for s_ in range(world):
-            _lib.check(lib.vx_copy(be._ctx, xn.ptr + s_ * seg_len * 4, yp.ptr + s_ * seg_stride * 4, seg_len * 4))
+            _lib.check(lib.vx_copy(be._ctx, xn.ptr + s_ * seg_len * 4,
+                                   yp.ptr + (s_ * seg_stride + seg_stride - seg_len) * 4, seg_len * 4))   # the slab's tail
         src = xn.ptr
     want = np.empty(rows, np.float32)
     be.slow_read_buffer(yp, want)

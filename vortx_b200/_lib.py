@@ -54,7 +54,7 @@ class VxGemvOp(C.Structure):
                 ("x", C.c_void_p), ("y", C.c_void_p), ("y_xvec", C.c_void_p), ("peer_y_xvec", C.POINTER(C.c_void_p)),
                 ("n_peers", C.c_size_t), ("y_row0", C.c_size_t), ("y_stride", C.c_size_t),
                 ("peer_y", C.POINTER(C.c_void_p)), ("n_peer_y", C.c_size_t),
-                ("x_seg_len", C.c_size_t), ("x_seg_stride", C.c_size_t)]
+                ("x_seg_len", C.c_size_t), ("x_seg_stride", C.c_size_t), ("x_seg_first", C.c_size_t)]
 
 
 class VortxError(RuntimeError):

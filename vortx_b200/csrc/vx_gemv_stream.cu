@@ -72,10 +72,10 @@ struct OpParams {
     int32_t y_vec;                        // or -1: no flagged output
     uint32_t y_gen_add;
     const uint64_t* x_pairs;
-    // x may be a window of a longer flagged vector: `x_seg_len` consecutive elements out of every
-    // `x_seg_stride` (x = the first x_seg_len elements of each rank's slab, when the vector holds one slab
+    // x may be a window of a longer flagged vector: `x_seg_len` consecutive elements, starting at element
+    // `x_seg_first`, out of every `x_seg_stride` (a piece of each rank's slab, when the vector holds one slab
     // per rank).  x_seg_len == 0: x is the vector's first cols elements.
-    uint32_t x_seg_len, x_seg_stride;
+    uint32_t x_seg_len, x_seg_stride, x_seg_first;
     uint64_t* y_pairs;                    // this rank's vector, advanced to the slab's first element
     uint64_t* y_pairs_peer[vx::kMaxPeers];
     uint32_t n_pair_peer;
@@ -302,6 +302,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
             const uint32_t x_gen = x_pairs ? *(volatile const uint32_t*)p.vec_hdr[op.x_vec] + op.x_gen_add : 0;
             const uint32_t x_aligned = op.x_aligned;
             const uint32_t seg_len = XCH ? op.x_seg_len : 0, seg_stride = XCH ? op.x_seg_stride : 0;
+            const uint32_t seg_first = XCH ? op.x_seg_first : 0;
 #pragma unroll
             for (int j = 0; j < CPT; ++j) {
                 const uint32_t c = tc + j * p.tpr;
@@ -312,7 +313,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                     // generation yet is still on its way (from a peer, or from another block of this
                     // grid) and is read again (bounded).
                     const uint32_t e = c * W;  // first element of the chunk; segments are whole chunks
-                    const uint64_t* src = x_pairs + (seg_len ? (size_t)(e / seg_len) * seg_stride + e % seg_len : (size_t)e);
+                    const uint64_t* src = x_pairs + (seg_len ? (size_t)(e / seg_len) * seg_stride + seg_first + e % seg_len : (size_t)e);
                     const long long start = clock64();
                     bool ok = false;
                     while (!ok) {
@@ -336,7 +337,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                         }
                         if (!ok) {
                             if (*abort_flag != 0u || clock64() - start > kWaitCycles) break;
-                            __nanosleep(40);  // leave the L2 ports to the stores that are on their way
+                            // No __nanosleep here: measured on B200, a block whose warps sleep while they wait runs
+                            // its next tiles about three times slower for tens of microseconds (a chained product
+                            // took 33 us instead of 17.5 us when every block had to wait for the rows computed last).
                         }
                     }
                     if (!ok) {
@@ -739,11 +742,14 @@ vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_
             o.x_vec = v;
             o.x_gen_add = p.vec_writes[v];  // writes by the GEMVs before this one
             o.x_pairs = reinterpret_cast<const uint64_t*>(static_cast<const uint8_t*>(g.x_xvec) + vx::kExchangeHeader);
-            VX_REQUIRE(g.x_seg_len == 0 || (g.x_seg_len % 32 == 0 && g.x_seg_stride >= g.x_seg_len &&
+            VX_REQUIRE(g.x_seg_len == 0 || (g.x_seg_len % 32 == 0 && g.x_seg_first % 2 == 0 &&
+                                            g.x_seg_first + g.x_seg_len <= g.x_seg_stride && g.x_seg_stride % 2 == 0 &&
                                             g.x_seg_stride <= 0xFFFFFFFFull && g.w->cols % g.x_seg_len == 0),
-                       VX_ERR_INVALID_ARGUMENT, "GEMV %zu: x window of %zu elements every %zu", i, g.x_seg_len, g.x_seg_stride);
+                       VX_ERR_INVALID_ARGUMENT, "GEMV %zu: x window of %zu elements from %zu, every %zu", i, g.x_seg_len,
+                       g.x_seg_first, g.x_seg_stride);
             o.x_seg_len = (uint32_t)g.x_seg_len;
             o.x_seg_stride = (uint32_t)g.x_seg_stride;
+            o.x_seg_first = (uint32_t)g.x_seg_first;
             b->flagged = true;
         }
         if (g.y_xvec) {

@@ -276,7 +276,8 @@ class GemvBatch:
     Each entry is a dict: w (QuantizedMatrix), and optionally row0, nrows, x (plain device pointer), x_xvec
     (exchange vector to read x from), y (plain rows), y_xvec (exchange vector to write), peers (the same
     vector on the peer GPUs), y_row0, y_stride, peer_y (peer buffers that receive the plain rows as well),
-    x_seg_len / x_seg_stride (x is a window: that many elements out of every stride of x_xvec).  Entries may depend on each other only through exchange
+    x_seg_len / x_seg_stride / x_seg_first (x is a window: that many elements, from that offset, out of every
+    stride of x_xvec).  Entries may depend on each other only through exchange
     vectors.  Pointers are captured at construction."""
 
     def __init__(self, backend: Backend, entries):
@@ -297,6 +298,7 @@ class GemvBatch:
             arr[i].n_peer_y = len(plain)
             arr[i].x_seg_len = e.get("x_seg_len", 0)
             arr[i].x_seg_stride = e.get("x_seg_stride", 0)
+            arr[i].x_seg_first = e.get("x_seg_first", 0)
             arr[i].w = w._h
             arr[i].row0 = row0
             arr[i].nrows = w.rows - row0 if nrows is None else nrows

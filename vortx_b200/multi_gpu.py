@@ -172,12 +172,13 @@ class PeerScatterGemv:
                             "peer_y": [self.y.ptrs[r] + off for r in self._others]})
         return GemvBatch(self.backend, entries)
 
-    def chain_batch(self, weights_list, x_ptr: int, window: bool = False):
+    def chain_batch(self, weights_list, x_ptr: int, window: bool = False, window_at_end: bool = True):
         """The whole chain as ONE persistent launch per GPU (GemvBatch): link 0 reads the plain x, link l reads
         exchange vector (l - 1) % 2 and writes l % 2.  Returns the batch; after `launch()`, `unpack((len - 1) % 2, ...)`
         ends the chain.  x of a link is the vector's first `cols` elements, or with `window` (contiguous slabs,
-        rows > cols) the first cols / world elements of every rank's slab: rows of every rank, and each tile's rows
-        still leave for a peer as one contiguous store."""
+        rows > cols) cols / world elements of every rank's slab — its last ones by default, the rows every rank
+        computes last, so that the link waits for the end of the previous one as a product over all rows would —:
+        rows of every rank, and each tile's rows still leave for a peer as one contiguous store."""
         from .linalg import GemvBatch
         if window and (self.cyclic or self.cols % self.world or self.rows % self.world or (self.cols // self.world) % 32):
             raise ValueError("the windowed chain takes equal contiguous slabs and cols / world a multiple of 32")
@@ -192,6 +193,7 @@ class PeerScatterGemv:
                 e["x_xvec"] = self.vectors[(l - 1) % 2].local.ptr
                 if window:
                     e["x_seg_len"], e["x_seg_stride"] = self.cols // self.world, self.rows // self.world
+                    e["x_seg_first"] = e["x_seg_stride"] - e["x_seg_len"] if window_at_end else 0
             entries.append(e)
         return GemvBatch(self.backend, entries)
 
