@@ -213,8 +213,9 @@ def run_ours(args):
     #   "peer" (default): the step is a CHAIN in one persistent launch per GPU.  Each rank owns a contiguous slab
     #       of rows; the GEMV's epilogue stores each row as a {value, generation} pair into an exchange vector on
     #       every GPU over NVLink (a tile's rows leave as one contiguous store), and the next GEMV takes its x from
-    #       the head of every rank's slab in that vector (COLS / N elements each: rows of every rank), re-reading
-    #       pairs that have not arrived yet while its weights already stream.  GEMV 0 of a step reads the plain x;
+    #       the END of every rank's slab in that vector (COLS / N elements each: the rows every rank computes last,
+    #       so the GEMV cannot start before the previous one is complete on every GPU), re-reading pairs that have
+    #       not arrived yet while its weights already stream.  GEMV 0 of a step reads the plain x;
     #       the step ends by unpacking the last vector to plain f32.
     #   "peer-launches": the same dependency with one launch per GEMV and rows dealt out in turn.
     #   "peer-barrier": plain peer stores from the epilogue + a one-warp barrier kernel after every GEMV.
@@ -685,8 +686,11 @@ def emit(line: dict) -> None:
 
 EXCHANGE_TEXT = {
     "peer": "chain of dependent GEMVs in one persistent launch per GPU: rows stored as {value, generation} pairs into "
-            "every GPU's exchange vector from the kernel epilogue, awaited pair by pair where the next GEMV reads its x",
-    "peer-launches": "the same chain with one launch per GEMV",
+            "every GPU's exchange vector from the kernel epilogue; the next GEMV's x is the END of every rank's slab "
+            "in that vector (the rows computed last: it cannot start before the previous one is complete everywhere), "
+            "awaited pair by pair",
+    "peer-launches": "flagged pairs with one launch per GEMV and rows dealt out in turn; x is the vector's first 8192 "
+                     "elements (rows computed early: a looser dependency than 'peer')",
     "separate": "N = 1 only: one launch per GEMV instead of the list launch",
     "peer-barrier": "peer stores from the kernel epilogue + a barrier kernel after every GEMV",
     "nccl": "NCCL all-gather after every GEMV",
