@@ -554,8 +554,9 @@ bool choose_config_tr(vx_context* ctx, uint32_t tile_rows, uint32_t nchunks, uin
     // prefetch its first tiles while this one is still running.
     int64_t per_sm = option(ctx, "gemv.ctas_per_sm", 0);
     if (per_sm <= 0) per_sm = tiles >= 16u * (uint32_t)ctx->sm_count ? 2 : 1;
-    // The flagged kernel needs 128 registers: one CTA per SM.  (Capped at 102 for two CTAs per SM it spills
-    // in the main loop and a chained product measured 20.8 us instead of 15.3 us.)
+    // One flagged CTA per SM.  Its blocks wait on each other's rows by re-reading memory, and a block that
+    // spins next to a working one on the same SM takes its issue slots: with two per SM (the kernel fits in 86
+    // registers when asked) a fully dependent chained product measured 104 us instead of 18 us.
     if (flagged) per_sm = 1;
     per_sm = std::min<int64_t>(per_sm, 4);
     const size_t budget = (size_t)(200 * 1024) / (size_t)per_sm - fixed;
