@@ -33,6 +33,7 @@ static const char* const kKnownOptions[] = {
     "gemv.rows_per_warp", // rows a warp carries at once
     "gemv.block_threads", // CTA size of the GEMV kernels
     "gemv.ctas_per_sm",   // persistent grid = SMs x this
+    "gemv.block_wait",    // flagged x in a list: 1 one warp waits for the block, 0 every thread for its own chunk, -1 (default) by tiles per block
     "gemm.simt.force_generic",  // 1: always take the generic-stride SIMT kernel
     "gemm.tf32.stages",   // TMA pipeline depth
     "gemm.tf32.raster",   // tile rasterisation group height

@@ -90,6 +90,7 @@ struct StreamParams {
     uint32_t stage_bytes;
     uint32_t q_stage_bytes;  // TR * row bytes: where the scales start inside a stage
     uint32_t n_ops;          // up to kInlineOps: inline_ops; more: ops[] in device memory
+    uint32_t block_wait;     // flagged x: one warp waits for the block (see the consumers)
     uint32_t n_vec;
     const OpParams* ops;
     uint32_t* vec_hdr[kMaxVecs];   // headers of the exchange vectors the list touches (own memory)
@@ -303,6 +304,39 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
             const uint32_t x_aligned = op.x_aligned;
             const uint32_t seg_len = XCH ? op.x_seg_len : 0, seg_stride = XCH ? op.x_seg_stride : 0;
             const uint32_t seg_first = XCH ? op.x_seg_first : 0;
+            if (XCH && x_pairs && p.block_wait) {
+                // One warp waits for the whole block: it re-reads the last two pairs of every chunk of x until
+                // they all carry the generation; the other consumer warps sleep at a hardware barrier
+                // meanwhile.  (Eight warps re-reading their own chunks at full rate took the issue slots and
+                // the load pipe from this SM's epilogue warp, which still had the rows to deliver that other
+                // blocks were waiting for: with 3 tiles per block and product, at 8 GPUs, a fully dependent
+                // chained product took 26 us.)  What the probes do not cover is caught by each thread's own
+                // read below.  The extra round of probes costs about 2 us per product, so the host only asks
+                // for it when a block has few tiles per product and waiting dominates.
+                if (warp == 0) {
+                    const long long start = clock64();
+                    for (;;) {
+                        bool all = true;
+                        // eight probes per lane in flight at a time (256 chunks per round)
+                        for (uint32_t c0 = 0; c0 < p.nchunks; c0 += 256) {
+                            uint64_t pa[8], pb[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const uint32_t c = min(c0 + lane + 32u * i, p.nchunks - 1);
+                                const uint32_t e = c * W + (W - 2);
+                                ld_volatile_v2_u64(x_pairs + (seg_len ? (size_t)(e / seg_len) * seg_stride + seg_first + e % seg_len : (size_t)e),
+                                                   pa[i], pb[i]);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                all = all && (uint32_t)(pa[i] >> 32) == x_gen && (uint32_t)(pb[i] >> 32) == x_gen;
+                        }
+                        if (__all_sync(0xffffffffu, all)) break;
+                        if (*abort_flag != 0u || clock64() - start > kWaitCycles) break;   // the reads below report it
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+            }
 #pragma unroll
             for (int j = 0; j < CPT; ++j) {
                 const uint32_t c = tc + j * p.tpr;
@@ -785,6 +819,9 @@ vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_
     const uint32_t tiles = (max_rows + b->cfg.tr - 1) / b->cfg.tr;
     const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * b->cfg.per_sm);
     b->grid = dim3(std::min(tiles, slots));
+    // few tiles per block and product: the blocks mostly wait for each other, let one warp do it
+    const int64_t bw = vx::option(ctx, "gemv.block_wait", -1);
+    p.block_wait = bw >= 0 ? (bw != 0) : (tiles < 5 * slots ? 1u : 0u);
     vx::DeviceGuard guard(ctx->device);
     if (n_ops <= (size_t)kInlineOps) {
         for (size_t i = 0; i < n_ops; ++i) p.inline_ops[i] = host[i];
