@@ -237,6 +237,8 @@ def run_ours(args):
     # the kernel-only figure; chained through the exchange vectors for "peer".
     plain_batch = vb.GemvBatch(be, [{"w": layers[l], "x": x_dev.data_ptr(), "y": y_full[l].data_ptr() + row0 * 4}
                                     for l in range(LAYERS)])
+    if os.environ.get("VX_GEMV_BLOCK_WAIT"):     # 0 / 1 overrides the library's choice of how blocks wait for x
+        be.set_option("gemv.block_wait", int(os.environ["VX_GEMV_BLOCK_WAIT"]))
     chain_batch = chain_w.chain_batch(layers, x_dev.data_ptr(), window=True) if n > 1 else None
 
     def step_device(exchange=args.exchange):
