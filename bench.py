@@ -3,20 +3,27 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload ("q4_0_gemv_28672x8192_x32"): the Q4_0 GEMV y = W x with W 28672 x 8192 (the FFN
-up-projection shape of the multi-GPU configuration), x f32 of length 8192, W ~ N(0, 0.02)
-before quantisation, x ~ N(0, 1), all seeded and synthetic.  One STEP is a pass over 32
-such matrices held at 32 different addresses (4.2 GB of weights at N = 1, far beyond the
-126 MB L2), i.e. 32 dependent GEMV launches replayed from one CUDA graph.  With N > 1 the rows
-of every matrix are split into N contiguous slabs (strong scaling: total work fixed), each
-rank computes its slab straight into its slice of y and the slices are all-gathered with NCCL.
+Workload ("q4_0_gemv_28672x8192_x32"): the Q4_0 GEMV y = W x with W 28672 x 8192 (the FFN up-projection
+shape of the multi-GPU configuration), x f32 of length 8192, W ~ N(0, 0.02) before quantisation,
+x ~ N(0, 1), all seeded and synthetic.  One STEP is a pass over 32 such matrices held at 32 different
+addresses (4.2 GB of weights at N = 1, far beyond the 126 MB L2), issued as ONE persistent list launch and
+replayed from a CUDA graph.  With N > 1 the rows of every matrix are split into N contiguous slabs (strong
+scaling: total work fixed); each rank computes its slab, and the kernel's epilogue stores every finished row
+into the y of every GPU over NVLink (the all-gather of the output, fused into the GEMV); one barrier kernel per
+step tells every rank that all rows of all 32 products have landed.  The same dependency structure at every N:
+32 independent products.  The CHAINED form (product l + 1 takes its x from the rows every rank computed last
+in product l, exchanged through flagged pairs inside the kernel) is reported at every N, 1 included, under
+`extra.chained`, and NCCL's all-gather after every product under `extra.nccl_all_gather`.
 
 The line printed by rank 0:
-  value      algorithmic bytes per step / device time per step, weights resident in HBM
-             (bytes per GEMV = 132 120 576 of blocks + 32 768 n of x + 114 688 of y)
-  e2e        the same through the public API with host buffers: per GEMV the activation is
-             copied from pinned host memory, the product is read back to the host
-  roofline   the streaming GEMV kernel against the measured HBM copy bandwidth
+  value      algorithmic bytes per step / device time per step (weights resident in HBM, CUDA events, max over
+             ranks; bytes per GEMV = 132 120 576 of blocks + 32 768 n of x + 114 688 of y).  The timed region is
+             repeated in blocks of K steps for at least a second; the median block is reported, min / max beside it
+  check      outside the timed region: products of the last step against the CPU oracle (f64), the gathered y
+             identical on every rank, and the chained form bit for bit against the same chain run plainly on one GPU
+  e2e        the same through the public API with host buffers: the step's x vectors are copied from pinned
+             host memory, the products are read back to the host
+  roofline   the list launch against the measured HBM copy bandwidth (and a read-only pass measured here)
   cpu_baseline  the CPU oracle's GEMV on the host cores, on a bounded sample (rank 0, N = 1)
 `--impl reference` times that CPU implementation alone, on the same configuration.
 """
@@ -41,6 +48,11 @@ ROWS, COLS, LAYERS = 28672, 8192, 32
 QBLOCK = 18  # bytes per Q4_0 block
 METRIC = "q4_0_gemv_hbm_bandwidth"
 UNIT = "GB/s"
+WORKLOAD = "q4_0_gemv_28672x8192_x32"
+CHECKED_PRODUCTS = (0, 13, 31)
+# DRAM traffic of one 28672 x 8192 product inside a list launch: ncu dram__bytes_read + write of a list of 8
+# (1060.5 MB, second captured launch) / 8, from profiles/gemv_stream_list_q4_0_28672x8192_x8.md
+NCU_TRAFFIC_PER_PRODUCT = 132_560_000
 
 
 def gemv_bytes(rows: int, cols: int, n_gpus: int = 1, batch: int = 1, qblock: int = QBLOCK) -> int:
@@ -111,11 +123,10 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def make_weights(rows: int, cols: int, seed: int) -> np.ndarray:
-    """One Q4_0 block stream for a rows x cols matrix ~ N(0, 0.02), quantised by the library's host quantiser."""
-    import vortx_b200 as vb
+def slab_matrix(rows: int, seed: int) -> np.ndarray:
+    """The f32 weights of one slab before quantisation: rows x COLS ~ N(0, 0.02)."""
     from vortx_b200 import synth
-    return vb.quantize(vb.Q4_0, synth.normal_matrix(rows, cols, seed))
+    return synth.normal_matrix(rows, COLS, seed)
 
 
 # ------------------------------------------------------------------------ CPU arm ----
@@ -143,11 +154,14 @@ def cpu_gemv_rate(blocks: np.ndarray, rows: int, steps: int, warmup: int):
 
 def run_reference(args):
     """`--impl reference`: the reference has no quantised GEMV and its CPU backend (khal) cannot be
-    built here, so this arm times the CPU oracle's GEMV, the stand-in the parity tests use."""
+    built here, so this arm times the CPU oracle's GEMV, the stand-in the parity tests use.  Nothing of the
+    product library is loaded: the weights are quantised by the oracle's own quantiser."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    blocks = make_weights(ROWS, COLS, seed=100)
+    import oracle as o
+    o.build()
+    blocks = o.quantize(o.Q4_0, slab_matrix(ROWS, seed=100))
     gbs, dt, threads = cpu_gemv_rate(blocks, ROWS, args.steps, args.warmup)
     sample = (f"each step is {CPU_GEMVS_PER_STEP} of the workload's {LAYERS} GEMVs ({ROWS} x {COLS} Q4_0), "
               f"{threads} host threads; C++ restatement of the GEMV, not khal")
@@ -155,8 +169,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "q4_0 x f32 -> f32", "data": "synthetic",
-        "config": {"workload": "q4_0_gemv_28672x8192_x32", "rows": ROWS, "cols": COLS, "batch": 1,
-                   "sampled": sample},
+        "config": {"workload": WORKLOAD, "rows": ROWS, "cols": COLS, "batch": 1, "sampled": sample},
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -167,10 +180,14 @@ def run_reference(args):
 # ------------------------------------------------------------------------ GPU arm ----
 
 def run_ours(args):
+    # NCCL is only the rendezvous and the comparison form here.  NVLS off: a rank must never end while NCCL has
+    # buffers bound to an NVLink multicast object.
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch
     import torch.distributed as dist
     import vortx_b200 as vb
     from vortx_b200 import _lib, synth
+    from vortx_b200.multi_gpu import PeerBuffers
 
     t_start = time.perf_counter()
 
@@ -197,121 +214,229 @@ def run_ours(args):
     be = vb.Backend(local, stream=stream.cuda_stream)
 
     n = world
-    assert ROWS % n == 0
+    assert ROWS % n == 0 and COLS % n == 0
     shard = ROWS // n
     row0 = rank * shard
+    others = [r for r in range(n) if r != rank]
 
-    # One quantised shard, uploaded LAYERS times to distinct addresses (identical bytes are still
-    # distinct cache lines, and the step walks all of them before coming back).
-    blocks = make_weights(shard, COLS, seed=100 + rank)
-    layers = [vb.QuantizedMatrix(be, vb.Q4_0, blocks, shard, COLS) for _ in range(LAYERS)]
-    x_host = synth.normal_vectors(1, COLS, seed=1)[0]
-    x_dev = torch.from_numpy(x_host).to(dev)
-    y_full = torch.zeros(LAYERS, ROWS, device=dev, dtype=torch.float32)  # one y per layer
-
-    # N > 1: how the rows of y reach every GPU.
-    #   "peer" (default): the step is a CHAIN in one persistent launch per GPU.  Each rank owns a contiguous slab
-    #       of rows; the GEMV's epilogue stores each row as a {value, generation} pair into an exchange vector on
-    #       every GPU over NVLink (a tile's rows leave as one contiguous store), and the next GEMV takes its x from
-    #       the END of every rank's slab in that vector (COLS / N elements each: the rows every rank computes last,
-    #       so the GEMV cannot start before the previous one is complete on every GPU), re-reading pairs that have
-    #       not arrived yet while its weights already stream.  GEMV 0 of a step reads the plain x;
-    #       the step ends by unpacking the last vector to plain f32.
-    #   "peer-launches": the same dependency with one launch per GEMV and rows dealt out in turn.
-    #   "peer-barrier": plain peer stores from the epilogue + a one-warp barrier kernel after every GEMV.
-    #   "nccl": all-gather after every GEMV.
-    scatter = chain = None
-    if n > 1:
-        from vortx_b200.multi_gpu import PeerScatterGemv
-        scatter = PeerScatterGemv(be, ROWS, COLS, LAYERS, vectors=0)
-        chain = PeerScatterGemv(be, ROWS, COLS, 1, vectors=2, cyclic=True)      # "peer-launches": rows dealt out in turn
-        chain_w = PeerScatterGemv(be, ROWS, COLS, 1, vectors=2)                  # "peer": contiguous slabs, windowed x
-
-    def gemv(layer: int, xptr: int):
-        yptr = y_full[layer].data_ptr() + row0 * 4
-        st = lib.vx_gemv_q_rows(be._ctx, layers[layer]._h, 0, shard, xptr, COLS, yptr, shard, 1)
-        if st != 0:
-            raise RuntimeError(_lib.last_error())
-
-    # The step's 32 products as ONE persistent launch (a GEMV list): plain and independent at N = 1 and for
-    # the kernel-only figure; chained through the exchange vectors for "peer".
-    plain_batch = vb.GemvBatch(be, [{"w": layers[l], "x": x_dev.data_ptr(), "y": y_full[l].data_ptr() + row0 * 4}
-                                    for l in range(LAYERS)])
-    if os.environ.get("VX_GEMV_BLOCK_WAIT"):     # 0 / 1 overrides the library's choice of how blocks wait for x
-        be.set_option("gemv.block_wait", int(os.environ["VX_GEMV_BLOCK_WAIT"]))
-    chain_batch = chain_w.chain_batch(layers, x_dev.data_ptr(), window=True) if n > 1 else None
-
-    def step_device(exchange=args.exchange):
-        if n == 1 and exchange != "separate":
-            plain_batch.launch()
-            return
-        if n > 1 and exchange == "peer":
-            chain_batch.launch()
-            chain_w.unpack((LAYERS - 1) % 2, chain_w.y_ptr(0))
-            return
-        if n > 1 and exchange == "peer-launches":      # the same chain, one launch per GEMV
-            chain.dispatch_chained(layers[0], 0, x_ptr=x_dev.data_ptr())
-            for l in range(1, LAYERS):
-                chain.dispatch_chained(layers[l], l % 2, x_vec=(l - 1) % 2)
-            chain.unpack((LAYERS - 1) % 2, chain.y_ptr(0))
-            return
-        for l in range(LAYERS):
-            if n > 1 and exchange == "peer-barrier":
-                scatter.dispatch(layers[l], x_dev.data_ptr(), l)
-            else:
-                gemv(l, x_dev.data_ptr())
-                if n > 1 and exchange == "nccl":
-                    dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
-
-    note("weights uploaded")
-    # Warm-up outside the graph (also sizes NCCL's buffers), then capture one step.
-    launches_before = be.launch_count()
-    step_device()
-    launches_per_step = be.launch_count() - launches_before
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream):
-        step_device()
-    torch.cuda.synchronize()
-
-    note("step captured")
     def barrier():
         if n > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        graph.replay()
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record(stream)
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if n > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / args.steps
-    bytes_per_step = LAYERS * gemv_bytes(ROWS, COLS, n)
-    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    def max_over_ranks(values):
+        t = torch.tensor(list(values), device=dev, dtype=torch.float64)
+        if n > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
 
-    note("timed region done")
-    # Kernel-only figure for the roofline: the step's products on this GPU's rows without any exchange
-    # (N = 1: the step itself), timed live with CUDA events on the launching stream.  The dominant kernel is
-    # the list launch: LAYERS products per launch.
-    def time_graph(fn, reps):
+    # One quantised slab per rank (its own seed), uploaded LAYERS times to distinct addresses (identical bytes
+    # are still distinct cache lines, and the step walks all of them before coming back).
+    blocks = vb.quantize(vb.Q4_0, slab_matrix(shard, seed=100 + rank))
+    layers = [vb.QuantizedMatrix(be, vb.Q4_0, blocks, shard, COLS) for _ in range(LAYERS)]
+    xs_host = synth.normal_vectors(LAYERS, COLS, seed=1)        # e2e: one x per product; x 0 is the timed step's x
+    x_dev = torch.from_numpy(xs_host[0]).to(dev)
+
+    # Buffers every rank can store into: y of every product (full length), the barrier's flags, two exchange vectors.
+    if n > 1:
+        y_all = PeerBuffers(be, LAYERS * ROWS * 4)
+        flags = PeerBuffers(be, 64 * 4)
+        vecs = [PeerBuffers(be, lib.vx_xvec_bytes(ROWS)) for _ in range(2)]
+        y_ptrs, flag_ptrs = y_all.ptrs, flags.ptrs
+        vec_ptrs = [v.ptrs for v in vecs]
+    else:
+        y_buf = torch.zeros(LAYERS * ROWS, device=dev, dtype=torch.float32)
+        vec_bufs = [torch.zeros(lib.vx_xvec_bytes(ROWS), device=dev, dtype=torch.uint8) for _ in range(2)]
+        y_ptrs, flag_ptrs = [y_buf.data_ptr()], None
+        vec_ptrs = [[v.data_ptr()] for v in vec_bufs]
+    y_local = y_ptrs[rank]
+    import ctypes as C
+    flags_arr = (C.c_void_p * n)(*flag_ptrs) if n > 1 else None
+
+    def finish():
+        """One arrival barrier across the GPUs: after it, on this stream, every rank's rows have landed here."""
+        if n > 1:
+            _lib.check(lib.vx_peer_barrier(be._ctx, flags_arr, n, rank))
+
+    def gather_list(x_ptrs):
+        """The step as ONE list launch: product l reads x_ptrs[l]; its rows go into y[l] here and on every peer."""
+        entries = []
+        for l in range(LAYERS):
+            off = (l * ROWS + row0) * 4
+            entries.append({"w": layers[l], "nrows": shard, "x": x_ptrs[l], "y": y_local + off,
+                            "peer_y": [y_ptrs[r] + off for r in others]})
+        return vb.GemvBatch(be, entries)
+
+    def chain_list():
+        """The chained step as one list launch: product 0 reads the plain x, product l the last COLS / n elements
+        of every rank's slab of exchange vector (l - 1) % 2 — the rows every rank computes last — and writes
+        vector l % 2 on every GPU."""
+        seg_len, seg_stride = COLS // n, ROWS // n
+        entries = []
+        for l in range(LAYERS):
+            e = {"w": layers[l], "nrows": shard, "y_xvec": vec_ptrs[l % 2][rank],
+                 "peers": [vec_ptrs[l % 2][r] for r in others], "y_row0": row0, "y_stride": 1}
+            if l == 0:
+                e["x"] = x_dev.data_ptr()
+            else:
+                e["x_xvec"] = vec_ptrs[(l - 1) % 2][rank]
+                e["x_seg_len"], e["x_seg_stride"], e["x_seg_first"] = seg_len, seg_stride, seg_stride - seg_len
+            entries.append(e)
+        return vb.GemvBatch(be, entries)
+
+    value_batch = gather_list([x_dev.data_ptr()] * LAYERS)
+    chain_batch = chain_list()
+    chain_out = torch.zeros(ROWS, device=dev, dtype=torch.float32)
+
+    def step_value():
+        value_batch.launch()
+        finish()
+
+    def step_chain():
+        chain_batch.launch()
+        _lib.check(lib.vx_xvec_unpack(be._ctx, vec_ptrs[(LAYERS - 1) % 2][rank], ROWS, chain_out.data_ptr()))
+
+    graphs = []     # every CUDA graph made here; all are destroyed before the process group goes away
+
+    def capture(fn):
         fn()
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=stream):
             fn()
+        torch.cuda.synchronize()
+        graphs.append(g)
+        return g
+
+    def time_blocks(g, steps, warmup, min_seconds=1.0, max_blocks=400):
+        """Blocks of exactly `steps` replays, each bracketed by a barrier + synchronize and timed with CUDA events
+        on the launching stream, repeated until `min_seconds` of device time have been covered.  Returns the
+        per-step times (ms) of all blocks, each the max over ranks."""
+        for _ in range(max(warmup, 3)):
+            g.replay()
+        barrier()
+        blocks_ms, total = [], 0.0
+        while True:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record(stream)
+            for _ in range(steps):
+                g.replay()
+            e1.record(stream)
+            barrier()
+            blocks_ms.append(e0.elapsed_time(e1))
+            total += blocks_ms[-1]
+            # every rank must take the same number of blocks: decide on the max over ranks
+            if max_over_ranks([total])[0] >= min_seconds * 1e3 or len(blocks_ms) >= max_blocks:
+                break
+        return [v / steps for v in max_over_ranks(blocks_ms)]
+
+    note("weights uploaded")
+    launches_before = be.launch_count()
+    step_value()
+    launches_per_step = be.launch_count() - launches_before
+    graph = capture(step_value)
+    note("step captured")
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    per_step = time_blocks(graph, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = statistics.median(per_step)
+    bytes_per_step = LAYERS * gemv_bytes(ROWS, COLS, n)
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    note(f"timed region done: {len(per_step)} blocks of {args.steps} steps")
+
+    # ---- check (outside the timed region): the last step's products against the oracle, on every rank's copy
+    check = {"ok": True}
+    import oracle as o
+    o.build()
+    y_host = np.empty(LAYERS * ROWS, np.float32)
+    _lib.check(lib.vx_download(be._ctx, y_host.ctypes.data, y_local, y_host.nbytes))
+    y_host = y_host.reshape(LAYERS, ROWS)
+    want64, absdot = o.gemv_f64(o.Q4_0, blocks, shard, COLS, xs_host[:1])       # this rank's rows of every product
+    if n > 1:
+        parts = [torch.empty(2, shard, device=dev, dtype=torch.float64) for _ in range(n)]
+        dist.all_gather(parts, torch.from_numpy(np.stack([want64[0], absdot[0]])).to(dev))
+        full = torch.cat(parts, dim=1).cpu().numpy()
+        want_full, absdot_full = full[0], full[1]
+    else:
+        want_full, absdot_full = want64[0], absdot[0]
+    rels = []
+    for l in CHECKED_PRODUCTS:
+        diff = np.abs(y_host[l].astype(np.float64) - want_full)
+        rels.append(float(diff.max() / np.abs(want_full).max()))
+        check["ok"] = check["ok"] and rels[-1] <= 1e-4 and bool((diff <= 2e-6 * absdot_full).all())
+    same = all(np.array_equal(y_host[l].view(np.uint32), y_host[0].view(np.uint32)) for l in range(LAYERS))
+    check["ok"] = check["ok"] and same      # 32 copies of one matrix times one x: 32 identical products
+    check["max_rel"] = max(rels)
+    check["what"] = (f"products {list(CHECKED_PRODUCTS)} of the last timed step, all {ROWS} rows as gathered on this GPU, "
+                     "against the f64 CPU oracle (max-norm relative <= 1e-4, every row within 2e-6 of sum|w||x|); "
+                     "all 32 products bit-identical")
+    if n > 1:
+        # the gathered y is the same on every GPU
+        digest = torch.from_numpy(y_host.view(np.int32).astype(np.int64).sum(axis=1)).to(dev)
+        lo, hi = digest.clone(), digest.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        check["same_on_every_rank"] = bool(torch.equal(lo, hi))
+        check["ok"] = check["ok"] and check["same_on_every_rank"]
+    note("value form checked")
+
+    # ---- the chained form, at every N
+    chain_graph = capture(step_chain)
+    chain_steps = time_blocks(chain_graph, args.steps, args.warmup, min_seconds=0.3)
+    chain_ms = statistics.median(chain_steps)
+    chain_got = chain_out.cpu().numpy()
+    chained = {"ms_per_step": chain_ms, "GB/s": bytes_per_step / (chain_ms * 1e-3) / 1e9,
+               "us_per_product": chain_ms * 1e3 / LAYERS,
+               "what": "32 dependent products in one list launch per GPU; x of product l + 1 = the last 8192 / N rows "
+                       "every rank computed in product l, exchanged as {value, generation} pairs inside the kernel"}
+    # bit for bit against the same chain run plainly on ONE GPU (rank 0 gets every slab)
+    if n > 1:
+        mine = torch.from_numpy(blocks).to(dev)
+        slabs = [torch.empty_like(mine) for _ in range(n)]
+        dist.all_gather(slabs, mine)
+        whole_blocks = torch.cat(slabs).cpu().numpy() if rank == 0 else None
+    else:
+        whole_blocks = blocks
+    chain_ok = True
+    if rank == 0:
+        whole = vb.QuantizedMatrix(be, vb.Q4_0, whole_blocks, ROWS, COLS)
+        yp = torch.empty(ROWS, device=dev, dtype=torch.float32)
+        xn = torch.empty(COLS, device=dev, dtype=torch.float32)
+        seg_len, seg_stride = COLS // n, ROWS // n
+        src = x_dev.data_ptr()
+        for l in range(LAYERS):
+            _lib.check(lib.vx_gemv_q_rows(be._ctx, whole._h, 0, ROWS, src, COLS, yp.data_ptr(), ROWS, 1))
+            for s_ in range(n):
+                _lib.check(lib.vx_copy(be._ctx, xn.data_ptr() + s_ * seg_len * 4,
+                                       yp.data_ptr() + ((s_ + 1) * seg_stride - seg_len) * 4, seg_len * 4))
+            src = xn.data_ptr()
+        be.synchronize()
+        chain_want = yp.cpu().numpy()
+        whole.free()
+        chain_ok = bool(np.array_equal(chain_want.view(np.uint32), chain_got.view(np.uint32))) and \
+            bool(np.isfinite(chain_got).all()) and float(np.abs(chain_got).max()) > 0.0
+    if n > 1:
+        # every rank ended on the same vector
+        d = torch.tensor([int(chain_got.view(np.int32).astype(np.int64).sum())], device=dev)
+        lo, hi = d.clone(), d.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        chain_ok = chain_ok and bool(torch.equal(lo, hi))
+    chained["check_ok"] = chain_ok
+    check["chained_ok"] = chain_ok
+    check["ok"] = check["ok"] and chain_ok
+    note("chained form timed and checked")
+
+    # ---- kernel-only figure for the roofline: the list launch over this GPU's rows with no exchange at all
+    plain_batch = vb.GemvBatch(be, [{"w": layers[l], "x": x_dev.data_ptr(), "y": y_local + (l * ROWS + row0) * 4}
+                                    for l in range(LAYERS)])
+
+    def time_graph(fn, reps):
+        g = capture(fn)
         for _ in range(3):
             g.replay()
         torch.cuda.synchronize()
@@ -325,83 +450,105 @@ def run_ours(args):
 
     reps = max(3, args.steps)
     launch_us = time_graph(plain_batch.launch, reps)
-    separate_us = time_graph(lambda: [gemv(l, x_dev.data_ptr()) for l in range(LAYERS)], reps) / LAYERS
+
+    def separate():
+        for l in range(LAYERS):
+            _lib.check(lib.vx_gemv_q_rows(be._ctx, layers[l]._h, 0, shard, x_dev.data_ptr(), COLS,
+                                          y_local + (l * ROWS + row0) * 4, shard, 1))
+    separate_us = time_graph(separate, reps) / LAYERS
     shard_bytes = gemv_bytes(shard, COLS)
     list_bytes = LAYERS * shard_bytes
     peak, peak_kind = measured_peak_hbm()
     achieved = list_bytes / (launch_us * 1e-6) / 1e9
+    # a read-only pass over the same 32 weight buffers (vx_checksum_u32), as a second denominator
+    sums = torch.zeros(LAYERS, device=dev, dtype=torch.int32)
 
+    def read_only():
+        for l in range(LAYERS):
+            _lib.check(lib.vx_qweights_checksum(be._ctx, layers[l]._h, sums.data_ptr() + 4 * l))
+    read_us = time_graph(read_only, reps)
+    read_only_gbs = sum(w.device_bytes() for w in layers) / (read_us * 1e-6) / 1e9
+    check["weights_intact"] = bool((sums == sums[0]).all().item())      # 32 uploads of the same bytes
+    check["ok"] = check["ok"] and check["weights_intact"]
     note("kernel-only timing done")
-    # End to end through the public API with host buffers: the step's 32 x vectors go up from pinned host
-    # memory in one copy, the step runs (each product reads its own x), and the 32 y vectors come back in one
-    # copy.  N > 1: every rank uploads x and reads back the whole y of every product, gathered on the device
-    # (one list launch whose epilogue stores the rows on every GPU + one barrier kernel; or NCCL).
-    xs_pin = torch.from_numpy(np.tile(x_host, (LAYERS, 1))).pin_memory()
+
+    # ---- end to end through the public API with host buffers: the step's 32 x vectors (all different) go up from
+    # pinned host memory in one copy, the step runs (fused gather + barrier at N > 1), and the products come back:
+    # rank 0's host reads every product whole, the other ranks' hosts the rows their GPU computed.
+    xs_pin = torch.from_numpy(xs_host).pin_memory()
     ys_pin = torch.empty(LAYERS, ROWS, dtype=torch.float32).pin_memory()
     xs_dev = torch.empty(LAYERS, COLS, device=dev, dtype=torch.float32)
-    e2e_batch = vb.GemvBatch(be, [{"w": layers[l], "x": xs_dev[l].data_ptr(), "y": y_full[l].data_ptr() + row0 * 4}
-                                  for l in range(LAYERS)])
-
-    e2e_scatter = scatter.scatter_batch(layers, [xs_dev[l].data_ptr() for l in range(LAYERS)]) if n > 1 else None
+    e2e_batch = gather_list([xs_dev[l].data_ptr() for l in range(LAYERS)])
 
     def step_e2e():
         _lib.check(lib.vx_upload(be._ctx, xs_dev.data_ptr(), xs_pin.data_ptr(), LAYERS * COLS * 4))
-        if n == 1:
-            e2e_batch.launch()
-            src = y_full.data_ptr()
-        elif args.exchange.startswith("peer"):
-            e2e_scatter.launch()      # rows of all 32 products stored here and on every peer ...
-            scatter.finish()          # ... and one arrival barrier for the step
-            src = scatter.y_ptr(0)
+        e2e_batch.launch()
+        finish()
+        if rank == 0:
+            _lib.check(lib.vx_download(be._ctx, ys_pin.data_ptr(), y_local, LAYERS * ROWS * 4))
         else:
-            e2e_batch.launch()
-            for l in range(LAYERS):
-                dist.all_gather_into_tensor(y_full[l], y_full[l, row0:row0 + shard])
-            src = y_full.data_ptr()
-        _lib.check(lib.vx_download(be._ctx, ys_pin.data_ptr(), src, LAYERS * ROWS * 4))
+            # this rank's slab of every product (strided in y): one 2-D copy
+            _lib.check(lib.vx_download_2d(be._ctx, ys_pin.data_ptr() + row0 * 4, ROWS * 4, y_local + row0 * 4, ROWS * 4,
+                                          shard * 4, LAYERS))
 
-    for _ in range(2):
+    for _ in range(3):
         step_e2e()
     barrier()
-    e2e_steps = max(2, min(args.steps, 10))
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        step_e2e()
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-    if n > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
+    e2e_steps = max(5, min(args.steps, 20))
+    e2e_blocks = []
+    for _ in range(5):
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            step_e2e()
+        barrier()
+        e2e_blocks.append((time.perf_counter() - t0) * 1e3 / e2e_steps)
+    e2e_ms = statistics.median(max_over_ranks(e2e_blocks))
     e2e_value = bytes_per_step / (e2e_ms * 1e-3) / 1e9
-
+    # the e2e results too: different x per product, so every product has its own answer
+    e2e_rels = []
+    if rank == 0:
+        for l in CHECKED_PRODUCTS:
+            w64, ad = o.gemv_f64(o.Q4_0, blocks, shard, COLS, xs_host[l:l + 1])
+            got = ys_pin[l, row0:row0 + shard].numpy()
+            diff = np.abs(got.astype(np.float64) - w64[0])
+            e2e_rels.append(float(diff.max() / np.abs(w64[0]).max()))
+            check["ok"] = check["ok"] and e2e_rels[-1] <= 1e-4 and bool((diff <= 2e-6 * ad[0]).all())
+        check["e2e_max_rel"] = max(e2e_rels)
     note("end-to-end timing done")
-    extra = {}
+
+    extra = {"chained": chained,
+             "timed_region": {"blocks": len(per_step), "steps_per_block": args.steps,
+                              "ms_per_step_median": ms_per_step, "ms_per_step_min": min(per_step),
+                              "ms_per_step_max": max(per_step), "seconds": sum(per_step) * args.steps * 1e-3},
+             "read_only_pass": {"GB/s": read_only_gbs, "kernel": "checksum_kernel over the 32 weight buffers",
+                                "frac_of_copy_peak": read_only_gbs / peak}}
     if n > 1:
-        # the other ways of exchanging y, timed the same way, for comparison
-        for other in ("peer", "peer-launches", "peer-barrier", "nccl"):
-            if other == args.exchange:
-                continue
-            step_device(other)
-            torch.cuda.synchronize()
-            og = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(og, stream=stream):
-                step_device(other)
-            for _ in range(3):
-                og.replay()
-            barrier()
-            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            o0.record(stream)
-            for _ in range(args.steps):
-                og.replay()
-            o1.record(stream)
-            barrier()
-            t = torch.tensor([o0.elapsed_time(o1)], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            other_ms = float(t.item()) / args.steps
-            extra[f"exchange_{other}"] = {"ms_per_step": other_ms, "GB/s": bytes_per_step / (other_ms * 1e-3) / 1e9}
         extra["kernels_only"] = {"us_per_list_launch": launch_us, "GB/s_per_gpu": achieved}
-        note("exchange variants timed")
+        # NCCL's all-gather after every product (the wording of the configuration), launched eagerly: no NCCL
+        # kernel is ever captured in a CUDA graph here
+        y_t = [torch.empty(ROWS, device=dev, dtype=torch.float32) for _ in range(LAYERS)]
+
+        def step_nccl():
+            for l in range(LAYERS):
+                _lib.check(lib.vx_gemv_q_rows(be._ctx, layers[l]._h, 0, shard, x_dev.data_ptr(), COLS,
+                                              y_t[l].data_ptr() + row0 * 4, shard, 1))
+                dist.all_gather_into_tensor(y_t[l], y_t[l][row0:row0 + shard])
+        for _ in range(3):
+            step_nccl()
+        barrier()
+        n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0.record(stream)
+        for _ in range(max(3, min(args.steps, 10))):
+            step_nccl()
+        n1.record(stream)
+        barrier()
+        nccl_ms = max_over_ranks([n0.elapsed_time(n1)])[0] / max(3, min(args.steps, 10))
+        nccl_same = bool(np.array_equal(y_t[5].cpu().numpy().view(np.uint32), y_host[5].view(np.uint32)))
+        extra["nccl_all_gather"] = {"ms_per_step": nccl_ms, "GB/s": bytes_per_step / (nccl_ms * 1e-3) / 1e9,
+                                    "launch": "eager (no graph)", "same_bits_as_fused": nccl_same}
+        check["ok"] = check["ok"] and nccl_same
+        note("NCCL form timed")
         # (the headline numbers above must not be lost to a failure in this side measurement: every rank
         # runs the same code, so a library error raises on all of them alike)
         try:
@@ -411,14 +558,15 @@ def run_ours(args):
     cpu = None
     if rank == 0 and n == 1:
         try:
-            extra = side_configs(be, lib, torch, stream)
+            extra.update(side_configs(be, lib, torch, stream))
         except _lib.VortxError as e:
-            extra = {"side_configs_failed": str(e)}
+            extra["side_configs_failed"] = str(e)
         try:
             gbs, dt, threads = cpu_gemv_rate(blocks, ROWS, steps=5, warmup=1)
             cpu = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
                    "sample": f"5 x {CPU_GEMVS_PER_STEP} GEMVs of {ROWS} x {COLS} Q4_0 (the step has {LAYERS}); "
                              "C++ restatement of the GEMV, not khal"}
+            extra["cpu_baselines"] = cpu_side_baselines(o, threads)
         except Exception as e:  # the oracle is test infrastructure; its absence must not hide the GPU numbers
             cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {e}"}
 
@@ -428,35 +576,84 @@ def run_ours(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "q4_0 x f32 (24-bit fixed point) -> f32",
             "data": "synthetic",
-            "config": {"workload": "q4_0_gemv_28672x8192_x32", "rows": ROWS, "cols": COLS, "batch": 1,
+            "config": {"workload": WORKLOAD, "rows": ROWS, "cols": COLS, "batch": 1,
                        "gemv_per_step": LAYERS,
-                       "sharding": (f"rows/{n} per GPU; y exchanged by " + EXCHANGE_TEXT[args.exchange]) if n > 1 else "none",
+                       "sharding": (f"rows/{n} per GPU; every row stored into the y of every GPU by the kernel's epilogue "
+                                    "(NVLink stores), one barrier kernel per step") if n > 1 else "none",
+                       "dependencies": "32 independent products per step at every N (the chained form: extra.chained)",
                        "l2": "inputs larger than L2: 32 weight copies walked in turn",
-                       "launch": "CUDA graph replay; the 32 products of a step are one persistent list launch"},
+                       "launch": "CUDA graph replay; the 32 products of a step are one persistent list launch",
+                       "timed": f"median of {len(per_step)} blocks of {args.steps} steps"},
+            "check": check,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": LAYERS * COLS * 4, "d2h_bytes_per_step": LAYERS * ROWS * 4},
-            "gpu_launches": launches_per_step * args.steps,
+                    "h2d_bytes_per_step": LAYERS * COLS * 4, "d2h_bytes_per_step": LAYERS * ROWS * 4,
+                    "what": "per step: 32 x vectors up from pinned memory, the list launch"
+                            + (" + barrier kernel" if n > 1 else "") + ", every product down to rank 0's host"
+                            + (" (the other ranks read back the rows they computed)" if n > 1 else "")},
+            "gpu_launches": launches_per_step * args.steps * len(per_step),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": f"{peak_kind} HBM copy bandwidth", "datasheet_peak": 8000.0,
-                         "frac_datasheet": achieved / 8000.0, "kernel": "gemv_stream_kernel",
+                         "peak_source": f"{peak_kind} HBM copy bandwidth (read + write)", "datasheet_peak": 8000.0,
+                         "frac_datasheet": achieved / 8000.0, "read_only_peak": read_only_gbs,
+                         "frac_read_only": achieved / read_only_gbs, "kernel": "gemv_stream_kernel (list launch)",
                          "bytes_per_launch": list_bytes, "us_per_launch": launch_us, "gemvs_per_launch": LAYERS,
                          "one_gemv_per_launch": {"us_per_launch": separate_us, "bytes_per_launch": shard_bytes,
                                                  "achieved": shard_bytes / (separate_us * 1e-6) / 1e9},
-                         "traffic": LAYERS * 135_400_000 if n == 1 else None,
-                         "traffic_source": "ncu dram__bytes_read + write of one 28672 x 8192 product (135.4 MB, profiles/gemv_stream_q4_0_28672x8192.md) x the 32 products of the list launch"},
+                         "traffic": LAYERS * NCU_TRAFFIC_PER_PRODUCT if n == 1 else None,
+                         "traffic_source": "ncu dram__bytes_read + dram__bytes_write of a list launch of 8 products "
+                                           "(1060.5 MB) scaled by 32 / 8: every product reads its own matrix once"},
             "clocks": clocks,
             "extra": extra,
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
         emit(line)
+
+    # ---- leave cleanly: lists and graphs first (a CUDA graph that captured work keeps references alive), then the
+    # IPC mappings, then a last barrier with nothing in flight.  The process group is not torn down collectively:
+    # every rank is past the barrier, has nothing in flight and holds no NVLS binding, and simply exits.
+    for b in (value_batch, chain_batch, plain_batch, e2e_batch):
+        b.free()
+    graphs.clear()
+    graph = chain_graph = None
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
     if n > 1:
-        # NCCL's communicator teardown was seen to hang on this pool's boxes after all work had
-        # completed; every rank has synchronised and rank 0 has printed, so leave without it.
+        dist.barrier()
+        for pb in [y_all, flags] + vecs:
+            pb.close()
         barrier()
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+def cpu_side_baselines(o, threads):
+    """The CPU restatement on the other configurations, each a bounded sample with all host threads (reported
+    baselines, not targets): the tiled GEMM at 1024^3 and 2048^3, the Q8_0 GEMV 4096^2, the Q4_0 GEMV 8192^2."""
+    from vortx_b200 import synth
+    out = {"cores": threads, "kind": "port", "note": "C++ restatement of vortx-shaders on the host cores, not khal"}
+    for dim, reps in ((1024, 3), (2048, 1)):
+        a, b = synth.uniform_matrix(dim, dim, 0), synth.uniform_matrix(dim, dim, 1)
+        c = np.zeros(dim * dim, np.float32)
+        sh = o.shape_contiguous(1, 1, dim, dim)
+        o.gemm_tiled(c, a.ravel(), b.ravel(), sh, sh, sh, nthreads=threads)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            o.gemm_tiled(c, a.ravel(), b.ravel(), sh, sh, sh, nthreads=threads)
+        dt = (time.perf_counter() - t0) / reps
+        out[f"gemm_tiled_{dim}"] = {"ms": dt * 1e3, "GFLOP/s": 2 * dim ** 3 / dt / 1e9, "sample": f"{reps} call(s) after one warm-up"}
+    out["gemm_tiled_8192"] = "skipped: minutes per call with this SIMT-shaped code"
+    for name, qt, dim, bb in (("q8_0_gemv_4096x4096", o.Q8_0, 4096, 34), ("q4_0_gemv_8192x8192", o.Q4_0, 8192, 18)):
+        blocks = o.quantize(qt, synth.normal_matrix(dim, dim, seed=0))
+        x = synth.normal_vectors(1, dim, seed=1)[0]
+        o.gemv(qt, blocks, dim, dim, x, nthreads=threads)
+        t0 = time.perf_counter()
+        for _ in range(10):
+            o.gemv(qt, blocks, dim, dim, x, nthreads=threads)
+        dt = (time.perf_counter() - t0) / 10
+        out[name] = {"ms": dt * 1e3, "GB/s": gemv_bytes(dim, dim, 1, 1, bb) / dt / 1e9, "sample": "10 calls after one warm-up"}
+    return out
 
 
 def sharded_gemm_numbers(be, torch, dist, stream, world, rank, barrier):
@@ -602,6 +799,71 @@ def side_configs(be, lib, torch, stream):
             us = time_graph(fn, 1, reps=3)
             be.set_option("gemm.tf32.tma_store", 1)
             out[name]["plain_store_epilogue"] = {"us": us, "TFLOP/s": 2 * dim ** 3 / us / 1e6}
+            # sustained: the same product back to back for at least a second (the burst figure above is three calls)
+            reps = max(10, int(1.2e6 / us))
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(reps):
+                fn()
+            b.record(stream)
+            torch.cuda.synchronize()
+            sus = a.elapsed_time(b) * 1e3 / reps
+            out[name]["sustained"] = {"us": sus, "TFLOP/s": 2 * dim ** 3 / sus / 1e6, "calls": reps,
+                                      "seconds": sus * reps * 1e-6}
+            # cuBLAS TF32 on the same inputs (torch.matmul with TF32 allowed): the library figure beside ours
+            prev = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = True
+            try:
+                for _ in range(3):
+                    torch.matmul(A, B, out=Cm)
+                torch.cuda.synchronize()
+                a.record(stream)
+                for _ in range(3):
+                    torch.matmul(A, B, out=Cm)
+                b.record(stream)
+                torch.cuda.synchronize()
+                cb = a.elapsed_time(b) * 1e3 / 3
+                reps_c = max(10, int(1.2e6 / cb))
+                a.record(stream)
+                for _ in range(reps_c):
+                    torch.matmul(A, B, out=Cm)
+                b.record(stream)
+                torch.cuda.synchronize()
+                cs = a.elapsed_time(b) * 1e3 / reps_c
+                out[name]["cublas_tf32"] = {"us": cb, "TFLOP/s": 2 * dim ** 3 / cb / 1e6,
+                                            "sustained_us": cs, "sustained_TFLOP/s": 2 * dim ** 3 / cs / 1e6}
+            finally:
+                torch.backends.cuda.matmul.allow_tf32 = prev
+        del A, B, Cm
+
+    # The reference example's sweep (examples/gemm_bench.rs:29, :70-115): naive against tiled at every size, 3 warm-up
+    # and 10 timed calls with a synchronise after each, wall clock; the tensor-core kernel beside them.
+    sweep = []
+    for dim in (64, 128, 256, 512, 768, 1024, 1536, 2048, 4096):
+        A = torch.rand(dim, dim, device="cuda") * 2 - 1
+        B = torch.rand(dim, dim, device="cuda") * 2 - 1
+        Cm = torch.empty(dim, dim, device="cuda")
+        sh = _lib.VxShapes3()
+        for s in (sh.out, sh.lhs, sh.rhs):
+            s.n = s.c = 1
+            s.h = s.w = dim
+            s.n_stride = s.c_stride = dim * dim
+            s.h_stride, s.w_stride = dim, 1
+        row = {"size": dim}
+        for label, mode in (("naive_ms", _lib.VX_GEMM_NAIVE), ("tiled_ms", _lib.VX_GEMM_SIMT_EXACT), ("tf32_ms", _lib.VX_GEMM_TF32)):
+            def call():
+                _lib.check(lib.vx_gemm_f32(be._ctx, mode, Cm.data_ptr(), A.data_ptr(), B.data_ptr(), C.byref(sh), 0, 0, 0))
+                be.synchronize()
+            for _ in range(3):
+                call()
+            t0 = time.perf_counter()
+            for _ in range(10):
+                call()
+            row[label] = (time.perf_counter() - t0) * 1e3 / 10
+        row["speedup_tiled_over_naive"] = row["naive_ms"] / row["tiled_ms"]
+        sweep.append(row)
+        del A, B, Cm
+    out["gemm_bench_sweep"] = {"protocol": "3 warm-up + 10 timed calls, synchronise after each, wall clock", "rows": sweep}
     return out
 
 

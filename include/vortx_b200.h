@@ -68,6 +68,11 @@ VX_API vx_status vx_free(vx_context* ctx, void* device_ptr);
 VX_API vx_status vx_upload(vx_context* ctx, void* device_dst, const void* host_src, size_t bytes);
 /* backend.slow_read_buffer(buf, host) — src/linalg/gemm.rs:423-426.  Blocks until done. */
 VX_API vx_status vx_download(vx_context* ctx, void* host_dst, const void* device_src, size_t bytes);
+/* slow_read_buffer of a strided view (src/tensor/tensor_ref.rs:101-103 carries the offset, the layout the
+ * row stride): `rows` pieces of `width_bytes`, src_pitch bytes apart on the device, land dst_pitch bytes
+ * apart on the host, in one copy.  Blocks until done. */
+VX_API vx_status vx_download_2d(vx_context* ctx, void* host_dst, size_t dst_pitch, const void* device_src,
+                                size_t src_pitch, size_t width_bytes, size_t rows);
 /* encoder.copy_buffer_to_buffer(src, src_off, dst, dst_off, len) —
  * src/tensor/tensor_impl.rs:207-213.  Offsets are applied by the caller. */
 VX_API vx_status vx_copy(vx_context* ctx, void* device_dst, const void* device_src, size_t bytes);
@@ -145,8 +150,15 @@ VX_API vx_status vx_qweights_info(const vx_qweights* w, int32_t* qtype, size_t* 
                                   size_t* device_bytes);
 /* Device dequantisation into a row-major f32 matrix (rows*cols floats). */
 VX_API vx_status vx_dequantize(vx_context* ctx, const vx_qweights* w, float* device_out);
-/* y[v*y_stride + r] = sum_c W[r, c] * x[v*x_stride + c], v < batch, f32 accumulation.
- * x and y are device pointers; strides in elements between batch vectors. */
+/* y[v*y_stride + r] = sum_c W[r, c] * x[v*x_stride + c], v < batch.
+ * x and y are device pointers; strides in elements between batch vectors.
+ * Arithmetic of the default kernel: each 16-byte chunk of a row (32 Q4_0 / 16 Q8_0 weights) is multiplied
+ * with x held as 24-bit fixed point relative to the largest |x| of that chunk; the integer sum of a chunk
+ * is exact, and the chunk sums, scaled by d * sx, are accumulated in f32.  An x value therefore carries an
+ * absolute error of up to 2^-24 of its chunk's largest value: the same as f32 for values near the chunk's
+ * maximum, coarser for values far below it (a 1e-3 next to a 1e4 keeps about 1 significant bit; an f32
+ * accumulation would lose the same value in the rounding of the sum).  A NaN or infinity in x makes every
+ * row NaN.  The result is within 1e-4 (max-norm relative) of the f64 product at the sizes tested. */
 VX_API vx_status vx_gemv_q(vx_context* ctx, const vx_qweights* w, const float* x, size_t x_stride,
                            float* y, size_t y_stride, size_t batch);
 /* Same, for a contiguous slab of rows [row0, row0+nrows): y receives nrows values per vector. */
@@ -282,8 +294,9 @@ VX_API vx_status vx_reduce(vx_context* ctx, vx_reduce_op op, vx_dtype dtype, vx_
  * live in a fixed 4 KB array inside the library's device image instead of allocated scratch.
  *   - At most 67 108 864 elements (1024 partials x 65 536 elements per block); more is refused
  *     with VX_ERR_UNSUPPORTED.
- *   - The first call on each device looks up the array's device address; make that first call
- *     before any stream capture on that device.
+ *   - The first call on each device looks up the array's device address and loads the code of every
+ *     kernel the entry point can launch (any operation, any type); make that first call before any
+ *     stream capture on that device.  Later calls on that device load and allocate nothing.
  *   - All calls share the one array: two calls whose kernels can overlap on the GPU (different
  *     streams, no dependency) race.  Nothing needs clearing between calls.
  * Results equal those of vx_reduce(.., VX_REDUCE_WIDE, ..): identical for integers and for
@@ -311,6 +324,16 @@ VX_API vx_status vx_contiguous(vx_context* ctx, void* dest, uint64_t cap_dest, c
  * result[it_r(id)] = source[it_s(id mod source sizes)]. */
 VX_API vx_status vx_repeat(vx_context* ctx, float* result, const vx_shape* shape_result, uint64_t cap_result,
                            const float* source, const vx_shape* shape_source, uint64_t cap_source);
+
+/* ------------------------------------------------------------------ checksum ---- */
+/* No reference counterpart.  One read-only pass over a device buffer (16-byte aligned, a whole number of
+ * 16-byte groups): *device_out receives the XOR of all its 32-bit words, word j of each group rotated
+ * left by 8 j bits.  Stream-ordered.  It verifies an upload without a read-back (compare with the same
+ * fold of the host bytes), and, as a kernel that only reads, it is the read-only HBM bandwidth probe of
+ * the benchmark. */
+VX_API vx_status vx_checksum_u32(vx_context* ctx, const void* device_ptr, size_t bytes, uint32_t* device_out);
+/* The same fold over the device form of quantised weights (both planes and their zero padding). */
+VX_API vx_status vx_qweights_checksum(vx_context* ctx, const vx_qweights* w, uint32_t* device_out);
 
 /* ----------------------------------------------------------------- tuning ---- */
 /* Integer knobs for experiments ("gemv.variant", "gemv.rows_per_warp", "gemm.tf32.stages"...).

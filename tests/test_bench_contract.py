@@ -32,3 +32,14 @@ def test_reference_arm_prints_one_json_line():
 
 def test_reference_arm_other_ranks_stay_silent():
     assert _run({"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"}, ("--gpus", "2")) == []
+
+
+def test_reference_arm_never_loads_the_product_library():
+    """The CPU arm quantises with the oracle's own quantiser and times the oracle: libvortx_b200.so is not mapped."""
+    code = ("import sys, runpy; sys.argv = ['bench.py', '--impl', 'reference', '--steps', '1', '--warmup', '0']\n"
+            "try:\n    runpy.run_path('bench.py', run_name='__main__')\nexcept SystemExit:\n    pass\n"
+            "maps = open('/proc/self/maps').read()\n"
+            "assert 'libvortx_oracle' in maps\n"
+            "assert 'libvortx_b200' not in maps, 'the reference arm mapped the product library'\n")
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert res.returncode == 0, res.stderr[-2000:]

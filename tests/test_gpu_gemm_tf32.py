@@ -105,6 +105,54 @@ def test_tf32_4096_against_simt(backend, tile_m):
     assert _rel_fro(got, ref) <= TOL
 
 
+def test_tf32_8192_against_simt(backend):
+    """The size the GEMM figures are quoted on: 8192^3, A and B uniform [-1, 1) from seeds 0 and 1, tensor-core
+    result against the exact SIMT result at 5e-3 relative Frobenius; and the column panels 2 / 4 / 8 GPUs would
+    compute, run here one after the other into one C, give the same bits as the unsharded product."""
+    import ctypes as C
+    lib = _lib.load()
+    dim = 8192
+    A = synth.uniform_matrix(dim, dim, seed=0)
+    B = synth.uniform_matrix(dim, dim, seed=1)
+    ad, bd = backend.init_buffer(A.ravel()), backend.init_buffer(B.ravel())
+    c_tf32, c_simt, c_panels = (backend.uninit_buffer(dim * dim) for _ in range(3))
+
+    def shapes(ncols):
+        sh = _lib.VxShapes3()
+        for s, (h, w, hs) in ((sh.out, (dim, ncols, dim)), (sh.lhs, (dim, dim, dim)), (sh.rhs, (dim, ncols, dim))):
+            s.n = s.c = 1
+            s.h, s.w = h, w
+            s.n_stride = s.c_stride = h * hs
+            s.h_stride, s.w_stride = hs, 1
+        return sh
+
+    sh = shapes(dim)
+    _lib.check(lib.vx_gemm_f32(backend._ctx, _lib.VX_GEMM_TF32, c_tf32.ptr, ad.ptr, bd.ptr, C.byref(sh), 0, 0, 0))
+    assert vb.Gemm.last_kernel(backend) == "tcgen05_tf32"
+    _lib.check(lib.vx_gemm_f32(backend._ctx, _lib.VX_GEMM_SIMT_EXACT, c_simt.ptr, ad.ptr, bd.ptr, C.byref(sh), 0, 0, 0))
+    got, ref = np.empty(dim * dim, np.float32), np.empty(dim * dim, np.float32)
+    backend.slow_read_buffer(c_tf32, got)
+    backend.slow_read_buffer(c_simt, ref)
+    rel = _rel_fro(got, ref)
+    print("TF32 against SIMT at 8192^3: relative Frobenius error", rel)
+    assert rel <= TOL
+    # a row of the exact result against the f64 product, to tie the comparison to something outside the library
+    row64 = A[77].astype(np.float64) @ B.astype(np.float64)
+    assert np.abs(ref.reshape(dim, dim)[77] - row64).max() <= 1e-3
+    panels = np.empty(dim * dim, np.float32)
+    for world in (2, 4, 8):
+        ncols = dim // world
+        shp = shapes(ncols)
+        _lib.check(lib.vx_memset(backend._ctx, c_panels.ptr, 0xFF, dim * dim * 4))
+        for r in range(world):
+            _lib.check(lib.vx_gemm_f32(backend._ctx, _lib.VX_GEMM_TF32, c_panels.ptr + r * ncols * 4, ad.ptr,
+                                       bd.ptr + r * ncols * 4, C.byref(shp), 0, 0, 0))
+        backend.slow_read_buffer(c_panels, panels)
+        assert _rel_fro(panels, ref) <= TOL, world
+        # the same tensor-core arithmetic per element (k order and tile height do not depend on the panel width)
+        assert np.array_equal(panels.view(np.uint32), got.view(np.uint32)), world
+
+
 @pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 200), (129, 72, 40), (1024, 2048, 512)])
 def test_tf32_scatter_epilogue_writes_every_destination(backend, m, n, k):
     """vx_gemm_tf32_scatter with two further buffers of the SAME GPU standing in for peers: the epilogue's tiled TMA

@@ -1,8 +1,9 @@
-"""Two GPUs, one process each: the row-sharded GEMV whose epilogue stores y into the peer's memory, followed
-by the cross-GPU barrier kernel, against the CPU oracle; and the NCCL all-gather form of the same product.
+"""2, 4 and 8 GPUs, one process each: the row-sharded GEMV whose epilogue stores y into the peers' memory, followed
+by the cross-GPU barrier kernel, against the CPU oracle; the NCCL all-gather form of the same product; chains of
+dependent products with the exchange fused into the kernel; the column-sharded TF32 GEMM.
 
-Skipped on a box with one GPU.  Ranks are child processes; each leaves only after a final host barrier, with
-no kernel in flight."""
+Every test runs at each world size the box has GPUs for and is skipped otherwise.  Ranks are child processes;
+each leaves only after a final host barrier, with no kernel in flight."""
 import os
 import socket
 
@@ -83,7 +84,7 @@ def _worker(rank, world, port, out_dir):
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **results)
     dist.barrier()
     be.close()
-    os._exit(0)   # skip NCCL teardown, which has hung on these boxes after all work was done
+    os._exit(0)   # every rank is past the final barrier with nothing in flight; no communicator teardown
 
 
 def _chain_worker(rank, world, port, out_dir):
@@ -179,6 +180,19 @@ def _chain_worker(rank, world, port, out_dir):
     results["window_want"], results["window_got"] = want, got
     batch.free()
     dist.barrier()
+    # the same chain WITHOUT a window reads the vector's first `cols` elements: rows of the first ranks only.  A rank
+    # none of whose rows is among them would never be waited for; the library must refuse its list, launching nothing.
+    before = be.launch_count()
+    try:
+        bad = g.chain_batch([mine] * wl, xd.ptr, window=False)
+        bad.free()
+        results["unwindowed_refused"] = np.array([0])
+    except _lib.VortxError as e:
+        assert e.status == _lib.VX_ERR_UNSUPPORTED, e
+        results["unwindowed_refused"] = np.array([1])
+    assert be.launch_count() == before
+    results["row0"] = np.array([g.row0])
+    dist.barrier()
     g.close()
     np.savez(os.path.join(out_dir, f"chain{rank}.npz"), **results)
     dist.barrier()
@@ -202,11 +216,19 @@ def _run_ranks(target, world, out_dir):
         assert p.exitcode == 0
 
 
-@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-def test_chained_gemv_with_fused_exchange_on_two_gpus(tmp_path, oracle):
+WORLDS = [2, 4, 8]
+
+
+def _need(world):
+    if _gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_chained_gemv_with_fused_exchange(tmp_path, oracle, world):
     import vortx_b200 as vb
     from vortx_b200 import synth
-    world = 2
+    _need(world)
     _run_ranks(_chain_worker, world, str(tmp_path))
     n, links = 2048, 6
     w = synth.normal_matrix(n, n, seed=31) * np.float32(50.0 / 45.0)
@@ -231,26 +253,16 @@ def test_chained_gemv_with_fused_exchange_on_two_gpus(tmp_path, oracle):
     for r in range(world):
         assert np.array_equal(got[r]["window_got"].view(np.uint32), got[r]["window_want"].view(np.uint32))
         assert np.isfinite(got[r]["window_got"]).all() and np.abs(got[r]["window_got"]).max() > 0
+        # 4096 rows, 2048 columns: only ranks whose slab starts below row 2048 are among the awaited elements
+        assert int(got[r]["unwindowed_refused"][0]) == (1 if int(got[r]["row0"][0]) >= 2048 else 0), r
 
 
-@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-def test_peer_scatter_and_nccl_gemv_on_two_gpus(tmp_path, oracle):
-    import torch.multiprocessing as mp
+@pytest.mark.parametrize("world", WORLDS)
+def test_peer_scatter_and_nccl_gemv(tmp_path, oracle, world):
     import vortx_b200 as vb
     from vortx_b200 import synth
-    world = 2
-    ctx = mp.get_context("spawn")
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, str(tmp_path))) for r in range(world)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=240)
-    for p in procs:
-        if p.is_alive():
-            p.kill()          # the exact child started above
-            pytest.fail("a rank did not finish in time")
-        assert p.exitcode == 0
+    _need(world)
+    _run_ranks(_worker, world, str(tmp_path))
     rows, cols, slots = 1024, 2048, 3
     w = synth.normal_matrix(rows, cols, seed=21)
     xs = synth.normal_vectors(slots, cols, seed=22)
@@ -308,9 +320,9 @@ def _gemm_worker(rank, world, port, out_dir):
 GEMM_CASES = [(512, 512, 256), (300, 1024, 200), (1024, 2048, 1024), (200, 1000, 96), (129, 72, 40)]
 
 
-@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-def test_column_sharded_tf32_gemm_on_two_gpus(tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", WORLDS)
+def test_column_sharded_tf32_gemm(tmp_path, world):
+    _need(world)
     _run_ranks(_gemm_worker, world, str(tmp_path))
     got = [np.load(tmp_path / f"gemm{r}.npz") for r in range(world)]
     for m, n, k in GEMM_CASES:
@@ -326,3 +338,113 @@ def test_column_sharded_tf32_gemm_on_two_gpus(tmp_path):
             if f"nccl_{key}" in got[r]:                             # equal panels only
                 assert np.array_equal(peer.view(np.uint32), got[r][f"nccl_{key}"].view(np.uint32))   # same kernel, same tiles
             assert np.array_equal(peer.view(np.uint32), got[0][f"peer_{key}"].view(np.uint32))   # one C everywhere
+
+
+# ------------------------------------------------- the benchmark's own shape, 28672 x 8192 Q4_0 ----
+
+BIG_ROWS, BIG_COLS, BIG_LINKS = 28672, 8192, 3
+
+
+def _big_slab(world, rank):
+    """Rank `rank`'s rows of the 28672 x 8192 matrix, each slab from its own seed (as the benchmark does)."""
+    from vortx_b200 import synth
+    return synth.normal_matrix(BIG_ROWS // world, BIG_COLS, seed=100 + rank) * np.float32(25.0 / 45.0)
+
+
+def _big_worker(rank, world, port, out_dir):
+    """Row slabs of the up-projection on `world` GPUs: (a) independent products whose rows the epilogue stores on
+    every GPU, completed by one barrier (what the benchmark times); (b) a chain of dependent products in one list
+    launch per GPU, x of link l the tail of every rank's slab of link l - 1 (the benchmark's chained form)."""
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import vortx_b200 as vb
+    from vortx_b200 import synth
+    from vortx_b200.multi_gpu import PeerScatterGemv
+    be = vb.Backend(rank)
+    qm = vb.QuantizedMatrix.from_f32(be, vb.Q4_0, _big_slab(world, rank))
+    xs = synth.normal_vectors(BIG_LINKS, BIG_COLS, seed=1)
+    xd = be.init_buffer(xs.ravel())
+    results = {}
+    g = PeerScatterGemv(be, BIG_ROWS, BIG_COLS, BIG_LINKS)
+    # (a) independent products, rows stored on every GPU by the epilogue, one barrier
+    batch = g.scatter_batch([qm] * BIG_LINKS, [xd.ptr + l * BIG_COLS * 4 for l in range(BIG_LINKS)])
+    for rep in range(2):
+        batch.launch()
+        g.finish()
+    be.synchronize()
+    y = np.empty(BIG_LINKS * BIG_ROWS, np.float32)
+    be.slow_read_buffer(g.y.local, y.view(np.uint8))
+    results["scatter"] = y.reshape(BIG_LINKS, BIG_ROWS).copy()
+    batch.free()
+    dist.barrier()
+    # (b) the chain; every link also leaves its own rows as plain f32 so that each link can be checked alone
+    plain = be.init_buffer(np.zeros(BIG_LINKS * g.nrows, np.float32))
+    entries = []
+    seg_len, seg_stride = BIG_COLS // world, BIG_ROWS // world
+    for l in range(BIG_LINKS):
+        e = {"w": qm, "nrows": g.nrows, "y": plain.ptr + l * g.nrows * 4, "y_xvec": g.vectors[l % 2].local.ptr,
+             "peers": [g.vectors[l % 2].ptrs[r] for r in g._others], "y_row0": g.row0, "y_stride": 1}
+        if l == 0:
+            e["x"] = xd.ptr
+        else:
+            e["x_xvec"] = g.vectors[(l - 1) % 2].local.ptr
+            e["x_seg_len"], e["x_seg_stride"], e["x_seg_first"] = seg_len, seg_stride, seg_stride - seg_len
+        entries.append(e)
+    chain = vb.GemvBatch(be, entries)
+    for rep in range(3):
+        chain.launch()
+        g.unpack((BIG_LINKS - 1) % 2, g.y_ptr(0))
+    be.synchronize()
+    be.slow_read_buffer(g.y.local, y.view(np.uint8))
+    results["chain_last"] = y[:BIG_ROWS].copy()                       # the whole last vector, as this GPU received it
+    mine = np.empty(BIG_LINKS * g.nrows, np.float32)
+    be.slow_read_buffer(plain, mine)
+    results["chain_rows"] = mine.reshape(BIG_LINKS, g.nrows)
+    chain.free()
+    dist.barrier()
+    g.close()
+    np.savez(os.path.join(out_dir, f"big{rank}.npz"), **results)
+    dist.barrier()
+    be.close()
+    os._exit(0)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_q4_0_28672x8192_sharded_over_the_gpus(tmp_path, oracle, world):
+    import vortx_b200 as vb
+    from vortx_b200 import synth
+    _need(world)
+    _run_ranks(_big_worker, world, str(tmp_path))
+    got = [np.load(tmp_path / f"big{r}.npz") for r in range(world)]
+    shard = BIG_ROWS // world
+    blocks = [vb.quantize(vb.Q4_0, _big_slab(world, r)) for r in range(world)]
+    xs = synth.normal_vectors(BIG_LINKS, BIG_COLS, seed=1)
+
+    def product(x):
+        parts = [oracle.gemv_f64(vb.Q4_0, blocks[r], shard, BIG_COLS, x[None, :]) for r in range(world)]
+        return np.concatenate([p[0][0] for p in parts]), np.concatenate([p[1][0] for p in parts])
+
+    # (a) every GPU holds every product, all of it
+    for l in range(BIG_LINKS):
+        y64, absdot = product(xs[l])
+        for r in range(world):
+            y = got[r]["scatter"][l]
+            assert np.abs(y - y64).max() / np.abs(y64).max() <= 1e-4, (l, r)
+            assert (np.abs(y - y64) <= 2e-6 * absdot).all(), (l, r)
+            assert np.array_equal(y.view(np.uint32), got[0]["scatter"][l].view(np.uint32))
+    # (b) link by link: each link against the oracle applied to the x the GPUs actually used
+    seg_len = BIG_COLS // world
+    x = xs[0]
+    for l in range(BIG_LINKS):
+        y64, absdot = product(x)
+        y = np.concatenate([got[r]["chain_rows"][l] for r in range(world)])
+        assert np.abs(y - y64).max() / np.abs(y64).max() <= 1e-4, l
+        assert (np.abs(y - y64) <= 2e-6 * absdot).all(), l
+        x = np.concatenate([y[(r + 1) * shard - seg_len:(r + 1) * shard] for r in range(world)])   # the slabs' tails
+    for r in range(world):
+        assert np.array_equal(got[r]["chain_last"].view(np.uint32), y.view(np.uint32)), r          # one vector everywhere

@@ -125,3 +125,77 @@ def test_column_sharded_gemm_relayout_gives_the_unsharded_product(tmp_path, worl
     for r in range(world):
         got = np.load(tmp_path / f"c{r}.npy")
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), r
+
+
+# ------------------------------------------------------------------ a rank that leaves ----
+
+from vortx_b200.multi_gpu import PeerLost, RankWatch  # noqa: E402
+
+
+def _leaving_worker(rank, world, port, out_dir):
+    """Three steps of a sharded product; rank `world - 1` leaves, between steps, after the first.  The others
+    must learn of it on the host before they launch step 2 (PeerLost), not by hanging in a collective."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    watch = RankWatch.for_default_group()
+    steps_done, error = 0, ""
+    try:
+        for step in range(1, 4):
+            if rank == world - 1 and step == 2:
+                watch.leave()                      # between steps, nothing in flight
+                break
+            watch.announce(step)
+            watch.await_all(step, timeout_s=5.0)
+            t = torch.full((4,), float(rank + step))
+            parts = [torch.empty(4) for _ in range(world)]
+            dist.all_gather(parts, t)              # the step's exchange
+            assert [float(p[0]) for p in parts] == [float(r + step) for r in range(world)]
+            steps_done = step
+    except PeerLost as e:
+        error = str(e)
+    with open(os.path.join(out_dir, f"leave{rank}.txt"), "w") as f:
+        f.write(f"{steps_done}|{error}")
+    # rank 0 hosts the store: it stays until the others have written their result
+    if rank == 0:
+        import time
+        deadline = time.monotonic() + 15
+        while time.monotonic() < deadline and not all(
+                os.path.exists(os.path.join(out_dir, f"leave{r}.txt")) for r in range(world)):
+            time.sleep(0.01)
+    os._exit(0)      # no collective teardown with a rank missing
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_a_rank_that_leaves_between_steps_is_noticed_on_the_host(tmp_path, world):
+    import time
+    t0 = time.monotonic()
+    mp.spawn(_leaving_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert time.monotonic() - t0 < 60
+    for r in range(world):
+        done, error = (tmp_path / f"leave{r}.txt").read_text().split("|", 1)
+        if r == world - 1:
+            assert (done, error) == ("1", "")
+        else:
+            assert done == "1" and f"rank {world - 1} has left the group before step 2" in error
+
+
+def test_a_rank_that_falls_silent_costs_one_timeout():
+    """No process group: the watch over a plain in-memory store.  A rank that never announces the step makes
+    await_all raise after its timeout, naming the rank."""
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v.encode()
+
+        def get(self, k):
+            return self[k]
+
+    st = Store()
+    a, b = RankWatch(st, 0, 2), RankWatch(st, 1, 2)
+    a.announce(1)
+    b.announce(1)
+    a.await_all(1, timeout_s=0.2)
+    a.announce(2)
+    with pytest.raises(PeerLost, match="rank 1 has not reached step 2"):
+        a.await_all(2, timeout_s=0.05)

@@ -83,3 +83,26 @@ def test_static_reduction_limits_and_errors(backend):
     r = np.ones(1, np.float32)
     backend.slow_read_buffer(out, r)
     assert r[0] == 0.0
+
+
+def test_static_reduction_leaves_device_memory_alone(backend):
+    """What the entry point is for: after the first call on a device (which looks the array's address up and
+    loads the code of every kernel it can launch), further calls, of any operation and type, change nothing in
+    the device's free memory."""
+    import torch
+    lib = _lib.load()
+    rng = np.random.Generator(np.random.Philox(12))
+    inputs = {dt: backend.init_buffer(rng.integers(1, 3, size=200_001).astype(dt)) for dt in (np.float32, np.uint32, np.int32)}
+    out = backend.init_buffer(np.zeros(1, np.float32))
+    shape = _shape(200_001)
+    stream = C.c_void_p(backend.stream)
+    _lib.check(lib.vx_reduce_static(backend.device, stream, 0, 0, inputs[np.float32].ptr, C.byref(shape), out.ptr))
+    backend.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(backend.device)
+    for rep in range(3):
+        for dt, code in ((np.float32, 0), (np.uint32, 1), (np.int32, 2)):
+            for op in range(5 if code == 0 else 4):
+                _lib.check(lib.vx_reduce_static(backend.device, stream, op, code, inputs[dt].ptr, C.byref(shape), out.ptr))
+    backend.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(backend.device)
+    assert free_after == free_before

@@ -133,6 +133,9 @@ SIGNATURES = {
     "vx_contiguous": (C.c_int32, [_P, _P, C.c_uint64, _P, C.POINTER(VxShape), C.c_uint64, C.c_uint32]),
     "vx_repeat": (C.c_int32, [_P, _P, C.POINTER(VxShape), C.c_uint64, _P, C.POINTER(VxShape), C.c_uint64]),
     "vx_op_assign_dispatch": (C.c_int32, [_P, C.c_int, C.c_int32, _P, _LP, C.c_uint64, _P, _LP, C.c_uint64]),
+    "vx_checksum_u32": (C.c_int32, [_P, _P, C.c_size_t, _P]),
+    "vx_qweights_checksum": (C.c_int32, [_P, _P, _P]),
+    "vx_download_2d": (C.c_int32, [_P, _P, C.c_size_t, _P, C.c_size_t, C.c_size_t, C.c_size_t]),
     "vx_set_option": (C.c_int32, [_P, C.c_char_p, C.c_int64]),
     "vx_get_option": (C.c_int32, [_P, C.c_char_p, C.POINTER(C.c_int64)]),
     # host mirror

@@ -25,6 +25,15 @@ int64_t option(const vx_context* ctx, const char* key, int64_t fallback) {
     return it == ctx->options.end() ? fallback : it->second;
 }
 
+cudaError_t device_malloc(vx_context* ctx, void** ptr, size_t bytes) {
+    auto it = ctx->options.find("debug.fail_alloc_after");
+    if (it != ctx->options.end() && it->second > 0 && --it->second == 0) {
+        *ptr = nullptr;
+        return cudaErrorMemoryAllocation;
+    }
+    return cudaMalloc(ptr, bytes);
+}
+
 static const char* const kKnownOptions[] = {
     "gemv.variant",       // 2 (default) = TMA streaming kernel; 0 / 1 = register-staged kernels
     "gemv.stages",        // ring depth of the streaming kernel (0 = as many as fit)
@@ -41,6 +50,8 @@ static const char* const kKnownOptions[] = {
     "gemm.tf32.round_nearest",  // 1 (default): TMA rounds A and B to TF32 to nearest on load; 0: the tensor core truncates
     "gemm.tf32.tile_m",   // 128 or 256 forces the tile height of the TF32 kernel (0 = by problem size)
     "bounds_check",       // 1 (default): refuse layouts that reach beyond the stated capacity
+    "wait_cycles",        // budget, in SM clocks, of the device-side waits on exchange vectors and peer barriers (0 = about 0.2 s)
+    "debug.fail_alloc_after",  // n > 0: the n-th device allocation from now fails as if the device were full (tests)
 };
 
 static bool known_option(const char* key) {
@@ -176,7 +187,7 @@ vx_status vx_alloc(vx_context* ctx, size_t bytes, void** device_ptr) {
     *device_ptr = nullptr;
     vx::DeviceGuard guard(ctx->device);
     // A zero-length tensor (Tensor::with_capacity(0), an emptied vector) still needs a handle.
-    VX_CUDA(cudaMalloc(device_ptr, bytes ? bytes : 16));
+    VX_CUDA(vx::device_malloc(ctx, device_ptr, bytes ? bytes : 16));
     return VX_OK;
 }
 
@@ -205,6 +216,19 @@ vx_status vx_download(vx_context* ctx, void* dst, const void* src, size_t bytes)
         VX_REQUIRE(dst && src, VX_ERR_INVALID_ARGUMENT, "vx_download: null pointer");
         vx::DeviceGuard guard(ctx->device);
         VX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return vx_synchronize(ctx);
+}
+
+vx_status vx_download_2d(vx_context* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                         size_t width_bytes, size_t rows) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_download_2d: null context");
+    if (width_bytes != 0 && rows != 0) {
+        VX_REQUIRE(dst && src, VX_ERR_INVALID_ARGUMENT, "vx_download_2d: null pointer");
+        VX_REQUIRE(dst_pitch >= width_bytes && src_pitch >= width_bytes, VX_ERR_INVALID_ARGUMENT,
+                   "vx_download_2d: pitches (%zu, %zu) shorter than a row of %zu bytes", dst_pitch, src_pitch, width_bytes);
+        vx::DeviceGuard guard(ctx->device);
+        VX_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDeviceToHost, ctx->stream));
     }
     return vx_synchronize(ctx);
 }

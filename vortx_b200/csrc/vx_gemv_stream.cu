@@ -28,6 +28,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <atomic>
 #include <memory>
 #include <vector>
 
@@ -92,6 +93,7 @@ struct StreamParams {
     uint32_t n_ops;          // up to kInlineOps: inline_ops; more: ops[] in device memory
     uint32_t block_wait;     // flagged x: one warp waits for the block (see the consumers)
     uint32_t n_vec;
+    long long wait_cycles;   // budget of the flagged-x waits, in SM clocks
     const OpParams* ops;
     uint32_t* vec_hdr[kMaxVecs];   // headers of the exchange vectors the list touches (own memory)
     uint32_t vec_writes[kMaxVecs]; // how often the list writes each of them
@@ -332,7 +334,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                                 all = all && (uint32_t)(pa[i] >> 32) == x_gen && (uint32_t)(pb[i] >> 32) == x_gen;
                         }
                         if (__all_sync(0xffffffffu, all)) break;
-                        if (*abort_flag != 0u || clock64() - start > kWaitCycles) break;   // the reads below report it
+                        // one decision for the whole warp: the lanes must leave the loop together
+                        if (__any_sync(0xffffffffu, *abort_flag != 0u || clock64() - start > p.wait_cycles)) break;   // the reads below report it
                     }
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
@@ -370,7 +373,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                             ok = ok && good != 0;
                         }
                         if (!ok) {
-                            if (*abort_flag != 0u || clock64() - start > kWaitCycles) break;
+                            if (*abort_flag != 0u || clock64() - start > p.wait_cycles) break;
                             // No __nanosleep here: measured on B200, a block whose warps sleep while they wait runs
                             // its next tiles about three times slower for tens of microseconds (a chained product
                             // took 33 us instead of 17.5 us when every block had to wait for the rows computed last).
@@ -396,12 +399,22 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
                     for (int i = 0; i < W; ++i) xv[i] = 0.0f;
                 }
-                float amax = 0.0f;
+                float amax = 0.0f, poison = 0.0f;
 #pragma unroll
-                for (int i = 0; i < W; ++i) amax = fmaxf(amax, fabsf(xv[i]));
+                for (int i = 0; i < W; ++i) {
+                    amax = fmaxf(amax, fabsf(xv[i]));
+                    poison = fmaf(xv[i], 0.0f, poison);   // NaN as soon as one value is NaN or infinite (fmaxf skips NaN)
+                }
                 // |x * inv| <= 8388606.5 before rounding, so X stays within 24 signed bits without a clamp.
-                const float inv = amax > 0.0f ? 8388606.0f / amax : 0.0f;
-                sxs[j] = valid ? amax / 8388606.0f : 0.0f;
+                float inv = amax > 0.0f ? 8388606.0f / amax : 0.0f;
+                float sx = amax / 8388606.0f;
+                // a chunk whose largest value is below 8388606 / FLT_MAX: the quotient would overflow; scale by
+                // an exact power of two instead (|X| stays below 2^23, sx * inv == 1)
+                if (amax > 0.0f && amax < 4.9e-32f) { inv = 0x1p126f; sx = 0x1p-126f; }
+                // a NaN or an infinity in x reaches every row as NaN, as it would through f32 products and sums
+                // of mixed signs (an f32 accumulation could also end on +-inf; this kernel does not tell them apart)
+                if (poison != poison) { inv = 0.0f; sx = poison; }
+                sxs[j] = valid ? sx : 0.0f;
                 int sa = 0, sb = 0, sc = 0;
 #pragma unroll
                 for (int r = 0; r < DR; ++r) {
@@ -509,11 +522,13 @@ template <int QT, int CPT, int RP, int TR, bool XCH, int NCW = 8>
 vx_status launch_one(vx_context* ctx, const StreamParams& p, dim3 grid, size_t smem) {
     auto kernel = gemv_stream_kernel<QT, CPT, RP, TR, XCH, NCW>;
     // Raise the dynamic shared-memory limit once per device and kernel instance.
-    static size_t granted[64] = {};
+    // (contexts of different devices may launch from different threads: the record is atomic, and setting
+    // the attribute twice is harmless)
+    static std::atomic<size_t> granted[64];
     const int dev = ctx->device & 63;
-    if (granted[dev] < smem) {
+    if (granted[dev].load(std::memory_order_acquire) < smem) {
         VX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        granted[dev] = smem;
+        granted[dev].store(smem, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -524,7 +539,11 @@ vx_status launch_one(vx_context* ctx, const StreamParams& p, dim3 grid, size_t s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 ? 1 : 0;
+    // Weights quantised on the device by the kernel just before this one (vx_qweights_from_device) are only
+    // guaranteed visible once that kernel has completed, and the producer warp reads weights before
+    // griddepcontrol.wait: such a launch is an ordinary, fully serialised one.
+    cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 && !ctx->weights_fresh ? 1 : 0;
+    ctx->weights_fresh = false;
     VX_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return VX_OK;
 }
@@ -627,6 +646,46 @@ void fill_common(StreamParams* p, const StreamConfig& c, uint32_t nchunks, uint3
     p->stage_bytes = c.stage_bytes;
     p->q_stage_bytes = c.q_stage;
     p->status = ctx->d_status;
+    p->wait_cycles = vx::wait_cycles(ctx);
+}
+
+// Which rows of a producing entry a reading entry waits for, and whether that covers every thread block.
+//
+// A flagged reader only waits for the elements it reads.  A block of the PRODUCING entry none of whose rows
+// are among them is never waited for: it may still be reading its own x (the vector written two entries
+// ago) when a faster rank, already one entry further, writes that vector again.  A chain over two vectors
+// is therefore only safe when every block that takes part in the producing entry owns at least one awaited
+// row: nobody can then run ahead of a block that has not finished reading.  Tiles are dealt out to blocks
+// in turn (see first_tile), so the test is per block, and a grid that fails it is shrunk until it passes.
+struct AwaitedRows {
+    // element e of the vector is awaited iff awaited(e); rows of the producer map to elements row0 + r * stride
+    uint64_t cols = 0, seg_len = 0, seg_stride = 0, seg_first = 0;
+    bool awaited(uint64_t e) const {
+        if (seg_len == 0) return e < cols;
+        const uint64_t s = e / seg_stride, o = e % seg_stride;
+        return s < cols / seg_len && o >= seg_first && o < seg_first + seg_len;
+    }
+};
+
+// true when, with `grid` blocks and tiles of `tr` rows, every block that has a tile of producer entry
+// `op_index` (nrows rows, row r at element y_row0 + r * y_stride) also has a tile with an awaited row.
+bool every_block_awaited(const AwaitedRows& a, uint32_t op_index, uint32_t nrows, uint64_t y_row0, uint64_t y_stride,
+                         uint32_t tr, uint32_t grid) {
+    const uint32_t tiles = (nrows + tr - 1) / tr;
+    const uint32_t rot = (uint32_t)(((uint64_t)op_index * (tiles % grid)) % grid);
+    std::vector<uint8_t> seen(grid, 0);
+    for (uint32_t t = 0; t < tiles; ++t) {
+        bool hit = false;
+        for (uint32_t r = t * tr; r < std::min(nrows, (t + 1) * tr) && !hit; ++r) hit = a.awaited(y_row0 + (uint64_t)r * y_stride);
+        if (hit) seen[(t + rot) % grid] = 1;
+    }
+    const uint32_t taking_part = std::min(tiles, grid);
+    uint32_t covered = 0;
+    for (uint32_t b = 0; b < grid; ++b) {
+        const uint32_t first = (b + grid - rot) % grid;   // first_tile of block b
+        if (first < tiles && seen[b]) ++covered;
+    }
+    return covered == taking_part;
 }
 
 void fill_plain_op(OpParams* o, const vx_qweights* w, size_t row0, uint32_t nrows, const float* x, float* y,
@@ -712,6 +771,22 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
     const uint32_t tiles = (nrows + c.tr - 1) / c.tr;
     const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * c.per_sm);
     dim3 grid(std::min(tiles, slots));
+    if (flagged && xch->y_vec) {
+        // The next link of the chain reads the first `cols` elements of the vector written here (every rank
+        // issues the same launches on matrices of one shape).  Every block of this grid must own one of those
+        // rows, or nobody ever waits for it and a faster rank could rewrite the vector it still reads as x.
+        AwaitedRows a;
+        a.cols = w->cols;
+        uint32_t g = grid.x;
+        while (g > 1 && !every_block_awaited(a, 0, nrows, xch->y_row0, xch->y_stride, c.tr, g)) --g;
+        if (!every_block_awaited(a, 0, nrows, xch->y_row0, xch->y_stride, c.tr, g))
+            return fail(VX_ERR_UNSUPPORTED,
+                        "vx_gemv_q_rows_exchange: none of rows [%zu, +%u) (stride %zu) lies among the first %zu elements "
+                        "the next link reads, so no rank would ever wait for this one; deal the rows out in turn "
+                        "(y_stride = world) or use a list with a windowed x",
+                        xch->y_row0, nrows, xch->y_stride, w->cols);
+        grid.x = g;
+    }
     const vx_status st = flagged ? launch_tr<true>(ctx, w->type, c, p, grid) : launch_tr<false>(ctx, w->type, c, p, grid);
     if (st != VX_OK) return st;
     ctx->launches++;
@@ -819,14 +894,52 @@ vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, size_t n_
     const uint32_t tiles = (max_rows + b->cfg.tr - 1) / b->cfg.tr;
     const uint32_t slots = (uint32_t)std::max<int64_t>(1, ctx->sm_count * b->cfg.per_sm);
     b->grid = dim3(std::min(tiles, slots));
+    if (b->flagged) {
+        // Every flagged read must wait for at least one row of every block of the entry that produces the
+        // vector (see AwaitedRows); the producer of entry i's x is the latest earlier entry that writes the
+        // vector, or, for a list that is launched again and again, the last one of the list that does.
+        auto producer_of = [&](size_t i) -> long {
+            for (size_t j = i; j-- > 0;)
+                if (ops[j].y_xvec == ops[i].x_xvec) return (long)j;
+            for (size_t j = n_ops; j-- > i + 1;)
+                if (ops[j].y_xvec == ops[i].x_xvec) return (long)j;
+            return -1;   // written outside this list
+        };
+        auto safe = [&](uint32_t g, size_t* reader, size_t* producer) {
+            for (size_t i = 0; i < n_ops; ++i) {
+                if (!ops[i].x_xvec) continue;
+                const long j = producer_of(i);
+                if (j < 0) continue;
+                AwaitedRows a;
+                a.cols = ops[i].w->cols;
+                a.seg_len = ops[i].x_seg_len;
+                a.seg_stride = ops[i].x_seg_stride;
+                a.seg_first = ops[i].x_seg_first;
+                if (!every_block_awaited(a, (uint32_t)j, (uint32_t)ops[j].nrows, ops[j].y_row0, ops[j].y_stride, b->cfg.tr, g)) {
+                    *reader = i;
+                    *producer = (size_t)j;
+                    return false;
+                }
+            }
+            return true;
+        };
+        size_t reader = 0, producer = 0;
+        uint32_t g = b->grid.x;
+        while (g > 1 && !safe(g, &reader, &producer)) --g;
+        VX_REQUIRE(safe(g, &reader, &producer), VX_ERR_UNSUPPORTED,
+                   "GEMV %zu reads none of the rows this rank produces in GEMV %zu, so no rank would ever wait for "
+                   "this one and the vectors could be rewritten under it: give x a window over every rank's slab "
+                   "(x_seg_*) or deal the rows out in turn (y_stride = world)", reader, producer);
+        b->grid.x = g;
+    }
     // few tiles per block and product: the blocks mostly wait for each other, let one warp do it
     const int64_t bw = vx::option(ctx, "gemv.block_wait", -1);
-    p.block_wait = bw >= 0 ? (bw != 0) : (tiles < 5 * slots ? 1u : 0u);
+    p.block_wait = bw >= 0 ? (bw != 0) : (tiles < 5 * b->grid.x ? 1u : 0u);
     vx::DeviceGuard guard(ctx->device);
     if (n_ops <= (size_t)kInlineOps) {
         for (size_t i = 0; i < n_ops; ++i) p.inline_ops[i] = host[i];
     } else {
-        VX_CUDA(cudaMalloc(&b->d_ops, n_ops * sizeof(OpParams)));
+        VX_CUDA(vx::device_malloc(ctx, reinterpret_cast<void**>(&b->d_ops), n_ops * sizeof(OpParams)));
         const cudaError_t e = cudaMemcpy(b->d_ops, host.data(), n_ops * sizeof(OpParams), cudaMemcpyHostToDevice);
         if (e != cudaSuccess) {
             cudaFree(b->d_ops);
@@ -845,6 +958,7 @@ vx_status vx_gemv_batch_launch(vx_context* ctx, const vx_gemv_batch* b) {
     vx::DeviceGuard guard(ctx->device);
     StreamParams p = b->params;
     p.status = ctx->d_status;
+    p.wait_cycles = vx::wait_cycles(ctx);
     const StreamConfig& c = b->cfg;
     const vx_status st = b->flagged ? launch_tr<true>(ctx, b->qtype, c, p, b->grid) : launch_tr<false>(ctx, b->qtype, c, p, b->grid);
     if (st != VX_OK) return st;

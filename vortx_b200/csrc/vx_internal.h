@@ -70,6 +70,7 @@ struct vx_context {
     vx::DeviceStatus* d_status = nullptr;  // device
     vx::DeviceStatus* h_status = nullptr;  // pinned host mirror
     bool status_dirty = false;             // a kernel that may write d_status ran since the last check
+    bool weights_fresh = false;            // a kernel of this stream has written quantised weights since the last GEMV launch
     void* reduce_scratch = nullptr;        // per-block partials of the wide reduction (device)
     std::map<std::string, int64_t> options;
 };
@@ -89,6 +90,18 @@ struct vx_qweights {
 namespace vx {
 
 int64_t option(const vx_context* ctx, const char* key, int64_t fallback);
+
+// Budget of the device-side waits on exchange vectors and peer barriers, in SM clocks: the option
+// "wait_cycles", or about 0.2 s.
+inline long long wait_cycles(const vx_context* ctx) {
+    const int64_t v = option(ctx, "wait_cycles", 0);
+    return v > 0 ? (long long)v : 400ll * 1000 * 1000;
+}
+
+// Every device allocation of the library goes through here (cudaMalloc on the current device).  The option
+// "debug.fail_alloc_after" = n makes the n-th call from now return cudaErrorMemoryAllocation without
+// allocating, so that the out-of-memory paths can be tested without filling a device.
+cudaError_t device_malloc(vx_context* ctx, void** ptr, size_t bytes);
 
 // SIMT kernels (vx_gemm_simt.cu)
 vx_status launch_gemm_naive(vx_context* ctx, float* out, const float* lhs, const float* rhs,

@@ -25,7 +25,8 @@ using vx::fail;
 constexpr uint32_t kEpochSlot = 32;
 constexpr uint32_t kArrivalBase = 40;
 
-__global__ void peer_barrier_kernel(vx::PeerFlags peers, uint32_t world, uint32_t rank, vx::DeviceStatus* status) {
+__global__ void peer_barrier_kernel(vx::PeerFlags peers, uint32_t world, uint32_t rank, vx::DeviceStatus* status,
+                                    long long wait_cycles) {
     const uint32_t t = threadIdx.x;
     // Let a dependent-launch GEMV behind this kernel become resident and prefetch its weights
     // now; it reads x and writes y only after this kernel has completed.
@@ -47,7 +48,7 @@ __global__ void peer_barrier_kernel(vx::PeerFlags peers, uint32_t world, uint32_
         bool ok = false;
         while (!ok) {
             for (int i = 0; i < 32 && !ok; ++i) ok = (int32_t)(*mine - epoch) >= 0;
-            if (!ok && clock64() - start > 400ll * 1000 * 1000) break;
+            if (!ok && clock64() - start > wait_cycles) break;
         }
         if (!ok) {
             volatile vx::DeviceStatus* v = status;
@@ -62,7 +63,7 @@ __global__ void peer_barrier_kernel(vx::PeerFlags peers, uint32_t world, uint32_
 // Exchange vector -> plain f32.  Pairs that do not carry the vector's generation yet are still
 // on their way from a peer: re-read them, for at most about 0.2 s of SM clocks.
 __global__ void xvec_unpack_kernel(const uint32_t* hdr, const uint64_t* pairs, uint32_t n, float* out,
-                                   vx::DeviceStatus* status) {
+                                   vx::DeviceStatus* status, long long wait_cycles) {
     const uint32_t gen = *(volatile const uint32_t*)hdr;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const volatile uint64_t* src = pairs + i;
@@ -70,7 +71,7 @@ __global__ void xvec_unpack_kernel(const uint32_t* hdr, const uint64_t* pairs, u
         if ((uint32_t)(v >> 32) != gen) {
             const long long start = clock64();
             while ((uint32_t)((v = *src) >> 32) != gen) {
-                if (clock64() - start > 400ll * 1000 * 1000) {
+                if (clock64() - start > wait_cycles) {
                     volatile vx::DeviceStatus* st = status;
                     st->detail = i;
                     st->code = 32;
@@ -176,7 +177,7 @@ vx_status vx_xvec_unpack(vx_context* ctx, const void* xvec, size_t n, float* out
     xvec_unpack_kernel<<<blocks, threads, 0, ctx->stream>>>(
         static_cast<const uint32_t*>(xvec),
         reinterpret_cast<const uint64_t*>(static_cast<const uint8_t*>(xvec) + vx::kExchangeHeader), (uint32_t)n, out,
-        ctx->d_status);
+        ctx->d_status, vx::wait_cycles(ctx));
     VX_CUDA(cudaGetLastError());
     ctx->launches++;
     ctx->status_dirty = true;
@@ -213,7 +214,7 @@ vx_status vx_peer_barrier(vx_context* ctx, uint32_t* const* flags, size_t world,
         VX_REQUIRE(i >= world || flags[i], VX_ERR_INVALID_ARGUMENT, "flag array of rank %zu is null", i);
     }
     vx::DeviceGuard guard(ctx->device);
-    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(p, (uint32_t)world, (uint32_t)rank, ctx->d_status);
+    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(p, (uint32_t)world, (uint32_t)rank, ctx->d_status, vx::wait_cycles(ctx));
     VX_CUDA(cudaGetLastError());
     ctx->launches++;
     ctx->status_dirty = true;

@@ -574,7 +574,7 @@ vx_status vx_qweights_upload(vx_context* ctx, vx_qtype t, const void* blocks, si
         std::memcpy(staging + qplane + b * 2, in + b * bb, 2);
         std::memcpy(staging + b * qb, in + b * bb + 2, qb);
     }
-    e = cudaMalloc(&w->d_base, w->device_bytes);
+    e = vx::device_malloc(ctx, reinterpret_cast<void**>(&w->d_base), w->device_bytes);
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(w->d_base, staging, w->device_bytes, cudaMemcpyHostToDevice, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
@@ -614,7 +614,7 @@ vx_status vx_qweights_from_device(vx_context* ctx, vx_qtype t, const float* w_de
     const size_t qplane = round_up(nblocks * quant_bytes(t), 256);
     const size_t splane = round_up(nblocks * 2, 256);
     w->device_bytes = qplane + splane;
-    cudaError_t e = cudaMalloc(&w->d_base, w->device_bytes);
+    cudaError_t e = vx::device_malloc(ctx, reinterpret_cast<void**>(&w->d_base), w->device_bytes);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return fail(VX_ERR_OUT_OF_MEMORY, "allocating %zu bytes of quantised weights failed: %s", w->device_bytes,
@@ -640,6 +640,7 @@ vx_status vx_qweights_from_device(vx_context* ctx, vx_qtype t, const float* w_de
         return fail(VX_ERR_CUDA, "device quantisation failed: %s", cudaGetErrorString(e));
     }
     ctx->launches++;
+    ctx->weights_fresh = true;
     *out = w.release();
     return VX_OK;
 }

@@ -14,6 +14,8 @@
 //     global memory, and a second one-block kernel that folds the partials in index order.
 //     Integer results and f32 min / max are the same values as ORDERED; f32 sum / product / norm
 //     differ from it by rounding order only.  Deterministic run to run.
+#include <atomic>
+
 #include "vx_internal.h"
 
 namespace {
@@ -192,7 +194,7 @@ vx_status vx_reduce(vx_context* ctx, vx_reduce_op op, vx_dtype dtype, vx_reduce_
     const uint32_t max_partials = (uint32_t)ctx->sm_count * 4;
     if (wide) {
         // Scratch for the partials: owned by the context, allocated on first use.
-        if (!ctx->reduce_scratch) VX_CUDA(cudaMalloc(&ctx->reduce_scratch, (size_t)max_partials * 4));
+        if (!ctx->reduce_scratch) VX_CUDA(vx::device_malloc(ctx, &ctx->reduce_scratch, (size_t)max_partials * 4));
         partials = ctx->reduce_scratch;
     }
     switch (dtype) {
@@ -222,17 +224,42 @@ constexpr uint32_t kStaticPerBlock = 65536;          // elements one block folds
 constexpr uint64_t kStaticMaxElements = (uint64_t)kStaticPartials * kStaticPerBlock;  // 67 108 864
 static __device__ __align__(256) unsigned char g_static_partials[kStaticPartials * 4];
 
+// With lazy module loading (the CUDA default) a kernel's code reaches the device at its first launch, and
+// that load may allocate device memory.  Asking for the attributes of every instantiation the entry point
+// can launch loads them all now, so that only the first call on a device ever loads anything.
+template <class T, int OP>
+cudaError_t warm_pair() {
+    cudaFuncAttributes a;
+    cudaError_t e = cudaFuncGetAttributes(&a, reduce_wide_partials_kernel<T, OP>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, reduce_wide_final_kernel<T, OP>);
+    return e;
+}
+template <class T>
+cudaError_t warm_type(bool with_sqnorm) {
+    cudaError_t e = warm_pair<T, SUM>();
+    if (e == cudaSuccess) e = warm_pair<T, PROD>();
+    if (e == cudaSuccess) e = warm_pair<T, MIN>();
+    if (e == cudaSuccess) e = warm_pair<T, MAX>();
+    if (e == cudaSuccess && with_sqnorm) e = warm_pair<T, SQNORM>();
+    return e;
+}
+
 // Device address of g_static_partials on `device`, looked up on the first call for that device
-// (with that device current) and remembered.  No allocation: the symbol already exists.
+// (with that device current) and remembered; the same first call loads the code of every kernel the
+// entry point can launch.  No allocation by this library: the symbol already exists.  Two threads that
+// make the first call at once both look the address up and store the same value.
 vx_status static_partials_for(int device, void** out) {
-    static void* cached[64] = {};
+    static std::atomic<void*> cached[64];
     VX_REQUIRE(device >= 0 && device < 64, VX_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", device);
-    if (!cached[device]) {
-        void* p = nullptr;
+    void* p = cached[device].load(std::memory_order_acquire);
+    if (!p) {
         VX_CUDA(cudaGetSymbolAddress(&p, g_static_partials));
-        cached[device] = p;
+        VX_CUDA(warm_type<float>(true));
+        VX_CUDA(warm_type<uint32_t>(false));
+        VX_CUDA(warm_type<int32_t>(false));
+        cached[device].store(p, std::memory_order_release);
     }
-    *out = cached[device];
+    *out = p;
     return VX_OK;
 }
 

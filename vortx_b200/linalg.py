@@ -231,6 +231,21 @@ class QuantizedMatrix:
     def stream_bytes(self) -> int:
         return self.rows * (self.cols // 32) * _lib.load().vx_qblock_bytes(self.qtype)
 
+    def device_bytes(self) -> int:
+        """Bytes the weights occupy on the device (both planes with their padding)."""
+        n = C.c_size_t()
+        _lib.check(_lib.load().vx_qweights_info(self._h, None, None, None, C.byref(n)))
+        return int(n.value)
+
+    def checksum(self) -> int:
+        """vx_qweights_checksum: one read-only pass over the device form; blocks until done."""
+        out = self.backend.uninit_buffer(1, dtype=np.uint32)
+        _lib.check(_lib.load().vx_qweights_checksum(self.backend._ctx, self._h, out.ptr))
+        v = np.zeros(1, np.uint32)
+        self.backend.slow_read_buffer(out, v)
+        out.free()
+        return int(v[0])
+
     def free(self) -> None:
         if self._h and self.backend._ctx:
             _lib.check(_lib.load().vx_qweights_free(self.backend._ctx, self._h))

@@ -51,6 +51,61 @@ def panel_relayout_shape(m: int, world: int, ncols: int):
     return (1, m, world, ncols), (world * m * ncols, ncols, m * ncols, 1)
 
 
+class PeerLost(RuntimeError):
+    """A rank of the group has left, or has not reached the step the others are about to launch."""
+
+
+class RankWatch:
+    """Host-side liveness of the ranks, checked BEFORE a step's kernels are launched.
+
+    The fused kernels wait for their peers on the device with a bounded budget, and a collective on a
+    communicator that has lost a rank ends in a process-group timeout at best; both are late and costly ways
+    to learn that a peer is gone.  Each rank therefore publishes, in the key-value store the process group was
+    built on, the number of the step it is about to launch (`announce`), and `await_all` waits, with a short
+    timeout, until every rank has announced that step.  A rank that leaves on purpose says so (`leave`): the
+    others then raise PeerLost at their next `await_all` without waiting; a rank that died silently costs them
+    one timeout.  A rank leaves only between steps, with none of its kernels or collectives in flight."""
+
+    def __init__(self, store, rank: int, world: int, name: str = "vx_watch"):
+        self.store, self.rank, self.world, self.name = store, rank, world, name
+        self.store.set(self._key(rank), "0")
+
+    @classmethod
+    def for_default_group(cls, name: str = "vx_watch") -> "RankWatch":
+        import torch.distributed as dist
+        from torch.distributed.distributed_c10d import _get_default_store
+        return cls(_get_default_store(), dist.get_rank(), dist.get_world_size(), name)
+
+    def _key(self, r: int) -> str:
+        return f"{self.name}/{r}"
+
+    def announce(self, step: int) -> None:
+        self.store.set(self._key(self.rank), str(int(step)))
+
+    def leave(self) -> None:
+        self.store.set(self._key(self.rank), "gone")
+
+    def await_all(self, step: int, timeout_s: float = 5.0) -> None:
+        """Returns once every rank has announced `step` (or a later one); raises PeerLost otherwise."""
+        import time
+        deadline = time.monotonic() + timeout_s
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            while True:
+                try:
+                    v = self.store.get(self._key(r)).decode()
+                except Exception as e:      # the store itself is gone: its host rank has exited
+                    raise PeerLost(f"rank {self.rank}: the store is unreachable ({e})") from e
+                if v == "gone":
+                    raise PeerLost(f"rank {r} has left the group before step {step}")
+                if int(v) >= step:
+                    break
+                if time.monotonic() > deadline:
+                    raise PeerLost(f"rank {r} has not reached step {step} within {timeout_s} s (last seen at {v})")
+                time.sleep(0.002)
+
+
 class PeerBuffers:
     """One device buffer per rank, each mapped into every other rank's process with CUDA IPC.
 
@@ -151,7 +206,12 @@ class PeerScatterGemv:
     def dispatch_chained(self, weights, y_vec: int, x_vec: Optional[int] = None, x_ptr: int = 0) -> None:
         """One link: this rank's rows of W x into exchange vector `y_vec` on every GPU.  x is exchange vector
         `x_vec` (its first `cols` elements, awaited pair by pair) or, for the first link, the plain `x_ptr`.
-        A vector may be written again only after every rank has read it: alternate two."""
+        A vector may be written again only after every rank has read it: alternate two.  That holds only if
+        every thread block of every rank owns a row the next link waits for (nobody can then run ahead of a
+        block that is still reading): the library shrinks the grid until it does, and refuses the launch
+        (VX_ERR_UNSUPPORTED) when none of this rank's rows is among the first `cols` elements, as with
+        contiguous slabs of a matrix with more rows than columns; deal such rows out in turn (cyclic=True)
+        or use `chain_batch(window=True)`."""
         from . import _lib
         lib = _lib.load()
         xv = self.vectors[x_vec].local.ptr if x_vec is not None else None
