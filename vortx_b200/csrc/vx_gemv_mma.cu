@@ -1,0 +1,643 @@
+// Batched GEMV for block-quantised weights on the tensor cores: up to eight activation vectors per pass
+// over the weights, every weight byte read from HBM once.
+//
+// With one vector the streaming kernel (vx_gemv_stream.cu) does its dot products with dp4a on the integer
+// pipe, which is already 60 % busy at HBM speed; eight vectors would need eight passes over the weights.
+// Here the block sums are integer matrix products instead: per 32-weight block,
+//     S[row, vec] = sum_i q[row, i] * X[vec, i]
+// is an m16 n8 k32 tensor-core MMA on the raw quants (A, 16 rows) and on x held as fixed point (B, 8
+// columns).  x is split into three signed byte planes (balanced digits: X = 65536 a + 256 b + c with
+// a, b, c in [-128, 127]), and the block's f16 scale is applied to the exact integer sums in f32, as in
+// the streaming kernel.  Two forms:
+//   FULL    3 to 8 vectors: the 8 columns are 8 vectors, one MMA per plane, and the three int32 results
+//           are recombined exactly (65536 sa + 256 sb + sc) before the scale is applied;
+//   SINGLE  1 or 2 vectors: the 8 columns are (vector, plane) pairs, ONE MMA per block; every column keeps
+//           its own f32 sum and the planes are added, with their weights 65536 / 256 / 1, at the end.
+//
+//   * A pre-pass kernel turns the batch's x into the planes ONCE, in the register layout the MMA wants for
+//     its B operand, in scratch memory of the context: per 32 columns 3 (FULL) or 1 (SINGLE) planes of
+//     32 lanes x 8 bytes, then, for Q4_0, -8 * sum X per column (the "- 8" of the format, added to the
+//     accumulator's initial value).
+//     X is fixed point relative to the largest |x| of its vector inside a slice of 32 * NBW columns
+//     (256 for the usual shapes): |X| < 2^22 for Q4_0 and < 2^19 for Q8_0, so that a block's recombined
+//     sum still fits 32 bits.  The slice sums are scaled by the slice's factor in f32.
+//   * The main kernel is persistent, one CTA per SM: producer warp (bulk TMA copies of 16-row tiles, rows
+//     padded apart in shared memory so that fragment loads hit 32 different banks), 8 consumer warps,
+//     epilogue warp.  The columns are split over CS CTAs so that a CTA's share of the planes (25 bytes per
+//     column) stays resident in its shared memory; the 8 warps of a CTA split a tile's columns further and
+//     keep their B fragments in registers while they walk up to 8 row tiles.
+//   * Partial sums meet in shared memory (the 8 warps of a CTA, fixed order) and, when the columns are
+//     split over several CTAs, in scratch memory: each CTA stores its part, and whichever arrives last at
+//     the tile's counter adds the parts in a fixed order and writes y.  No CTA ever waits for another.
+// All waits are bounded (see vx_sm100.cuh).
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <atomic>
+
+#include "vx_internal.h"
+#include "vx_sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kVecs = 8;                 // vectors per pass (the MMA's n)
+constexpr int kUnitRows = 16;            // rows per tile (the MMA's m)
+constexpr int kGroup = 8;                // row tiles a warp carries per pass over its columns
+constexpr int kWarps = 8;                // consumer warps
+constexpr int kRedSlots = 4;
+constexpr int kRedStride = 20;           // floats between vectors in a reduction slot (16 rows + padding)
+constexpr int kRedWarp = kVecs * kRedStride;
+constexpr int kMaxStages = 8;
+enum { SINGLE = 0, FULL = 1 };
+// bytes of planes per 32 columns: 3 (FULL) or 1 (SINGLE) x 256, then 8 x int32
+__host__ __device__ constexpr uint32_t block_planes(int mode) { return mode == FULL ? 800u : 288u; }
+
+struct MmaParams {
+    const uint8_t* quants;
+    const uint8_t* scales;        // f16 plane, in bytes
+    uint32_t row_bytes;           // quants per row, bytes
+    uint32_t nb;                  // blocks per row
+    uint64_t row0;
+    uint32_t nrows;
+    uint32_t cs;                  // column parts
+    uint32_t kc_blocks;           // blocks per part
+    uint32_t nkt;                 // column tiles per part
+    uint32_t stages, stage_bytes, q_row_stride, s_row_stride, s_off;
+    const uint8_t* planes;        // [nb][block_planes(MODE)]
+    const float* sx;              // [slices][kVecs]: per column, the factor its slice sums are scaled by
+    float* y;
+    uint64_t y_stride;
+    uint32_t batch;
+    float* partial;               // [cs][kVecs][nrows16]
+    uint32_t* counters;           // one per row tile
+    uint32_t nrows16;             // rows rounded up to whole tiles
+    vx::DeviceStatus* status;
+};
+
+__device__ __forceinline__ void report(vx::DeviceStatus* st, uint32_t code) {
+    volatile vx::DeviceStatus* v = st;
+    v->detail = blockIdx.x;
+    v->code = code;
+    __threadfence_system();
+}
+
+// D = A * B + C, A 16 x 32 bytes (row; unsigned nibbles of Q4_0 or signed bytes of Q8_0), B 32 x 8 signed
+// bytes (col), int32 accumulators.
+template <bool A_SIGNED>
+__device__ __forceinline__ void mma_i8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const int (&c)[4]) {
+    if constexpr (A_SIGNED)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+    else
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+
+// ------------------------------------------------------------------------ pre-pass ----
+// One CTA per slice of 32 * NBW columns, one warp per column of the MMA's B operand: a vector (FULL), or a
+// (vector, plane) pair (SINGLE: column n is plane n % 3 of vector n / 3).  Word w of the slice (4 matrix
+// columns) belongs to block w / 8; inside the block, words 0..3 are the first B register of lanes t = 0..3
+// and words 4..7 the second one (the MMA's k = 4 t + i and 16 + 4 t + i).
+template <int QT, int MODE>
+__global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, uint64_t x_stride, uint32_t batch,
+                                                      uint32_t nbw, uint8_t* __restrict__ planes, float* __restrict__ sx) {
+    constexpr float kXMax = QT == 1 ? 4194302.0f : 524286.0f;
+    constexpr uint32_t kBP = block_planes(MODE);
+    const uint32_t slice = blockIdx.x, col = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t vec = MODE == FULL ? col : col / 3, plane = col % 3;
+    const uint32_t words = 8 * nbw;                  // 4-column words per slice: 8 .. 64
+    const bool live = vec < batch && (MODE == FULL || col < 6);
+    const float* src = x + (size_t)vec * x_stride + (size_t)slice * 32 * nbw;
+    const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+    float v[2][4];
+    float amax = 0.0f, poison = 0.0f;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t w = lane + 32 * r;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[r][i] = 0.0f;
+        if (live && w < words) {
+            if (aligned) {
+                const float4 f = __ldg(reinterpret_cast<const float4*>(src) + w);
+                v[r][0] = f.x; v[r][1] = f.y; v[r][2] = f.z; v[r][3] = f.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[r][i] = __ldg(src + 4 * w + i);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            amax = fmaxf(amax, fabsf(v[r][i]));
+            poison = fmaf(v[r][i], 0.0f, poison);
+        }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        poison += __shfl_xor_sync(0xffffffffu, poison, off);
+    }
+    float inv = amax > 0.0f ? kXMax / amax : 0.0f;
+    float s = amax / kXMax;
+    if (amax > 0.0f && amax < kXMax / 1.0e38f) { inv = 0x1p100f; s = 0x1p-100f; }   // the quotient would overflow
+    if (poison != poison) { inv = 0.0f; s = poison; }                                // NaN or infinity in x: NaN in y
+    if (lane == 0) {
+        const float weight = MODE == FULL ? 1.0f : plane == 0 ? 65536.0f : plane == 1 ? 256.0f : 1.0f;
+        sx[(size_t)slice * kVecs + col] = live ? s * weight : 0.0f;
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t w = lane + 32 * r;
+        // balanced digits: X = 65536 a + 256 b + c, every digit a signed byte
+        uint32_t da = 0, db = 0, dc = 0;
+        int sum = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int X = __float2int_rn(v[r][i] * inv);
+            const int c = (int)(int8_t)(X & 0xFF);
+            const int X1 = (X - c) >> 8;
+            const int b = (int)(int8_t)(X1 & 0xFF);
+            const int a = (X1 - b) >> 8;
+            da |= (uint32_t)(a & 0xFF) << (8 * i);
+            db |= (uint32_t)(b & 0xFF) << (8 * i);
+            dc |= (uint32_t)(c & 0xFF) << (8 * i);
+            sum += MODE == FULL ? X : plane == 0 ? a : plane == 1 ? b : c;
+        }
+        // the 8 words of a block sit in 8 consecutive lanes
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (w < words) {
+            const uint32_t blk = slice * nbw + w / 8, q = w & 7, t = q & 3, reg = q >> 2;
+            uint8_t* base = planes + (size_t)blk * kBP;
+            const uint32_t at = ((col * 4 + t) * 2 + reg) * 4;     // lane (col, t) of the MMA, register `reg`
+            if (MODE == FULL) {
+                *reinterpret_cast<uint32_t*>(base + at) = da;
+                *reinterpret_cast<uint32_t*>(base + 256 + at) = db;
+                *reinterpret_cast<uint32_t*>(base + 512 + at) = dc;
+            } else {
+                *reinterpret_cast<uint32_t*>(base + at) = plane == 0 ? da : plane == 1 ? db : dc;
+            }
+            if (q == 0) *reinterpret_cast<int*>(base + (kBP - 32) + col * 4) = QT == 1 && live ? -8 * sum : 0;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------ main kernel ----
+// Work of CTA c: column part c % cs; row tiles [u0, u1) of pair c / cs, in groups of kGroup.
+__device__ __forceinline__ void my_units(const MmaParams& p, uint32_t* u0, uint32_t* u1) {
+    const uint32_t pairs = gridDim.x / p.cs, pair = blockIdx.x / p.cs;
+    const uint32_t units = p.nrows16 / kUnitRows;
+    *u0 = (uint32_t)((uint64_t)units * pair / pairs);
+    *u1 = (uint32_t)((uint64_t)units * (pair + 1) / pairs);
+}
+
+template <int QT, int NBW, int MODE>
+__global__ void __launch_bounds__(kWarps * 32 + 64, 1) gemv_mma_kernel(const __grid_constant__ MmaParams p) {
+    constexpr int QB = QT == 1 ? 16 : 32;   // bytes of quants per block
+    constexpr int NP = MODE == FULL ? 3 : 1;
+    constexpr uint32_t kBP = block_planes(MODE);
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t plane_bytes = p.kc_blocks * kBP;
+    uint8_t* s_planes = smem;
+    float* s_sx = reinterpret_cast<float*>(smem + plane_bytes);                       // [nkt * kWarps][kVecs]
+    uint8_t* ring = smem + plane_bytes + ((p.nkt * kWarps * kVecs * 4 + 127) & ~127u);
+    float* red = reinterpret_cast<float*>(ring + (size_t)p.stages * p.stage_bytes);   // [kRedSlots][kWarps][kRedWarp]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + kRedSlots * kWarps * kRedWarp);
+    const uint32_t bar0 = smem_addr(bars);
+    auto full = [&](uint32_t s) { return bar0 + 8u * s; };
+    auto empty = [&](uint32_t s) { return bar0 + 8u * (kMaxStages + s); };
+    auto red_full = [&](uint32_t b) { return bar0 + 8u * (2 * kMaxStages + b); };
+    auto red_empty = [&](uint32_t b) { return bar0 + 8u * (2 * kMaxStages + kRedSlots + b); };
+    const uint32_t planes_bar = bar0 + 8u * (2 * kMaxStages + 2 * kRedSlots);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 2 * kRedSlots + 1);
+
+    const uint32_t tid = threadIdx.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        *abort_flag = 0u;
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), kWarps);
+        }
+        for (uint32_t b = 0; b < kRedSlots; ++b) {
+            mbar_init(red_full(b), kWarps);
+            mbar_init(red_empty(b), 1);
+        }
+        mbar_init(planes_bar, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    uint32_t u0, u1;
+    my_units(p, &u0, &u1);
+    const uint32_t kpart = blockIdx.x % p.cs;
+    const uint32_t kt_blocks = NBW * kWarps;                 // blocks per column tile
+    const uint32_t q_tile_bytes = kt_blocks * QB;            // quants per row and tile
+
+    if (tid >= kWarps * 32 + 32) {
+        // ------------------------------------------------------------ epilogue warp ----
+        // Lanes 0..15 take the tile's 16 rows for one vector, lanes 16..31 for the next one.
+        const uint32_t lane = tid & 31, r = lane & 15, half = lane >> 4;
+        constexpr int NV = MODE == FULL ? kVecs / 2 : 1;     // vectors per lane
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the kernel before the pre-pass
+        uint32_t k = 0;
+        for (uint32_t u = u0; u < u1; ++u, ++k) {
+            const uint32_t b = k % kRedSlots;
+            if (!mbar_wait(red_full(b), (k / kRedSlots) & 1, abort_flag)) report(p.status, 44);
+            const float* slot = red + (size_t)b * kWarps * kRedWarp;
+            const uint32_t row = u * kUnitRows + r;
+            float sum[NV];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const uint32_t v = 2 * i + half;
+                float s = 0.0f;
+                if (MODE == FULL) {
+#pragma unroll
+                    for (int w = 0; w < kWarps; ++w) s += slot[w * kRedWarp + v * kRedStride + r];
+                } else if (v < 2) {
+                    // the vector's three planes, each already weighted by 65536 / 256 / 1: high plane last
+#pragma unroll
+                    for (int pl = 2; pl >= 0; --pl) {
+                        float sp = 0.0f;
+#pragma unroll
+                        for (int w = 0; w < kWarps; ++w) sp += slot[w * kRedWarp + (3 * v + pl) * kRedStride + r];
+                        s += sp;
+                    }
+                }
+                sum[i] = s;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(red_empty(b));
+            if (p.cs == 1) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const uint32_t v = 2 * i + half;
+                    if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = sum[i];
+                }
+            } else {
+                // this part's sums go to scratch; whoever arrives last at the tile's counter adds the parts
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const uint32_t v = 2 * i + half;
+                    __stcg(p.partial + ((size_t)kpart * kVecs + v) * p.nrows16 + row, sum[i]);
+                }
+                __threadfence();
+                __syncwarp();
+                uint32_t old = 0;
+                if (lane == 0) old = atomicAdd(p.counters + u, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == p.cs - 1) {
+                    __threadfence();
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        const uint32_t v = 2 * i + half;
+                        float s = 0.0f;
+                        for (uint32_t kp = 0; kp < p.cs; ++kp)
+                            s += __ldcg(p.partial + ((size_t)kp * kVecs + v) * p.nrows16 + row);
+                        if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = s;
+                    }
+                    __syncwarp();
+                    if (lane == 0) p.counters[u] = 0;        // ready for the next launch
+                }
+            }
+        }
+        return;
+    }
+    if (tid >= kWarps * 32) {
+        // ------------------------------------------------------------ producer warp ----
+        // Lane r copies row r of every tile: its quants for the tile's columns and its scales.
+        const uint32_t lane = tid & 31;
+        const uint64_t policy = policy_evict_first();
+        uint32_t k = 0;
+        for (uint32_t g0 = u0; g0 < u1; g0 += kGroup) {
+            const uint32_t g1 = min(g0 + kGroup, u1);
+            for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+                const uint32_t blk0 = kpart * p.kc_blocks + kt * kt_blocks;       // first block of the tile in the row
+                for (uint32_t u = g0; u < g1; ++u, ++k) {
+                    const uint32_t s = k % p.stages, use = k / p.stages;
+                    if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1, abort_flag)) report(p.status, 41);
+                    const uint32_t first = u * kUnitRows;
+                    const uint32_t rows = min((uint32_t)kUnitRows, p.nrows - first);
+                    const uint32_t dst = smem_addr(ring + (size_t)s * p.stage_bytes);
+                    if (lane == 0) mbar_arrive_expect_tx(full(s), rows * (q_tile_bytes + kt_blocks * 2));
+                    __syncwarp();
+                    if (lane < rows) {
+                        const uint64_t row = p.row0 + first + lane;
+                        bulk_g2s_hint(dst + lane * p.q_row_stride, p.quants + row * p.row_bytes + (uint64_t)blk0 * QB,
+                                      q_tile_bytes, full(s), policy);
+                        bulk_g2s_hint(dst + p.s_off + lane * p.s_row_stride, p.scales + (row * p.nb + blk0) * 2,
+                                      kt_blocks * 2, full(s), policy);
+                    }
+                }
+            }
+        }
+        // do not leave while copies into this CTA's shared memory may still be in flight
+        if (lane == 0) {
+            for (uint32_t s = 0; s < p.stages && s < k; ++s) {
+                const uint32_t last_k = ((k - 1 - s) / p.stages) * p.stages + s;
+                if (!mbar_wait(empty(s), (last_k / p.stages) & 1, abort_flag)) report(p.status, 42);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumer warps ----
+    const uint32_t lane = tid & 31, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3;
+    // the planes are the pre-pass kernel's output: wait for it, then one bulk copy of this part's share
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) {
+        const uint32_t sx_bytes = p.nkt * kWarps * kVecs * 4;
+        mbar_arrive_expect_tx(planes_bar, plane_bytes + sx_bytes);
+        bulk_g2s(smem_addr(s_planes), p.planes + (size_t)kpart * plane_bytes, plane_bytes, planes_bar);
+        bulk_g2s(smem_addr(s_sx), p.sx + (size_t)kpart * p.nkt * kWarps * kVecs, sx_bytes, planes_bar);
+    }
+    if (!mbar_wait(planes_bar, 0, abort_flag)) report(p.status, 45);
+
+    uint32_t k = 0, kr = 0;
+    for (uint32_t g0 = u0; g0 < u1; g0 += kGroup) {
+        const uint32_t nu = min((uint32_t)kGroup, u1 - g0);
+        float acc[kGroup][4];
+#pragma unroll
+        for (int i = 0; i < kGroup; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+        for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+            // this warp's B fragments for its NBW blocks of the tile, kept in registers over the row tiles
+            uint32_t B[NBW][NP][2];
+            int init[NBW][2];
+            const uint32_t blk_local = kt * kt_blocks + warp * NBW;      // within this part's planes
+#pragma unroll
+            for (int j = 0; j < NBW; ++j) {
+                const uint8_t* pb = s_planes + (size_t)(blk_local + j) * kBP;
+#pragma unroll
+                for (int pl = 0; pl < NP; ++pl) {
+                    const uint2 v = *reinterpret_cast<const uint2*>(pb + pl * 256 + lane * 8);
+                    B[j][pl][0] = v.x;
+                    B[j][pl][1] = v.y;
+                }
+                const int2 iv = *reinterpret_cast<const int2*>(pb + (kBP - 32) + t * 8);
+                init[j][0] = iv.x;
+                init[j][1] = iv.y;
+            }
+            const float2 sxv = *reinterpret_cast<const float2*>(s_sx + (size_t)(kt * kWarps + warp) * kVecs + 2 * t);
+
+#pragma unroll
+            for (int i = 0; i < kGroup; ++i) {
+                if ((uint32_t)i < nu) {
+                    const uint32_t s = k % p.stages;
+                    if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 43);
+                    const uint8_t* sq = ring + (size_t)s * p.stage_bytes;
+                    const uint8_t* ss = sq + p.s_off;
+                    // the NBW scales of rows g and g + 8
+                    __align__(16) __half dlo[NBW], dhi[NBW];
+                    {
+                        const uint8_t* a = ss + g * p.s_row_stride + warp * NBW * 2;
+                        const uint8_t* b = ss + (g + 8) * p.s_row_stride + warp * NBW * 2;
+                        if constexpr (NBW == 8) {
+                            *reinterpret_cast<uint4*>(dlo) = *reinterpret_cast<const uint4*>(a);
+                            *reinterpret_cast<uint4*>(dhi) = *reinterpret_cast<const uint4*>(b);
+                        } else if constexpr (NBW == 4) {
+                            *reinterpret_cast<uint2*>(dlo) = *reinterpret_cast<const uint2*>(a);
+                            *reinterpret_cast<uint2*>(dhi) = *reinterpret_cast<const uint2*>(b);
+                        } else if constexpr (NBW == 2) {
+                            *reinterpret_cast<uint32_t*>(dlo) = *reinterpret_cast<const uint32_t*>(a);
+                            *reinterpret_cast<uint32_t*>(dhi) = *reinterpret_cast<const uint32_t*>(b);
+                        } else {
+                            dlo[0] = *reinterpret_cast<const __half*>(a);
+                            dhi[0] = *reinterpret_cast<const __half*>(b);
+                        }
+                    }
+                    float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int j = 0; j < NBW; ++j) {
+                        const uint8_t* qa = sq + g * p.q_row_stride + (warp * NBW + j) * QB + t * 4;
+                        const uint8_t* qb = qa + 8 * p.q_row_stride;
+                        uint32_t A[4];
+                        if constexpr (QT == 1) {
+                            const uint32_t wa = *reinterpret_cast<const uint32_t*>(qa);
+                            const uint32_t wb = *reinterpret_cast<const uint32_t*>(qb);
+                            A[0] = wa & 0x0F0F0F0Fu;
+                            A[1] = wb & 0x0F0F0F0Fu;
+                            A[2] = (wa >> 4) & 0x0F0F0F0Fu;
+                            A[3] = (wb >> 4) & 0x0F0F0F0Fu;
+                        } else {
+                            A[0] = *reinterpret_cast<const uint32_t*>(qa);
+                            A[1] = *reinterpret_cast<const uint32_t*>(qb);
+                            A[2] = *reinterpret_cast<const uint32_t*>(qa + 16);
+                            A[3] = *reinterpret_cast<const uint32_t*>(qb + 16);
+                        }
+                        const int c_init[4] = {init[j][0], init[j][1], init[j][0], init[j][1]};
+                        const float dl = __half2float(dlo[j]), dh = __half2float(dhi[j]);
+                        if constexpr (MODE == FULL) {
+                            const int zero[4] = {0, 0, 0, 0};
+                            int ca[4], cb[4], cc[4];
+                            mma_i8<QT == 0>(ca, A, B[j][0][0], B[j][0][1], zero);
+                            mma_i8<QT == 0>(cb, A, B[j][1][0], B[j][1][1], zero);
+                            mma_i8<QT == 0>(cc, A, B[j][2][0], B[j][2][1], c_init);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                // sum q X = 65536 sa + 256 sb + sc, exact in 32 bits by the bound on |X|
+                                const int tsum = ca[e] * 65536 + (cb[e] * 256 + cc[e]);
+                                sacc[e] = fmaf(e < 2 ? dl : dh, (float)tsum, sacc[e]);
+                            }
+                        } else {
+                            int c[4];
+                            mma_i8<QT == 0>(c, A, B[j][0][0], B[j][0][1], c_init);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) sacc[e] = fmaf(e < 2 ? dl : dh, (float)c[e], sacc[e]);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty(s));
+                    ++k;
+                    acc[i][0] = fmaf(sxv.x, sacc[0], acc[i][0]);
+                    acc[i][1] = fmaf(sxv.y, sacc[1], acc[i][1]);
+                    acc[i][2] = fmaf(sxv.x, sacc[2], acc[i][2]);
+                    acc[i][3] = fmaf(sxv.y, sacc[3], acc[i][3]);
+                    if (kt == p.nkt - 1) {
+                        // the tile is complete for this warp's columns: hand it to the epilogue warp
+                        const uint32_t b = kr % kRedSlots;
+                        if (kr >= kRedSlots && !mbar_wait(red_empty(b), ((kr / kRedSlots) - 1) & 1, abort_flag)) report(p.status, 46);
+                        float* slot = red + ((size_t)b * kWarps + warp) * kRedWarp;
+                        slot[(2 * t) * kRedStride + g] = acc[i][0];
+                        slot[(2 * t + 1) * kRedStride + g] = acc[i][1];
+                        slot[(2 * t) * kRedStride + g + 8] = acc[i][2];
+                        slot[(2 * t + 1) * kRedStride + g + 8] = acc[i][3];
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(red_full(b));
+                        ++kr;
+                    }
+                }
+            }
+        }
+    }
+}
+
+struct MmaConfig {
+    uint32_t cs, nbw, stages, stage_bytes, q_row_stride, s_row_stride, s_off, kc_blocks, nkt;
+    int mode;
+    size_t smem;
+};
+
+// false: the shape does not fit (columns not a multiple of 256 per part, or too many).
+bool choose(const vx_qweights* w, uint32_t batch, MmaConfig* c) {
+    const uint32_t nb = (uint32_t)w->blocks_per_row;
+    const uint32_t qb = w->type == VX_Q4_0 ? 16 : 32;
+    c->mode = batch <= 2 ? SINGLE : FULL;
+    const uint32_t bp = block_planes(c->mode);
+    for (uint32_t cs = 1; cs <= 8; cs *= 2) {
+        if (nb % (cs * kWarps) != 0) continue;
+        const uint32_t kc_blocks = nb / cs;
+        if ((size_t)kc_blocks * bp > 104 * 1024) continue;
+        uint32_t nbw = 8;
+        while (nbw > 1 && kc_blocks % (nbw * kWarps) != 0) nbw >>= 1;
+        const uint32_t kt_blocks = nbw * kWarps;
+        c->cs = cs;
+        c->nbw = nbw;
+        c->kc_blocks = kc_blocks;
+        c->nkt = kc_blocks / kt_blocks;
+        c->q_row_stride = kt_blocks * qb + 16;                  // rows 16 bytes out of step: fragment loads hit 32 banks
+        c->s_row_stride = ((kt_blocks * 2 + 15) & ~15u) + 16;
+        c->s_off = (kUnitRows * c->q_row_stride + 127) & ~127u;
+        c->stage_bytes = (c->s_off + kUnitRows * c->s_row_stride + 127) & ~127u;
+        const size_t fixed = (size_t)kc_blocks * bp + ((c->nkt * kWarps * kVecs * 4 + 127) & ~127u) +
+                             (size_t)kRedSlots * kWarps * kRedWarp * 4 + (2 * kMaxStages + 2 * kRedSlots + 2) * 8;
+        const size_t room = (size_t)227 * 1024 - 1024 - fixed;
+        const uint32_t stages = (uint32_t)std::min<size_t>(kMaxStages, room / c->stage_bytes);
+        if (stages < 2) continue;
+        c->stages = stages;
+        c->smem = fixed + (size_t)stages * c->stage_bytes;
+        return true;
+    }
+    return false;
+}
+
+template <int QT, int NBW, int MODE>
+vx_status launch_main(vx_context* ctx, const MmaParams& p, uint32_t grid, size_t smem) {
+    auto kernel = gemv_mma_kernel<QT, NBW, MODE>;
+    static std::atomic<size_t> granted[64];
+    const int dev = ctx->device & 63;
+    if (granted[dev].load(std::memory_order_acquire) < smem) {
+        VX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        granted[dev].store(smem, std::memory_order_release);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kWarps * 32 + 64);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // the weights may have been written by a kernel of this stream (device quantiser): then no early start
+    cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 && !ctx->weights_fresh ? 1 : 0;
+    ctx->weights_fresh = false;
+    VX_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    return VX_OK;
+}
+
+template <int QT, int MODE>
+vx_status launch_nbw(vx_context* ctx, uint32_t nbw, const MmaParams& p, uint32_t grid, size_t smem) {
+    switch (nbw) {
+        case 8: return launch_main<QT, 8, MODE>(ctx, p, grid, smem);
+        case 4: return launch_main<QT, 4, MODE>(ctx, p, grid, smem);
+        case 2: return launch_main<QT, 2, MODE>(ctx, p, grid, smem);
+        default: return launch_main<QT, 1, MODE>(ctx, p, grid, smem);
+    }
+}
+
+// Grows one of the context's scratch buffers (never shrinks); new memory is zeroed.
+vx_status ensure(vx_context* ctx, void** buf, size_t* have, size_t want) {
+    if (*have >= want) return VX_OK;
+    VX_CUDA(cudaStreamSynchronize(ctx->stream));     // earlier launches may still use the old buffer
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *have = 0;
+    VX_CUDA(vx::device_malloc(ctx, buf, want));
+    VX_CUDA(cudaMemsetAsync(*buf, 0, want, ctx->stream));
+    *have = want;
+    return VX_OK;
+}
+
+}  // namespace
+
+namespace vx {
+
+// `batch` vectors (1..8) in one pass over rows [row0, row0 + nrows).  *eligible = false (nothing launched)
+// when the shape does not fit this kernel; the caller then takes the streaming kernel.
+vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows, const float* x,
+                          size_t x_stride, float* y, size_t y_stride, uint32_t batch, bool* eligible) {
+    *eligible = false;
+    MmaConfig c;
+    if (batch < 1 || batch > (uint32_t)kVecs || !choose(w, batch, &c)) return VX_OK;
+    const uint32_t nb = (uint32_t)w->blocks_per_row;
+    const uint32_t nrows16 = (nrows + kUnitRows - 1) / kUnitRows * kUnitRows;
+    const uint32_t slices = nb / c.nbw;
+    const size_t planes_bytes = ((size_t)nb * block_planes(c.mode) + 255) & ~(size_t)255;
+    vx_status st = ensure(ctx, &ctx->mma_planes, &ctx->mma_planes_bytes, planes_bytes + (size_t)slices * kVecs * 4);
+    if (st != VX_OK) return st;
+    if (c.cs > 1) {
+        st = ensure(ctx, &ctx->mma_partial, &ctx->mma_partial_bytes, (size_t)c.cs * kVecs * nrows16 * 4);
+        if (st != VX_OK) return st;
+        st = ensure(ctx, &ctx->mma_counters, &ctx->mma_counters_bytes, (size_t)(nrows16 / kUnitRows) * 4);
+        if (st != VX_OK) return st;
+    }
+    uint8_t* planes = static_cast<uint8_t*>(ctx->mma_planes);
+    float* sx = reinterpret_cast<float*>(planes + planes_bytes);
+
+    const bool q4 = w->type == VX_Q4_0;
+    if (c.mode == FULL) {
+        if (q4) xplanes_kernel<1, FULL><<<slices, 256, 0, ctx->stream>>>(x, x_stride, batch, c.nbw, planes, sx);
+        else xplanes_kernel<0, FULL><<<slices, 256, 0, ctx->stream>>>(x, x_stride, batch, c.nbw, planes, sx);
+    } else {
+        if (q4) xplanes_kernel<1, SINGLE><<<slices, 256, 0, ctx->stream>>>(x, x_stride, batch, c.nbw, planes, sx);
+        else xplanes_kernel<0, SINGLE><<<slices, 256, 0, ctx->stream>>>(x, x_stride, batch, c.nbw, planes, sx);
+    }
+    VX_CUDA(cudaGetLastError());
+    ctx->launches++;
+
+    MmaParams p{};
+    p.quants = w->d_quants;
+    p.scales = reinterpret_cast<const uint8_t*>(w->d_scales);
+    p.row_bytes = (uint32_t)w->quant_row_bytes;
+    p.nb = nb;
+    p.row0 = row0;
+    p.nrows = nrows;
+    p.cs = c.cs;
+    p.kc_blocks = c.kc_blocks;
+    p.nkt = c.nkt;
+    p.stages = c.stages;
+    p.stage_bytes = c.stage_bytes;
+    p.q_row_stride = c.q_row_stride;
+    p.s_row_stride = c.s_row_stride;
+    p.s_off = c.s_off;
+    p.planes = planes;
+    p.sx = sx;
+    p.y = y;
+    p.y_stride = y_stride;
+    p.batch = batch;
+    p.partial = static_cast<float*>(ctx->mma_partial);
+    p.counters = static_cast<uint32_t*>(ctx->mma_counters);
+    p.nrows16 = nrows16;
+    p.status = ctx->d_status;
+    const uint32_t units = nrows16 / kUnitRows;
+    const uint32_t pairs = std::max(1u, std::min((uint32_t)ctx->sm_count / c.cs, units));
+    const uint32_t grid = pairs * c.cs;
+    if (c.mode == FULL)
+        st = q4 ? launch_nbw<1, FULL>(ctx, c.nbw, p, grid, c.smem) : launch_nbw<0, FULL>(ctx, c.nbw, p, grid, c.smem);
+    else
+        st = q4 ? launch_nbw<1, SINGLE>(ctx, c.nbw, p, grid, c.smem) : launch_nbw<0, SINGLE>(ctx, c.nbw, p, grid, c.smem);
+    if (st != VX_OK) return st;
+    ctx->launches++;
+    ctx->status_dirty = true;
+    *eligible = true;
+    return VX_OK;
+}
+
+}  // namespace vx

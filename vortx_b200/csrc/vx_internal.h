@@ -72,6 +72,14 @@ struct vx_context {
     bool status_dirty = false;             // a kernel that may write d_status ran since the last check
     bool weights_fresh = false;            // a kernel of this stream has written quantised weights since the last GEMV launch
     void* reduce_scratch = nullptr;        // per-block partials of the wide reduction (device)
+    // scratch of the tensor-core batch GEMV (device, grown on demand): x as fixed-point planes, the parts
+    // of a column split, one counter per row tile
+    void* mma_planes = nullptr;
+    size_t mma_planes_bytes = 0;
+    void* mma_partial = nullptr;
+    size_t mma_partial_bytes = 0;
+    void* mma_counters = nullptr;
+    size_t mma_counters_bytes = 0;
     std::map<std::string, int64_t> options;
 };
 
@@ -145,5 +153,10 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
                              const float* x, float* y, float* const* y_peer, uint32_t n_peer,
                              const Exchange* xch, bool* eligible, uint32_t batch = 1, size_t x_stride = 0,
                              size_t y_stride = 0);
+
+// Tensor-core batch GEMV (vx_gemv_mma.cu): up to 8 vectors per pass over the weights.  *eligible = false
+// (nothing launched) when the column count does not fit it.
+vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows, const float* x,
+                          size_t x_stride, float* y, size_t y_stride, uint32_t batch, bool* eligible);
 
 }  // namespace vx

@@ -703,6 +703,19 @@ vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t row0, siz
     // row does not fit the ring.
     if (vx::option(ctx, "gemv.variant", 2) == 2) {
         size_t v = 0;
+        // Two and more vectors: the tensor-core kernel, eight vectors per pass over the weights.
+        const int64_t use_mma = vx::option(ctx, "gemv.batch_mma", -1);
+        if (use_mma != 0 && (batch >= 2 || use_mma == 1)) {
+            while (v < batch) {
+                const uint32_t take = (uint32_t)std::min<size_t>(8, batch - v);
+                bool eligible = false;
+                vx_status st = vx::launch_gemv_mma(ctx, w, row0, (uint32_t)nrows, x + v * x_stride, x_stride,
+                                                   y + v * y_stride, y_stride, take, &eligible);
+                if (st != VX_OK) return st;
+                if (!eligible) break;
+                v += take;
+            }
+        }
         while (v < batch) {
             const uint32_t take = (uint32_t)std::min<size_t>(8, batch - v);
             bool eligible = false;
