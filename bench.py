@@ -873,6 +873,11 @@ PROFILE_CASES = {
     "gemv_q4_0_8192x8192": ("gemv", 8192, 8192, "Q4_0", 4),
     "gemv_list_q4_0_28672x8192_x8": ("gemv_list", 28672, 8192, "Q4_0", 8),   # one list launch over 8 weight copies
     "gemv_q8_0_4096x4096": ("gemv", 4096, 4096, "Q8_0", 8),
+    "gemv_mma_q4_0_8192x8192_b8": ("gemv_batch", 8192, 8192, "Q4_0", 8),     # tensor-core batch kernel, 8 vectors
+    "gemv_mma_q4_0_8192x8192_b2": ("gemv_batch", 8192, 8192, "Q4_0", 2),     # its one-MMA form, 2 vectors
+    "gemv_mma_q4_0_28672x8192_b8": ("gemv_batch", 28672, 8192, "Q4_0", 8),
+    "gemv_mma_q4_0_28672x8192_b2": ("gemv_batch", 28672, 8192, "Q4_0", 2),
+    "gemv_mma_q8_0_4096x4096_b8": ("gemv_batch", 4096, 4096, "Q8_0", 8),
     "gemm_simt_exact_1024": ("gemm", 1024, 1024, "SIMT", 0),
     "gemm_tf32_4096": ("gemm", 4096, 4096, "TF32", 0),
     "gemm_tf32_8192": ("gemm", 8192, 8192, "TF32", 0),
@@ -889,7 +894,10 @@ def run_profile_case(name: str):
     be = vb.Backend(0)
     lib = _lib.load()
     rng = np.random.Generator(np.random.Philox(1))
-    if kind in ("gemv", "gemv_list"):
+    if kind == "gemv_batch":
+        # `copies` is the batch here; four copies of the weights so that they come from HBM
+        batch, copies = copies, 4
+    if kind in ("gemv", "gemv_list", "gemv_batch"):
         qt = vb.Q4_0 if what == "Q4_0" else vb.Q8_0
         bb = lib.vx_qblock_bytes(qt)
         nblocks = rows * cols // 32
@@ -899,9 +907,14 @@ def run_profile_case(name: str):
         blocks[:, 0] = sc & 0xFF
         blocks[:, 1] = sc >> 8
         ws = [vb.QuantizedMatrix(be, qt, blocks.ravel(), rows, cols) for _ in range(copies)]
-        x = be.init_buffer(rng.standard_normal(cols, dtype=np.float32))
-        y = be.uninit_buffer(rows)
-        if kind == "gemv_list":
+        nvec = batch if kind == "gemv_batch" else 1
+        x = be.init_buffer(rng.standard_normal(nvec * cols, dtype=np.float32))
+        y = be.uninit_buffer(nvec * rows)
+        if kind == "gemv_batch":
+            for _ in range(3):
+                for w in ws:
+                    vb.Gemv().dispatch(be, None, y, w, x, batch=nvec)
+        elif kind == "gemv_list":
             batch = vb.GemvBatch(be, [{"w": w, "x": x.ptr, "y": y.ptr} for w in ws])
             for _ in range(3):
                 batch.launch()

@@ -21,15 +21,16 @@
 //     X is fixed point relative to the largest |x| of its vector inside a slice of 32 * NBW columns
 //     (256 for the usual shapes): |X| < 2^22 for Q4_0 and < 2^19 for Q8_0, so that a block's recombined
 //     sum still fits 32 bits.  The slice sums are scaled by the slice's factor in f32.
-//   * The main kernel is persistent, one CTA per SM: producer warp (bulk TMA copies of 16-row tiles, rows
-//     padded apart in shared memory so that fragment loads hit 32 different banks), 8 consumer warps,
-//     epilogue warp.  The columns are split over CS CTAs so that a CTA's share of the planes (25 bytes per
+//   * The main kernel is persistent, one CTA per SM: producer thread (one tiled TMA load per 16-row tile,
+//     128-byte swizzle so that fragment loads hit 32 different banks), 8 consumer warps, epilogue warp.  The columns are split over CS CTAs so that a CTA's share of the planes (25 bytes per
 //     column) stays resident in its shared memory; the 8 warps of a CTA split a tile's columns further and
-//     keep their B fragments in registers while they walk up to 8 row tiles.
+//     keep their B fragments in registers while they walk up to 4 row tiles.
 //   * Partial sums meet in shared memory (the 8 warps of a CTA, fixed order) and, when the columns are
-//     split over several CTAs, in scratch memory: each CTA stores its part, and whichever arrives last at
-//     the tile's counter adds the parts in a fixed order and writes y.  No CTA ever waits for another.
+//     split over several CTAs, in scratch memory: the CTAs of a row tile run side by side; all but the
+//     first store their part as {value, launch serial} pairs, the first adds them in a fixed order and
+//     writes y.
 // All waits are bounded (see vx_sm100.cuh).
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -44,7 +45,7 @@ using namespace sm100;
 
 constexpr int kVecs = 8;                 // vectors per pass (the MMA's n)
 constexpr int kUnitRows = 16;            // rows per tile (the MMA's m)
-constexpr int kGroup = 8;                // row tiles a warp carries per pass over its columns
+constexpr int kGroup = 4;                // row tiles a warp walks with one set of B fragments
 constexpr int kWarps = 8;                // consumer warps
 constexpr int kRedSlots = 4;
 constexpr int kRedStride = 20;           // floats between vectors in a reduction slot (16 rows + padding)
@@ -64,14 +65,15 @@ struct MmaParams {
     uint32_t cs;                  // column parts
     uint32_t kc_blocks;           // blocks per part
     uint32_t nkt;                 // column tiles per part
-    uint32_t stages, stage_bytes, q_row_stride, s_row_stride, s_off;
+    uint32_t stages, stage_bytes, s_off;
+    uint32_t ring_off;            // offset of the ring in shared memory (1024-byte aligned: the swizzle works on address bits)
     const uint8_t* planes;        // [nb][block_planes(MODE)]
     const float* sx;              // [slices][kVecs]: per column, the factor its slice sums are scaled by
     float* y;
     uint64_t y_stride;
     uint32_t batch;
-    float* partial;               // [cs][kVecs][nrows16]
-    uint32_t* counters;           // one per row tile
+    uint64_t* partial;            // [cs - 1][kVecs][nrows16] pairs {f32 sum, u32 launch serial}
+    const uint32_t* serial;       // number of pre-pass kernels run so far on this context
     uint32_t nrows16;             // rows rounded up to whole tiles
     vx::DeviceStatus* status;
 };
@@ -88,11 +90,11 @@ __device__ __forceinline__ void report(vx::DeviceStatus* st, uint32_t code) {
 template <bool A_SIGNED>
 __device__ __forceinline__ void mma_i8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const int (&c)[4]) {
     if constexpr (A_SIGNED)
-        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
     else
-        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
@@ -104,7 +106,15 @@ __device__ __forceinline__ void mma_i8(int (&d)[4], const uint32_t (&a)[4], uint
 // and words 4..7 the second one (the MMA's k = 4 t + i and 16 + 4 t + i).
 template <int QT, int MODE>
 __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, uint64_t x_stride, uint32_t batch,
-                                                      uint32_t nbw, uint8_t* __restrict__ planes, float* __restrict__ sx) {
+                                                      uint32_t nbw, uint8_t* __restrict__ planes, float* __restrict__ sx,
+                                                      uint32_t* serial) {
+    // Programmatic dependent launch on both sides: the main kernel may become resident and start streaming
+    // weights while this one runs (it reads the planes only after this grid has completed), and this grid
+    // may start under the tail of the kernel before it, whose output x may be and whose planes these are.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // one thread of the grid counts the launch: the main kernel tags its exchanged partial sums with the count
+    if (blockIdx.x == 0 && threadIdx.x == 0) *serial = *serial + 1;
     constexpr float kXMax = QT == 1 ? 4194302.0f : 524286.0f;
     constexpr uint32_t kBP = block_planes(MODE);
     const uint32_t slice = blockIdx.x, col = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,9 +149,19 @@ __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ 
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
         poison += __shfl_xor_sync(0xffffffffu, poison, off);
     }
+    // a slice whose values are all tiny: scale it up by an exact power of two first, so that neither the
+    // quotient below nor its inverse leaves the normal range
+    const bool tiny = amax < 1.0e-20f;
+    if (tiny) {
+        amax *= 0x1p64f;
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[r][i] *= 0x1p64f;
+    }
     float inv = amax > 0.0f ? kXMax / amax : 0.0f;
     float s = amax / kXMax;
-    if (amax > 0.0f && amax < kXMax / 1.0e38f) { inv = 0x1p100f; s = 0x1p-100f; }   // the quotient would overflow
+    if (tiny) s *= 0x1p-64f;
     if (poison != poison) { inv = 0.0f; s = poison; }                                // NaN or infinity in x: NaN in y
     if (lane == 0) {
         const float weight = MODE == FULL ? 1.0f : plane == 0 ? 65536.0f : plane == 1 ? 256.0f : 1.0f;
@@ -195,17 +215,23 @@ __device__ __forceinline__ void my_units(const MmaParams& p, uint32_t* u0, uint3
 }
 
 template <int QT, int NBW, int MODE>
-__global__ void __launch_bounds__(kWarps * 32 + 64, 1) gemv_mma_kernel(const __grid_constant__ MmaParams p) {
+__global__ void __launch_bounds__(kWarps * 32 + 64, 1)
+gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUtensorMap map_q,
+                const __grid_constant__ CUtensorMap map_s) {
     constexpr int QB = QT == 1 ? 16 : 32;   // bytes of quants per block
     constexpr int NP = MODE == FULL ? 3 : 1;
     constexpr uint32_t kBP = block_planes(MODE);
-    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr bool S_SWZ = NBW == 8;        // the scales of a tile are 128 bytes per row: swizzled like the quants
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    // the swizzle of the tiled copies works on shared-memory address bits: start the layout on a 1024-byte boundary
+    uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const uint32_t plane_bytes = p.kc_blocks * kBP;
     uint8_t* s_planes = smem;
     float* s_sx = reinterpret_cast<float*>(smem + plane_bytes);                       // [nkt * kWarps][kVecs]
-    uint8_t* ring = smem + plane_bytes + ((p.nkt * kWarps * kVecs * 4 + 127) & ~127u);
+    uint8_t* ring = smem + p.ring_off;
     float* red = reinterpret_cast<float*>(ring + (size_t)p.stages * p.stage_bytes);   // [kRedSlots][kWarps][kRedWarp]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(red + kRedSlots * kWarps * kRedWarp);
+    float* s_acc = red + kRedSlots * kWarps * kRedWarp;                               // [kGroup][kWarps * 32] float4, if nkt > 1
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_acc + (p.nkt > 1 ? kGroup * kWarps * 32 * 4 : 0));
     const uint32_t bar0 = smem_addr(bars);
     auto full = [&](uint32_t s) { return bar0 + 8u * s; };
     auto empty = [&](uint32_t s) { return bar0 + 8u * (kMaxStages + s); };
@@ -243,6 +269,7 @@ __global__ void __launch_bounds__(kWarps * 32 + 64, 1) gemv_mma_kernel(const __g
         const uint32_t lane = tid & 31, r = lane & 15, half = lane >> 4;
         constexpr int NV = MODE == FULL ? kVecs / 2 : 1;     // vectors per lane
         asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the kernel before the pre-pass
+        const uint32_t serial = *(volatile const uint32_t*)p.serial;   // bumped by this launch's pre-pass kernel
         uint32_t k = 0;
         for (uint32_t u = u0; u < u1; ++u, ++k) {
             const uint32_t b = k % kRedSlots;
@@ -277,30 +304,41 @@ __global__ void __launch_bounds__(kWarps * 32 + 64, 1) gemv_mma_kernel(const __g
                     const uint32_t v = 2 * i + half;
                     if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = sum[i];
                 }
-            } else {
-                // this part's sums go to scratch; whoever arrives last at the tile's counter adds the parts
+            } else if (kpart != 0) {
+                // Parts other than the first hand their sums to the first part's CTA through scratch memory:
+                // value and launch serial in ONE 64-bit store, so that no fence is needed (a GPU-scope fence
+                // stalls the SM's whole memory pipeline while its TMA loads are in flight: measured, the
+                // fence-and-counter form of this exchange doubled the kernel's time).
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
                     const uint32_t v = 2 * i + half;
-                    __stcg(p.partial + ((size_t)kpart * kVecs + v) * p.nrows16 + row, sum[i]);
+                    const uint64_t pair = ((uint64_t)serial << 32) | __float_as_uint(sum[i]);
+                    st_relaxed_gpu_u64(p.partial + ((size_t)(kpart - 1) * kVecs + v) * p.nrows16 + row, pair);
                 }
-                __threadfence();
-                __syncwarp();
-                uint32_t old = 0;
-                if (lane == 0) old = atomicAdd(p.counters + u, 1u);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == p.cs - 1) {
-                    __threadfence();
+            } else {
+                // The first part adds the others' sums in a fixed order.  Their CTAs walk the same row tiles
+                // at the same time, so a pair that does not carry this launch's serial yet is about to; it is
+                // re-read for a bounded time.
 #pragma unroll
-                    for (int i = 0; i < NV; ++i) {
-                        const uint32_t v = 2 * i + half;
-                        float s = 0.0f;
-                        for (uint32_t kp = 0; kp < p.cs; ++kp)
-                            s += __ldcg(p.partial + ((size_t)kp * kVecs + v) * p.nrows16 + row);
-                        if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = s;
+                for (int i = 0; i < NV; ++i) {
+                    const uint32_t v = 2 * i + half;
+                    float s = sum[i];
+                    for (uint32_t kp = 1; kp < p.cs; ++kp) {
+                        const uint64_t* src = p.partial + ((size_t)(kp - 1) * kVecs + v) * p.nrows16 + row;
+                        uint64_t pair = ld_relaxed_gpu_u64(src);
+                        if ((uint32_t)(pair >> 32) != serial) {
+                            const long long start = clock64();
+                            while ((uint32_t)((pair = ld_relaxed_gpu_u64(src)) >> 32) != serial) {
+                                if (*abort_flag != 0u || clock64() - start > kWaitCycles) {
+                                    if (*abort_flag == 0u) report(p.status, 47);
+                                    *abort_flag = 1u;
+                                    break;
+                                }
+                            }
+                        }
+                        s += __uint_as_float((uint32_t)pair);
                     }
-                    __syncwarp();
-                    if (lane == 0) p.counters[u] = 0;        // ready for the next launch
+                    if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = s;
                 }
             }
         }
@@ -308,34 +346,31 @@ __global__ void __launch_bounds__(kWarps * 32 + 64, 1) gemv_mma_kernel(const __g
     }
     if (tid >= kWarps * 32) {
         // ------------------------------------------------------------ producer warp ----
-        // Lane r copies row r of every tile: its quants for the tile's columns and its scales.
-        const uint32_t lane = tid & 31;
-        const uint64_t policy = policy_evict_first();
-        uint32_t k = 0;
-        for (uint32_t g0 = u0; g0 < u1; g0 += kGroup) {
-            const uint32_t g1 = min(g0 + kGroup, u1);
-            for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-                const uint32_t blk0 = kpart * p.kc_blocks + kt * kt_blocks;       // first block of the tile in the row
-                for (uint32_t u = g0; u < g1; ++u, ++k) {
-                    const uint32_t s = k % p.stages, use = k / p.stages;
-                    if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1, abort_flag)) report(p.status, 41);
-                    const uint32_t first = u * kUnitRows;
-                    const uint32_t rows = min((uint32_t)kUnitRows, p.nrows - first);
-                    const uint32_t dst = smem_addr(ring + (size_t)s * p.stage_bytes);
-                    if (lane == 0) mbar_arrive_expect_tx(full(s), rows * (q_tile_bytes + kt_blocks * 2));
-                    __syncwarp();
-                    if (lane < rows) {
-                        const uint64_t row = p.row0 + first + lane;
-                        bulk_g2s_hint(dst + lane * p.q_row_stride, p.quants + row * p.row_bytes + (uint64_t)blk0 * QB,
-                                      q_tile_bytes, full(s), policy);
-                        bulk_g2s_hint(dst + p.s_off + lane * p.s_row_stride, p.scales + (row * p.nb + blk0) * 2,
-                                      kt_blocks * 2, full(s), policy);
+        // One thread, two tiled TMA loads per stage: the tile's quants as a box of 128 bytes x 16 rows x the
+        // tile's 128-byte column chunks (shared memory: [chunk][row][128 bytes], 128-byte swizzle, so that the
+        // eight rows a fragment load touches sit in eight different bank groups), and its scales.  Rows beyond
+        // the matrix read as zeros.  (Row-by-row bulk copies of 1 KB do not keep up: an SM completes about
+        // one bulk copy per 75 cycles whatever its size.)
+        if (tid == kWarps * 32) {
+            tma_prefetch_desc(&map_q);
+            tma_prefetch_desc(&map_s);
+            uint32_t k = 0;
+            for (uint32_t g0 = u0; g0 < u1; g0 += kGroup) {
+                const uint32_t g1 = min(g0 + kGroup, u1);
+                for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+                    const uint32_t blk0 = kpart * p.kc_blocks + kt * kt_blocks;       // first block of the tile in the row
+                    for (uint32_t u = g0; u < g1; ++u, ++k) {
+                        const uint32_t s = k % p.stages, use = k / p.stages;
+                        if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1, abort_flag)) report(p.status, 41);
+                        const int32_t row = (int32_t)(p.row0 + (uint64_t)u * kUnitRows);
+                        const uint32_t dst = smem_addr(ring + (size_t)s * p.stage_bytes);
+                        mbar_arrive_expect_tx(full(s), kUnitRows * (q_tile_bytes + (S_SWZ ? 128u : kt_blocks * 2)));
+                        tma_load_3d(dst, &map_q, 0, row, (int32_t)(blk0 * QB / 128), full(s));
+                        tma_load_2d(dst + p.s_off, &map_s, (int32_t)(blk0 * 2), row, full(s));
                     }
                 }
             }
-        }
-        // do not leave while copies into this CTA's shared memory may still be in flight
-        if (lane == 0) {
+            // do not leave while copies into this CTA's shared memory may still be in flight
             for (uint32_t s = 0; s < p.stages && s < k; ++s) {
                 const uint32_t last_k = ((k - 1 - s) / p.stages) * p.stages + s;
                 if (!mbar_wait(empty(s), (last_k / p.stages) & 1, abort_flag)) report(p.status, 42);
@@ -357,15 +392,12 @@ __global__ void __launch_bounds__(kWarps * 32 + 64, 1) gemv_mma_kernel(const __g
     }
     if (!mbar_wait(planes_bar, 0, abort_flag)) report(p.status, 45);
 
+    // Sums of a group's row tiles between two passes over the columns: shared memory, one float4 per thread
+    // and tile (only touched when a part has more than one column tile).
+    float4* acc_sm = reinterpret_cast<float4*>(s_acc) + warp * 32 + lane;
     uint32_t k = 0, kr = 0;
     for (uint32_t g0 = u0; g0 < u1; g0 += kGroup) {
         const uint32_t nu = min((uint32_t)kGroup, u1 - g0);
-        float acc[kGroup][4];
-#pragma unroll
-        for (int i = 0; i < kGroup; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
-
         for (uint32_t kt = 0; kt < p.nkt; ++kt) {
             // this warp's B fragments for its NBW blocks of the tile, kept in registers over the row tiles
             uint32_t B[NBW][NP][2];
@@ -385,93 +417,102 @@ __global__ void __launch_bounds__(kWarps * 32 + 64, 1) gemv_mma_kernel(const __g
                 init[j][1] = iv.y;
             }
             const float2 sxv = *reinterpret_cast<const float2*>(s_sx + (size_t)(kt * kWarps + warp) * kVecs + 2 * t);
+            const bool first_kt = kt == 0, last_kt = kt == p.nkt - 1;
 
-#pragma unroll
-            for (int i = 0; i < kGroup; ++i) {
-                if ((uint32_t)i < nu) {
-                    const uint32_t s = k % p.stages;
-                    if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 43);
-                    const uint8_t* sq = ring + (size_t)s * p.stage_bytes;
-                    const uint8_t* ss = sq + p.s_off;
-                    // the NBW scales of rows g and g + 8
-                    __align__(16) __half dlo[NBW], dhi[NBW];
-                    {
-                        const uint8_t* a = ss + g * p.s_row_stride + warp * NBW * 2;
-                        const uint8_t* b = ss + (g + 8) * p.s_row_stride + warp * NBW * 2;
-                        if constexpr (NBW == 8) {
-                            *reinterpret_cast<uint4*>(dlo) = *reinterpret_cast<const uint4*>(a);
-                            *reinterpret_cast<uint4*>(dhi) = *reinterpret_cast<const uint4*>(b);
-                        } else if constexpr (NBW == 4) {
-                            *reinterpret_cast<uint2*>(dlo) = *reinterpret_cast<const uint2*>(a);
-                            *reinterpret_cast<uint2*>(dhi) = *reinterpret_cast<const uint2*>(b);
-                        } else if constexpr (NBW == 2) {
-                            *reinterpret_cast<uint32_t*>(dlo) = *reinterpret_cast<const uint32_t*>(a);
-                            *reinterpret_cast<uint32_t*>(dhi) = *reinterpret_cast<const uint32_t*>(b);
-                        } else {
-                            dlo[0] = *reinterpret_cast<const __half*>(a);
-                            dhi[0] = *reinterpret_cast<const __half*>(b);
-                        }
+#pragma unroll 1
+            for (uint32_t i = 0; i < nu; ++i, ++k) {
+                const uint32_t s = k % p.stages;
+                if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 43);
+                const uint8_t* sq = ring + (size_t)s * p.stage_bytes;
+                const uint8_t* ss = sq + p.s_off;
+                // the NBW scales of rows g and g + 8 (rows of 16 NBW bytes; with NBW = 8 the 16-byte group of
+                // warp w sits at position w ^ row inside its row's 128 bytes)
+                __align__(16) __half dlo[NBW], dhi[NBW];
+                {
+                    const uint32_t srow = kt_blocks * 2;
+                    const uint32_t at = S_SWZ ? ((warp ^ g) * 16) : warp * NBW * 2;
+                    const uint8_t* a = ss + g * srow + at;
+                    const uint8_t* b = a + 8 * srow;
+                    if constexpr (NBW == 8) {
+                        *reinterpret_cast<uint4*>(dlo) = *reinterpret_cast<const uint4*>(a);
+                        *reinterpret_cast<uint4*>(dhi) = *reinterpret_cast<const uint4*>(b);
+                    } else if constexpr (NBW == 4) {
+                        *reinterpret_cast<uint2*>(dlo) = *reinterpret_cast<const uint2*>(a);
+                        *reinterpret_cast<uint2*>(dhi) = *reinterpret_cast<const uint2*>(b);
+                    } else if constexpr (NBW == 2) {
+                        *reinterpret_cast<uint32_t*>(dlo) = *reinterpret_cast<const uint32_t*>(a);
+                        *reinterpret_cast<uint32_t*>(dhi) = *reinterpret_cast<const uint32_t*>(b);
+                    } else {
+                        dlo[0] = *reinterpret_cast<const __half*>(a);
+                        dhi[0] = *reinterpret_cast<const __half*>(b);
                     }
-                    float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                }
+                // row g of the tile: [chunk][row][128 bytes]; 16-byte group `sub` of a row sits at sub ^ (row & 7)
+                const uint8_t* qrow = sq + g * 128 + t * 4;
+                float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                    for (int j = 0; j < NBW; ++j) {
-                        const uint8_t* qa = sq + g * p.q_row_stride + (warp * NBW + j) * QB + t * 4;
-                        const uint8_t* qb = qa + 8 * p.q_row_stride;
-                        uint32_t A[4];
-                        if constexpr (QT == 1) {
-                            const uint32_t wa = *reinterpret_cast<const uint32_t*>(qa);
-                            const uint32_t wb = *reinterpret_cast<const uint32_t*>(qb);
-                            A[0] = wa & 0x0F0F0F0Fu;
-                            A[1] = wb & 0x0F0F0F0Fu;
-                            A[2] = (wa >> 4) & 0x0F0F0F0Fu;
-                            A[3] = (wb >> 4) & 0x0F0F0F0Fu;
-                        } else {
-                            A[0] = *reinterpret_cast<const uint32_t*>(qa);
-                            A[1] = *reinterpret_cast<const uint32_t*>(qb);
-                            A[2] = *reinterpret_cast<const uint32_t*>(qa + 16);
-                            A[3] = *reinterpret_cast<const uint32_t*>(qb + 16);
-                        }
-                        const int c_init[4] = {init[j][0], init[j][1], init[j][0], init[j][1]};
-                        const float dl = __half2float(dlo[j]), dh = __half2float(dhi[j]);
-                        if constexpr (MODE == FULL) {
-                            const int zero[4] = {0, 0, 0, 0};
-                            int ca[4], cb[4], cc[4];
-                            mma_i8<QT == 0>(ca, A, B[j][0][0], B[j][0][1], zero);
-                            mma_i8<QT == 0>(cb, A, B[j][1][0], B[j][1][1], zero);
-                            mma_i8<QT == 0>(cc, A, B[j][2][0], B[j][2][1], c_init);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                // sum q X = 65536 sa + 256 sb + sc, exact in 32 bits by the bound on |X|
-                                const int tsum = ca[e] * 65536 + (cb[e] * 256 + cc[e]);
-                                sacc[e] = fmaf(e < 2 ? dl : dh, (float)tsum, sacc[e]);
-                            }
-                        } else {
-                            int c[4];
-                            mma_i8<QT == 0>(c, A, B[j][0][0], B[j][0][1], c_init);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) sacc[e] = fmaf(e < 2 ? dl : dh, (float)c[e], sacc[e]);
-                        }
+                for (int j = 0; j < NBW; ++j) {
+                    const uint32_t off = (warp * NBW + j) * QB;                       // byte offset of the block in the tile's row
+                    const uint8_t* qa = qrow + (off >> 7) * 2048 + ((((off >> 4) & 7) ^ g) << 4);
+                    const uint8_t* qb = qa + 1024;                                      // row g + 8: same swizzle
+                    uint32_t A[4];
+                    if constexpr (QT == 1) {
+                        const uint32_t wa = *reinterpret_cast<const uint32_t*>(qa);
+                        const uint32_t wb = *reinterpret_cast<const uint32_t*>(qb);
+                        A[0] = wa & 0x0F0F0F0Fu;
+                        A[1] = wb & 0x0F0F0F0Fu;
+                        A[2] = (wa >> 4) & 0x0F0F0F0Fu;
+                        A[3] = (wb >> 4) & 0x0F0F0F0Fu;
+                    } else {
+                        // the block's second 16 bytes: the next group of the row
+                        const uint8_t* qa2 = qrow + (off >> 7) * 2048 + (((((off >> 4) & 7) + 1) ^ g) << 4);
+                        A[0] = *reinterpret_cast<const uint32_t*>(qa);
+                        A[1] = *reinterpret_cast<const uint32_t*>(qb);
+                        A[2] = *reinterpret_cast<const uint32_t*>(qa2);
+                        A[3] = *reinterpret_cast<const uint32_t*>(qa2 + 1024);
                     }
+                    const int c_init[4] = {init[j][0], init[j][1], init[j][0], init[j][1]};
+                    const float dl = __half2float(dlo[j]), dh = __half2float(dhi[j]);
+                    if constexpr (MODE == FULL) {
+                        const int zero[4] = {0, 0, 0, 0};
+                        int ca[4], cb[4], cc[4];
+                        mma_i8<QT == 0>(ca, A, B[j][0][0], B[j][0][1], zero);
+                        mma_i8<QT == 0>(cb, A, B[j][1][0], B[j][1][1], zero);
+                        mma_i8<QT == 0>(cc, A, B[j][2][0], B[j][2][1], c_init);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            // sum q X = 65536 sa + 256 sb + sc, exact in 32 bits by the bound on |X|
+                            const int tsum = ca[e] * 65536 + (cb[e] * 256 + cc[e]);
+                            sacc[e] = fmaf(e < 2 ? dl : dh, (float)tsum, sacc[e]);
+                        }
+                    } else {
+                        int c[4];
+                        mma_i8<QT == 0>(c, A, B[j][0][0], B[j][0][1], c_init);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sacc[e] = fmaf(e < 2 ? dl : dh, (float)c[e], sacc[e]);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty(s));
+                float4 a4 = first_kt ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : acc_sm[i * (kWarps * 32)];
+                a4.x = fmaf(sxv.x, sacc[0], a4.x);
+                a4.y = fmaf(sxv.y, sacc[1], a4.y);
+                a4.z = fmaf(sxv.x, sacc[2], a4.z);
+                a4.w = fmaf(sxv.y, sacc[3], a4.w);
+                if (!last_kt) {
+                    acc_sm[i * (kWarps * 32)] = a4;
+                } else {
+                    // the tile is complete for this warp's columns: hand it to the epilogue warp
+                    const uint32_t b = kr % kRedSlots;
+                    if (kr >= kRedSlots && !mbar_wait(red_empty(b), ((kr / kRedSlots) - 1) & 1, abort_flag)) report(p.status, 46);
+                    float* slot = red + ((size_t)b * kWarps + warp) * kRedWarp;
+                    slot[(2 * t) * kRedStride + g] = a4.x;
+                    slot[(2 * t + 1) * kRedStride + g] = a4.y;
+                    slot[(2 * t) * kRedStride + g + 8] = a4.z;
+                    slot[(2 * t + 1) * kRedStride + g + 8] = a4.w;
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(empty(s));
-                    ++k;
-                    acc[i][0] = fmaf(sxv.x, sacc[0], acc[i][0]);
-                    acc[i][1] = fmaf(sxv.y, sacc[1], acc[i][1]);
-                    acc[i][2] = fmaf(sxv.x, sacc[2], acc[i][2]);
-                    acc[i][3] = fmaf(sxv.y, sacc[3], acc[i][3]);
-                    if (kt == p.nkt - 1) {
-                        // the tile is complete for this warp's columns: hand it to the epilogue warp
-                        const uint32_t b = kr % kRedSlots;
-                        if (kr >= kRedSlots && !mbar_wait(red_empty(b), ((kr / kRedSlots) - 1) & 1, abort_flag)) report(p.status, 46);
-                        float* slot = red + ((size_t)b * kWarps + warp) * kRedWarp;
-                        slot[(2 * t) * kRedStride + g] = acc[i][0];
-                        slot[(2 * t + 1) * kRedStride + g] = acc[i][1];
-                        slot[(2 * t) * kRedStride + g + 8] = acc[i][2];
-                        slot[(2 * t + 1) * kRedStride + g + 8] = acc[i][3];
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(red_full(b));
-                        ++kr;
-                    }
+                    if (lane == 0) mbar_arrive(red_full(b));
+                    ++kr;
                 }
             }
         }
@@ -479,7 +520,7 @@ __global__ void __launch_bounds__(kWarps * 32 + 64, 1) gemv_mma_kernel(const __g
 }
 
 struct MmaConfig {
-    uint32_t cs, nbw, stages, stage_bytes, q_row_stride, s_row_stride, s_off, kc_blocks, nkt;
+    uint32_t cs, nbw, stages, stage_bytes, s_off, ring_off, kc_blocks, nkt;
     int mode;
     size_t smem;
 };
@@ -501,24 +542,72 @@ bool choose(const vx_qweights* w, uint32_t batch, MmaConfig* c) {
         c->nbw = nbw;
         c->kc_blocks = kc_blocks;
         c->nkt = kc_blocks / kt_blocks;
-        c->q_row_stride = kt_blocks * qb + 16;                  // rows 16 bytes out of step: fragment loads hit 32 banks
-        c->s_row_stride = ((kt_blocks * 2 + 15) & ~15u) + 16;
-        c->s_off = (kUnitRows * c->q_row_stride + 127) & ~127u;
-        c->stage_bytes = (c->s_off + kUnitRows * c->s_row_stride + 127) & ~127u;
-        const size_t fixed = (size_t)kc_blocks * bp + ((c->nkt * kWarps * kVecs * 4 + 127) & ~127u) +
-                             (size_t)kRedSlots * kWarps * kRedWarp * 4 + (2 * kMaxStages + 2 * kRedSlots + 2) * 8;
-        const size_t room = (size_t)227 * 1024 - 1024 - fixed;
+        c->s_off = kUnitRows * kt_blocks * qb;                  // a multiple of 2048
+        c->stage_bytes = (c->s_off + kUnitRows * kt_blocks * 2 + 1023) & ~1023u;
+        const size_t head = (size_t)kc_blocks * bp + (size_t)c->nkt * kWarps * kVecs * 4;
+        c->ring_off = (uint32_t)((head + 1023) & ~(size_t)1023);
+        const size_t tail = (size_t)kRedSlots * kWarps * kRedWarp * 4 + (c->nkt > 1 ? (size_t)kGroup * kWarps * 32 * 16 : 0) +
+                            (2 * kMaxStages + 2 * kRedSlots + 2) * 8;
+        const size_t room = (size_t)227 * 1024 - 1024 - c->ring_off - tail;   // 1024: the dynamic window's own alignment
         const uint32_t stages = (uint32_t)std::min<size_t>(kMaxStages, room / c->stage_bytes);
         if (stages < 2) continue;
         c->stages = stages;
-        c->smem = fixed + (size_t)stages * c->stage_bytes;
+        c->smem = c->ring_off + (size_t)stages * c->stage_bytes + tail + 1024;
         return true;
     }
     return false;
 }
 
+// cuTensorMapEncodeTiled, fetched from the driver at run time (no link-time dependency on libcuda).
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+    static std::atomic<EncodeFn> fn{nullptr};
+    EncodeFn f = fn.load(std::memory_order_acquire);
+    if (!f) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            f = reinterpret_cast<EncodeFn>(sym);
+        (void)cudaGetLastError();
+        fn.store(f, std::memory_order_release);
+    }
+    return f;
+}
+
+// The quants plane as bytes [column chunk of 128][row][128]: box = 128 bytes x 16 rows x the tile's chunks.
+// The scales plane as bytes [row][2 nb]: box = the tile's scales x 16 rows.
+bool make_maps(const vx_qweights* w, const MmaConfig& c, CUtensorMap* map_q, CUtensorMap* map_s) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const uint32_t qb = w->type == VX_Q4_0 ? 16 : 32;
+    const uint32_t kt_blocks = c.nbw * kWarps;
+    const cuuint32_t ones[3] = {1, 1, 1};
+    {
+        const cuuint64_t dims[3] = {128, w->rows, w->quant_row_bytes / 128};
+        const cuuint64_t strides[2] = {w->quant_row_bytes, 128};
+        const cuuint32_t box[3] = {128, (cuuint32_t)kUnitRows, kt_blocks * qb / 128};
+        if (fn(map_q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w->d_quants, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    {
+        const cuuint64_t dims[2] = {w->blocks_per_row * 2, w->rows};
+        const cuuint64_t strides[1] = {w->blocks_per_row * 2};
+        const cuuint32_t box[2] = {kt_blocks * 2, (cuuint32_t)kUnitRows};
+        if (fn(map_s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->d_scales, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               c.nbw == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    return true;
+}
+
 template <int QT, int NBW, int MODE>
-vx_status launch_main(vx_context* ctx, const MmaParams& p, uint32_t grid, size_t smem) {
+vx_status launch_main(vx_context* ctx, const MmaParams& p, const CUtensorMap& mq, const CUtensorMap& ms, uint32_t grid,
+                      size_t smem) {
     auto kernel = gemv_mma_kernel<QT, NBW, MODE>;
     static std::atomic<size_t> granted[64];
     const int dev = ctx->device & 63;
@@ -538,17 +627,18 @@ vx_status launch_main(vx_context* ctx, const MmaParams& p, uint32_t grid, size_t
     // the weights may have been written by a kernel of this stream (device quantiser): then no early start
     cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 && !ctx->weights_fresh ? 1 : 0;
     ctx->weights_fresh = false;
-    VX_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    VX_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, mq, ms));
     return VX_OK;
 }
 
 template <int QT, int MODE>
-vx_status launch_nbw(vx_context* ctx, uint32_t nbw, const MmaParams& p, uint32_t grid, size_t smem) {
+vx_status launch_nbw(vx_context* ctx, uint32_t nbw, const MmaParams& p, const CUtensorMap& mq, const CUtensorMap& ms,
+                     uint32_t grid, size_t smem) {
     switch (nbw) {
-        case 8: return launch_main<QT, 8, MODE>(ctx, p, grid, smem);
-        case 4: return launch_main<QT, 4, MODE>(ctx, p, grid, smem);
-        case 2: return launch_main<QT, 2, MODE>(ctx, p, grid, smem);
-        default: return launch_main<QT, 1, MODE>(ctx, p, grid, smem);
+        case 8: return launch_main<QT, 8, MODE>(ctx, p, mq, ms, grid, smem);
+        case 4: return launch_main<QT, 4, MODE>(ctx, p, mq, ms, grid, smem);
+        case 2: return launch_main<QT, 2, MODE>(ctx, p, mq, ms, grid, smem);
+        default: return launch_main<QT, 1, MODE>(ctx, p, mq, ms, grid, smem);
     }
 }
 
@@ -576,28 +666,41 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
     *eligible = false;
     MmaConfig c;
     if (batch < 1 || batch > (uint32_t)kVecs || !choose(w, batch, &c)) return VX_OK;
+    CUtensorMap map_q, map_s;
+    if (!make_maps(w, c, &map_q, &map_s)) return VX_OK;
     const uint32_t nb = (uint32_t)w->blocks_per_row;
     const uint32_t nrows16 = (nrows + kUnitRows - 1) / kUnitRows * kUnitRows;
     const uint32_t slices = nb / c.nbw;
     const size_t planes_bytes = ((size_t)nb * block_planes(c.mode) + 255) & ~(size_t)255;
     vx_status st = ensure(ctx, &ctx->mma_planes, &ctx->mma_planes_bytes, planes_bytes + (size_t)slices * kVecs * 4);
     if (st != VX_OK) return st;
+    st = ensure(ctx, &ctx->mma_counters, &ctx->mma_counters_bytes, 256);
+    if (st != VX_OK) return st;
     if (c.cs > 1) {
-        st = ensure(ctx, &ctx->mma_partial, &ctx->mma_partial_bytes, (size_t)c.cs * kVecs * nrows16 * 4);
-        if (st != VX_OK) return st;
-        st = ensure(ctx, &ctx->mma_counters, &ctx->mma_counters_bytes, (size_t)(nrows16 / kUnitRows) * 4);
+        st = ensure(ctx, &ctx->mma_partial, &ctx->mma_partial_bytes, (size_t)(c.cs - 1) * kVecs * nrows16 * 8);
         if (st != VX_OK) return st;
     }
     uint8_t* planes = static_cast<uint8_t*>(ctx->mma_planes);
     float* sx = reinterpret_cast<float*>(planes + planes_bytes);
+    uint32_t* serial = static_cast<uint32_t*>(ctx->mma_counters);
 
     const bool q4 = w->type == VX_Q4_0;
-    if (c.mode == FULL) {
-        if (q4) xplanes_kernel<1, FULL><<<slices, 256, 0, ctx->stream>>>(x, x_stride, batch, c.nbw, planes, sx);
-        else xplanes_kernel<0, FULL><<<slices, 256, 0, ctx->stream>>>(x, x_stride, batch, c.nbw, planes, sx);
-    } else {
-        if (q4) xplanes_kernel<1, SINGLE><<<slices, 256, 0, ctx->stream>>>(x, x_stride, batch, c.nbw, planes, sx);
-        else xplanes_kernel<0, SINGLE><<<slices, 256, 0, ctx->stream>>>(x, x_stride, batch, c.nbw, planes, sx);
+    {
+        auto pre = c.mode == FULL ? (q4 ? xplanes_kernel<1, FULL> : xplanes_kernel<0, FULL>)
+                                  : (q4 ? xplanes_kernel<1, SINGLE> : xplanes_kernel<0, SINGLE>);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(slices);
+        cfg.blockDim = dim3(256);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        // Early start only without a column split: with one, the CTAs of a row tile wait for each other's sums
+        // and must start together, which they do when the grid starts on an idle GPU (measured: 20 % slower
+        // when the CTAs of a launch trickle in under the tail of the launch before).
+        cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 && c.cs == 1 ? 1 : 0;
+        VX_CUDA(cudaLaunchKernelEx(&cfg, pre, x, (uint64_t)x_stride, batch, c.nbw, planes, sx, serial));
     }
     VX_CUDA(cudaGetLastError());
     ctx->launches++;
@@ -614,25 +717,24 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
     p.nkt = c.nkt;
     p.stages = c.stages;
     p.stage_bytes = c.stage_bytes;
-    p.q_row_stride = c.q_row_stride;
-    p.s_row_stride = c.s_row_stride;
     p.s_off = c.s_off;
+    p.ring_off = c.ring_off;
     p.planes = planes;
     p.sx = sx;
     p.y = y;
     p.y_stride = y_stride;
     p.batch = batch;
-    p.partial = static_cast<float*>(ctx->mma_partial);
-    p.counters = static_cast<uint32_t*>(ctx->mma_counters);
+    p.partial = static_cast<uint64_t*>(ctx->mma_partial);
+    p.serial = serial;
     p.nrows16 = nrows16;
     p.status = ctx->d_status;
     const uint32_t units = nrows16 / kUnitRows;
     const uint32_t pairs = std::max(1u, std::min((uint32_t)ctx->sm_count / c.cs, units));
     const uint32_t grid = pairs * c.cs;
     if (c.mode == FULL)
-        st = q4 ? launch_nbw<1, FULL>(ctx, c.nbw, p, grid, c.smem) : launch_nbw<0, FULL>(ctx, c.nbw, p, grid, c.smem);
+        st = q4 ? launch_nbw<1, FULL>(ctx, c.nbw, p, map_q, map_s, grid, c.smem) : launch_nbw<0, FULL>(ctx, c.nbw, p, map_q, map_s, grid, c.smem);
     else
-        st = q4 ? launch_nbw<1, SINGLE>(ctx, c.nbw, p, grid, c.smem) : launch_nbw<0, SINGLE>(ctx, c.nbw, p, grid, c.smem);
+        st = q4 ? launch_nbw<1, SINGLE>(ctx, c.nbw, p, map_q, map_s, grid, c.smem) : launch_nbw<0, SINGLE>(ctx, c.nbw, p, map_q, map_s, grid, c.smem);
     if (st != VX_OK) return st;
     ctx->launches++;
     ctx->status_dirty = true;

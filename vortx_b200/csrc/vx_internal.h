@@ -73,7 +73,7 @@ struct vx_context {
     bool weights_fresh = false;            // a kernel of this stream has written quantised weights since the last GEMV launch
     void* reduce_scratch = nullptr;        // per-block partials of the wide reduction (device)
     // scratch of the tensor-core batch GEMV (device, grown on demand): x as fixed-point planes, the parts
-    // of a column split, one counter per row tile
+    // of a column split, the count of launches (word 0 of mma_counters)
     void* mma_planes = nullptr;
     size_t mma_planes_bytes = 0;
     void* mma_partial = nullptr;

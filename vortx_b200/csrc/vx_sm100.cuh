@@ -213,6 +213,14 @@ __device__ __forceinline__ int dp4a_ss(uint32_t a_signed, uint32_t b_signed, int
 __device__ __forceinline__ void st_relaxed_sys_u64(uint64_t* ptr, uint64_t v) {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(ptr), "l"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_gpu_u64(uint64_t* ptr, uint64_t v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(ptr), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_relaxed_gpu_u64(const uint64_t* ptr) {
+    uint64_t v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ptr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void ld_volatile_v2_u64(const uint64_t* ptr, uint64_t& a, uint64_t& b) {
     asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(ptr) : "memory");
 }
