@@ -3,8 +3,8 @@
 Two and more vectors take it by default; "gemv.batch_mma" = 1 sends single vectors through it too, which is
 how its one-MMA-per-block form (1 or 2 vectors) is reached.  Bars as for the streaming kernel: max-norm
 relative error <= 1e-4 against the f64 oracle and every element within 2e-6 of its conditioning sum |w||x|.
-x is held as 22-bit (Q4_0) or 19-bit (Q8_0) fixed point per 256-column slice here, so the second bar is the
-tighter one.
+x is held as 22-bit (Q4_0) or 19-bit (Q8_0) fixed point per slice of 128 or 256 columns here, so the second bar
+is the tighter one.  The column count must be a multiple of 256.
 """
 import numpy as np
 import pytest
@@ -47,9 +47,9 @@ def _run(backend, qm, x, row0=0, nrows=None, x_stride=None, y_stride=None):
 
 
 @pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
-@pytest.mark.parametrize("rows,cols,batch", [(16, 256, 2), (1, 256, 8), (37, 512, 3), (300, 768, 5), (130, 2048, 8),
-                                             (1000, 4096, 4), (257, 8192, 8), (64, 8192, 2), (90, 14336, 6),
-                                             (33, 28672, 8), (48, 1024, 11), (5000, 1024, 7)])
+@pytest.mark.parametrize("rows,cols,batch", [(16, 256, 2), (1, 512, 8), (37, 512, 3), (300, 768, 2), (300, 1536, 5),
+                                             (130, 2048, 8), (1000, 4096, 4), (257, 8192, 8), (64, 8192, 2),
+                                             (90, 14336, 6), (33, 28672, 8), (48, 1024, 11), (5000, 1024, 7)])
 def test_batch_gemv_on_tensor_cores(backend, oracle, qt, rows, cols, batch):
     w = synth.normal_matrix(rows, cols, seed=rows + cols)
     x = synth.normal_vectors(batch, cols, seed=batch)
@@ -102,9 +102,10 @@ def test_batch_gemv_slabs_strides_and_unaligned_x(backend, oracle):
     qm.free()
 
 
-def test_batch_gemv_falls_back_when_the_columns_do_not_fit(backend, oracle):
+@pytest.mark.parametrize("cols,batch", [(1056, 4), (1056, 2)])
+def test_batch_gemv_falls_back_when_the_columns_do_not_fit(backend, oracle, cols, batch):
     """Column counts that are not a multiple of 256 go through the streaming kernel, vector by vector."""
-    rows, cols, batch = 64, 1056, 4
+    rows = 64
     w = synth.normal_matrix(rows, cols, seed=3)
     x = synth.normal_vectors(batch, cols, seed=4)
     blocks = oracle.quantize(vb.Q4_0, w)

@@ -22,13 +22,20 @@
 //     (256 for the usual shapes): |X| < 2^22 for Q4_0 and < 2^19 for Q8_0, so that a block's recombined
 //     sum still fits 32 bits.  The slice sums are scaled by the slice's factor in f32.
 //   * The main kernel is persistent, one CTA per SM: producer thread (one tiled TMA load per 16-row tile,
-//     128-byte swizzle so that fragment loads hit 32 different banks), 8 consumer warps, epilogue warp.  The columns are split over CS CTAs so that a CTA's share of the planes (25 bytes per
-//     column) stays resident in its shared memory; the 8 warps of a CTA split a tile's columns further and
-//     keep their B fragments in registers while they walk up to 4 row tiles.
+//     128-byte swizzle so that fragment loads hit 32 different banks), 8 consumer warps, epilogue warp.
+//     The columns are split over CS CTAs so that a CTA's share of the planes (25 bytes per column, 9 in the
+//     SINGLE form) stays resident in its shared memory; the 8 warps of a CTA split a tile's columns further
+//     and keep their B fragments in registers while they walk up to 4 row tiles.
 //   * Partial sums meet in shared memory (the 8 warps of a CTA, fixed order) and, when the columns are
 //     split over several CTAs, in scratch memory: the CTAs of a row tile run side by side; all but the
 //     first store their part as {value, launch serial} pairs, the first adds them in a fixed order and
 //     writes y.
+// Measured on B200 while building this (they shaped the design): an SM completes about one untiled bulk
+// copy per 75 cycles whatever its size, and one thread issues one per 450, so row-by-row copies of 1 KB
+// top out near 3 TB/s (hence one tiled load per tile); mma.sync m16n8k32 s8 has 20 cycles latency and a
+// rate of one per 8 cycles per SM sub-partition, far from limiting; a GPU-scope fence per row tile in the
+// column split doubled the kernel's time.  What limits the kernel now is the integer epilogue of every
+// block (unpack, recombine, convert, scale): the consumers wait for data less than a tenth of their time.
 // All waits are bounded (see vx_sm100.cuh).
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -46,12 +53,14 @@ using namespace sm100;
 constexpr int kVecs = 8;                 // vectors per pass (the MMA's n)
 constexpr int kUnitRows = 16;            // rows per tile (the MMA's m)
 constexpr int kGroup = 4;                // row tiles a warp walks with one set of B fragments
-constexpr int kWarps = 8;                // consumer warps
 constexpr int kRedSlots = 4;
 constexpr int kRedStride = 20;           // floats between vectors in a reduction slot (16 rows + padding)
 constexpr int kRedWarp = kVecs * kRedStride;
-constexpr int kMaxStages = 8;
 enum { SINGLE = 0, FULL = 1 };
+// Consumer warps per CTA.  (16 warps of 4 blocks each measured no faster than 8 warps of 8 in the FULL form:
+// 2.65 against 2.85 TB/s on 28672 x 4096 Q4_0.)
+__host__ __device__ constexpr int warps_of(int mode) { return 8; }
+constexpr int kMaxStages = 8;
 // bytes of planes per 32 columns: 3 (FULL) or 1 (SINGLE) x 256, then 8 x int32
 __host__ __device__ constexpr uint32_t block_planes(int mode) { return mode == FULL ? 800u : 288u; }
 
@@ -215,13 +224,14 @@ __device__ __forceinline__ void my_units(const MmaParams& p, uint32_t* u0, uint3
 }
 
 template <int QT, int NBW, int MODE>
-__global__ void __launch_bounds__(kWarps * 32 + 64, 1)
+__global__ void __launch_bounds__(warps_of(MODE) * 32 + 64, 1)
 gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUtensorMap map_q,
                 const __grid_constant__ CUtensorMap map_s) {
     constexpr int QB = QT == 1 ? 16 : 32;   // bytes of quants per block
+    constexpr int kWarps = warps_of(MODE);
     constexpr int NP = MODE == FULL ? 3 : 1;
     constexpr uint32_t kBP = block_planes(MODE);
-    constexpr bool S_SWZ = NBW == 8;        // the scales of a tile are 128 bytes per row: swizzled like the quants
+    constexpr bool S_SWZ = NBW * kWarps == 64;   // the scales of a tile are 128 bytes per row: swizzled like the quants
     extern __shared__ __align__(128) uint8_t smem_raw[];
     // the swizzle of the tiled copies works on shared-memory address bits: start the layout on a 1024-byte boundary
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
@@ -425,12 +435,13 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
                 if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 43);
                 const uint8_t* sq = ring + (size_t)s * p.stage_bytes;
                 const uint8_t* ss = sq + p.s_off;
-                // the NBW scales of rows g and g + 8 (rows of 16 NBW bytes; with NBW = 8 the 16-byte group of
-                // warp w sits at position w ^ row inside its row's 128 bytes)
+                // the NBW scales of rows g and g + 8 (rows of 2 NBW kWarps bytes; when that is 128, 16-byte group
+                // number n of a row sits at position n ^ row inside it)
                 __align__(16) __half dlo[NBW], dhi[NBW];
                 {
                     const uint32_t srow = kt_blocks * 2;
-                    const uint32_t at = S_SWZ ? ((warp ^ g) * 16) : warp * NBW * 2;
+                    const uint32_t o = warp * NBW * 2;
+                    const uint32_t at = S_SWZ ? ((((o >> 4) ^ g) << 4) | (o & 15u)) : o;
                     const uint8_t* a = ss + g * srow + at;
                     const uint8_t* b = a + 8 * srow;
                     if constexpr (NBW == 8) {
@@ -531,11 +542,13 @@ bool choose(const vx_qweights* w, uint32_t batch, MmaConfig* c) {
     const uint32_t qb = w->type == VX_Q4_0 ? 16 : 32;
     c->mode = batch <= 2 ? SINGLE : FULL;
     const uint32_t bp = block_planes(c->mode);
+    const uint32_t kWarps = (uint32_t)warps_of(c->mode);
+    const uint32_t nbw_max = 8;
     for (uint32_t cs = 1; cs <= 8; cs *= 2) {
         if (nb % (cs * kWarps) != 0) continue;
         const uint32_t kc_blocks = nb / cs;
         if ((size_t)kc_blocks * bp > 104 * 1024) continue;
-        uint32_t nbw = 8;
+        uint32_t nbw = nbw_max;
         while (nbw > 1 && kc_blocks % (nbw * kWarps) != 0) nbw >>= 1;
         const uint32_t kt_blocks = nbw * kWarps;
         c->cs = cs;
@@ -583,7 +596,7 @@ bool make_maps(const vx_qweights* w, const MmaConfig& c, CUtensorMap* map_q, CUt
     EncodeFn fn = encode_fn();
     if (!fn) return false;
     const uint32_t qb = w->type == VX_Q4_0 ? 16 : 32;
-    const uint32_t kt_blocks = c.nbw * kWarps;
+    const uint32_t kt_blocks = c.nbw * (uint32_t)warps_of(c.mode);
     const cuuint32_t ones[3] = {1, 1, 1};
     {
         const cuuint64_t dims[3] = {128, w->rows, w->quant_row_bytes / 128};
@@ -598,7 +611,7 @@ bool make_maps(const vx_qweights* w, const MmaConfig& c, CUtensorMap* map_q, CUt
         const cuuint64_t strides[1] = {w->blocks_per_row * 2};
         const cuuint32_t box[2] = {kt_blocks * 2, (cuuint32_t)kUnitRows};
         if (fn(map_s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->d_scales, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               c.nbw == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               kt_blocks == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return false;
     }
@@ -617,7 +630,7 @@ vx_status launch_main(vx_context* ctx, const MmaParams& p, const CUtensorMap& mq
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kWarps * 32 + 64);
+    cfg.blockDim = dim3(warps_of(MODE) * 32 + 64);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];

@@ -82,6 +82,11 @@ __device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void* src, uin
         : "memory");
 }
 
+// Asks for `bytes` (a multiple of 16, from a 16-byte aligned address) to be brought into L2; nothing waits for it.
+__device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 // --------------------------------------------------------- tiled TMA (tensor map) ----
 // x is the innermost coordinate; x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int32_t x, int32_t y, uint32_t bar) {
