@@ -325,6 +325,26 @@ VX_API vx_status vx_contiguous(vx_context* ctx, void* dest, uint64_t cap_dest, c
 VX_API vx_status vx_repeat(vx_context* ctx, float* result, const vx_shape* shape_result, uint64_t cap_result,
                            const float* source, const vx_shape* shape_source, uint64_t cap_source);
 
+/* -------------------------------------------------------- packed-weight files ---- */
+/* No reference counterpart beyond the GGML dimension convention vortx's layouts carry (GGML_IDS and
+ * permute_ggml, src/shapes.rs:15-18, :261-265).  Reads GGUF containers (versions 2 and 3, little-endian):
+ * the file is mapped, its tensor records are listed, and a Q4_0 / Q8_0 matrix (GGML types 2 / 8, whose
+ * blocks are byte for byte this library's host block stream) goes straight from the mapping into
+ * vx_qweights_upload.  A GGML tensor lists its innermost dimension first: ne[0] = columns, ne[1] = rows. */
+typedef struct vx_wfile vx_wfile;
+VX_API vx_status vx_wfile_open(const char* path, vx_wfile** out);
+VX_API vx_status vx_wfile_close(vx_wfile* f);
+VX_API vx_status vx_wfile_count(const vx_wfile* f, size_t* count);
+/* Record `index`: name (truncated to name_cap - 1 characters), GGML type number, dimensions (unused ones 1)
+ * and size in bytes (0 for a type this library cannot size).  Any output pointer may be NULL. */
+VX_API vx_status vx_wfile_tensor(const vx_wfile* f, size_t index, char* name, size_t name_cap, uint32_t* ggml_type,
+                                 uint32_t* n_dims, uint64_t ne[4], uint64_t* bytes);
+VX_API vx_status vx_wfile_find(const vx_wfile* f, const char* name, size_t* index);
+/* The tensor's bytes inside the mapping (valid until vx_wfile_close): F32 / F16 / Q4_0 / Q8_0. */
+VX_API vx_status vx_wfile_data(const vx_wfile* f, size_t index, const void** data, uint64_t* bytes);
+/* Uploads a Q4_0 / Q8_0 matrix as device weights (rows = ne[1], columns = ne[0]). */
+VX_API vx_status vx_wfile_load_qweights(vx_context* ctx, const vx_wfile* f, size_t index, vx_qweights** out);
+
 /* ------------------------------------------------------------------ checksum ---- */
 /* No reference counterpart.  One read-only pass over a device buffer (16-byte aligned, a whole number of
  * 16-byte groups): *device_out receives the XOR of all its 32-bit words, word j of each group rotated

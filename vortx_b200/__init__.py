@@ -8,6 +8,7 @@ from ._lib import (LayoutError, ShapeMismatch, VortxError, load, LIB_PATH)
 from .backend import Backend, BufferUsages, GpuBuffer, GpuBufferSlice, GpuEncoder, GpuPass
 from .shapes import GGML_IDS, TensorLayout, TensorLayoutBuffers
 from .tensor import Tensor, TensorBuilder, TensorMut, TensorRef
+from .weights_file import WeightFile, write_gguf
 from .linalg import (Contiguous, Gemm, Gemv, GemvBatch, MatrixMode, N, OpAssign, OpAssignVariant, Q4_0, Q8_0, QuantizedMatrix,
                      Reduce, ReduceVariant, Repeat, T, dequantize_host, quantize)
 
@@ -16,5 +17,5 @@ __all__ = [
     "GGML_IDS", "TensorLayout", "TensorLayoutBuffers", "Tensor", "TensorBuilder", "TensorMut",
     "TensorRef", "Gemm", "Gemv", "GemvBatch", "Reduce", "ReduceVariant", "OpAssign", "OpAssignVariant", "Contiguous", "Repeat",
     "MatrixMode", "N", "T", "Q4_0", "Q8_0", "QuantizedMatrix",
-    "quantize", "dequantize_host", "LayoutError", "ShapeMismatch", "VortxError", "load", "LIB_PATH",
+    "quantize", "dequantize_host", "WeightFile", "write_gguf", "LayoutError", "ShapeMismatch", "VortxError", "load", "LIB_PATH",
 ]

@@ -133,6 +133,14 @@ SIGNATURES = {
     "vx_contiguous": (C.c_int32, [_P, _P, C.c_uint64, _P, C.POINTER(VxShape), C.c_uint64, C.c_uint32]),
     "vx_repeat": (C.c_int32, [_P, _P, C.POINTER(VxShape), C.c_uint64, _P, C.POINTER(VxShape), C.c_uint64]),
     "vx_op_assign_dispatch": (C.c_int32, [_P, C.c_int, C.c_int32, _P, _LP, C.c_uint64, _P, _LP, C.c_uint64]),
+    "vx_wfile_open": (C.c_int32, [C.c_char_p, C.POINTER(_P)]),
+    "vx_wfile_close": (C.c_int32, [_P]),
+    "vx_wfile_count": (C.c_int32, [_P, C.POINTER(C.c_size_t)]),
+    "vx_wfile_tensor": (C.c_int32, [_P, C.c_size_t, C.c_char_p, C.c_size_t, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                    C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "vx_wfile_find": (C.c_int32, [_P, C.c_char_p, C.POINTER(C.c_size_t)]),
+    "vx_wfile_data": (C.c_int32, [_P, C.c_size_t, C.POINTER(_P), C.POINTER(C.c_uint64)]),
+    "vx_wfile_load_qweights": (C.c_int32, [_P, _P, C.c_size_t, C.POINTER(_P)]),
     "vx_checksum_u32": (C.c_int32, [_P, _P, C.c_size_t, _P]),
     "vx_qweights_checksum": (C.c_int32, [_P, _P, _P]),
     "vx_download_2d": (C.c_int32, [_P, _P, C.c_size_t, _P, C.c_size_t, C.c_size_t, C.c_size_t]),
