@@ -37,7 +37,8 @@ enum {
     VX_ERR_OUT_OF_MEMORY = 5,    /* cudaMalloc failed                                         */
     VX_ERR_UNSUPPORTED = 6,      /* the requested kernel cannot take these operands           */
     VX_ERR_DEVICE_TIMEOUT = 7,   /* a bounded device-side wait gave up; results are invalid   */
-    VX_ERR_NO_DEVICE = 8         /* no usable sm_100 device / driver                          */
+    VX_ERR_NO_DEVICE = 8,        /* no usable sm_100 device / driver                          */
+    VX_ERR_COLLECTIVE = 9        /* an NCCL call failed, or NCCL could not be loaded          */
 };
 
 /* Thread-local text of the last failure on this thread ("" if none). */
@@ -264,6 +265,42 @@ VX_API vx_status vx_gemm_tf32_scatter(vx_context* ctx, float* out, const float* 
  * that is rewritten later needs its own ordering against the readers (a second barrier or a
  * second buffer). */
 VX_API vx_status vx_peer_barrier(vx_context* ctx, uint32_t* const* flags, size_t world, size_t rank);
+
+/* ------------------------------------------------------- a group of GPUs of one node ---- */
+/* No reference counterpart.  One vx_group per context and rank (a process or thread per GPU): an NCCL
+ * communicator for the collective forms, plus what the fused forms need (buffers every rank can store into,
+ * mapped through CUDA IPC, and the arrival flags of vx_peer_barrier).  NCCL is loaded at run time
+ * (libnccl.so.2, or the path in the environment variable VX_NCCL_LIBRARY); without it these entry points
+ * return VX_ERR_COLLECTIVE for more than one rank.  Every rank makes the same calls in the same order.
+ *   rank 0: vx_group_unique_id -> its 128 bytes reach the other ranks by any means (a file, a socket)
+ *   all:    vx_group_create(ctx, world, rank, id) ... vx_group_destroy, with no work in flight. */
+typedef struct vx_group vx_group;
+VX_API vx_status vx_group_unique_id(void* id128);
+VX_API vx_status vx_group_create(vx_context* ctx, size_t world, size_t rank, const void* id128, vx_group** out);
+VX_API vx_status vx_group_destroy(vx_group* g);
+VX_API vx_status vx_group_info(const vx_group* g, size_t* world, size_t* rank);
+/* Collectives, stream-ordered on the context's stream.  all_gather: recv holds world x bytes_per_rank; send
+ * NULL = in place (this rank's part already sits at recv + rank * bytes_per_rank). */
+VX_API vx_status vx_group_all_gather(vx_group* g, const void* send, void* recv, size_t bytes_per_rank);
+VX_API vx_status vx_group_broadcast(vx_group* g, void* buffer, size_t bytes, size_t root);
+/* vx_peer_barrier over the group's own flags: after it, on this rank's stream, every rank's earlier peer stores
+ * have landed here. */
+VX_API vx_status vx_group_barrier(vx_group* g);
+/* A zeroed buffer of `bytes` on every rank, each mapped into all the others: ptrs[r] (world entries) is the
+ * pointer through which THIS process reaches rank r's buffer (ptrs[rank] its own).  Peer pointers are for
+ * stores from this library's kernels only.  Collective; blocks until done. */
+VX_API vx_status vx_group_peer_alloc(vx_group* g, size_t bytes, void** ptrs);
+VX_API vx_status vx_group_peer_free(vx_group* g, void* const* ptrs);
+/* Row-sharded GEMV: `slab` holds this rank's rows [row0, row0 + slab rows) of W; every finished row is stored at
+ * float index row0 + r of the y of EVERY rank (y_all from vx_group_peer_alloc, y_offset bytes into each), then
+ * the group's barrier.  After it, stream-ordered, the whole y is on this GPU.  x is replicated. */
+VX_API vx_status vx_group_gemv_q(vx_group* g, const vx_qweights* slab, size_t row0, const float* x,
+                                 void* const* y_all, size_t y_offset);
+/* Column-sharded GEMM: C[m, n] = A[m, k] B[k, n], this rank computing columns [col0, col0 + ncols) from its
+ * panel of B (rows rhs_stride floats apart) on the tensor cores, its epilogue storing every tile into the C of
+ * every rank (c_all from vx_group_peer_alloc, row-major m x n), then the group's barrier.  A is replicated. */
+VX_API vx_status vx_group_gemm_tf32(vx_group* g, const float* lhs, const float* rhs_panel, size_t m, size_t n,
+                                    size_t k, size_t col0, size_t ncols, size_t rhs_stride, void* const* c_all);
 
 /* --------------------------------------------------------------- reductions ---- */
 /* Reduce::launch(backend, shapes, pass, variant, input, output) — src/linalg/reduce.rs:79-207 —

@@ -20,6 +20,7 @@ VX_ERR_OUT_OF_MEMORY = 5
 VX_ERR_UNSUPPORTED = 6
 VX_ERR_DEVICE_TIMEOUT = 7
 VX_ERR_NO_DEVICE = 8
+VX_ERR_COLLECTIVE = 9
 
 VX_GEMM_AUTO, VX_GEMM_NAIVE, VX_GEMM_SIMT_EXACT, VX_GEMM_TF32 = 0, 1, 2, 3
 VX_DISPATCH, VX_DISPATCH_NAIVE, VX_DISPATCH_TILED, VX_DISPATCH_TF32 = 0, 1, 2, 3
@@ -126,6 +127,18 @@ SIGNATURES = {
     "vx_gemv_batch_free": (C.c_int32, [_P, _P]),
     "vx_gemm_tf32_scatter": (C.c_int32, [_P, _P, _P, _P, C.POINTER(VxShapes3), C.POINTER(_P), C.c_size_t]),
     "vx_peer_barrier": (C.c_int32, [_P, C.POINTER(_P), C.c_size_t, C.c_size_t]),
+    "vx_group_unique_id": (C.c_int32, [_P]),
+    "vx_group_create": (C.c_int32, [_P, C.c_size_t, C.c_size_t, _P, C.POINTER(_P)]),
+    "vx_group_destroy": (C.c_int32, [_P]),
+    "vx_group_info": (C.c_int32, [_P, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "vx_group_all_gather": (C.c_int32, [_P, _P, _P, C.c_size_t]),
+    "vx_group_broadcast": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t]),
+    "vx_group_barrier": (C.c_int32, [_P]),
+    "vx_group_peer_alloc": (C.c_int32, [_P, C.c_size_t, C.POINTER(_P)]),
+    "vx_group_peer_free": (C.c_int32, [_P, C.POINTER(_P)]),
+    "vx_group_gemv_q": (C.c_int32, [_P, _P, C.c_size_t, _P, C.POINTER(_P), C.c_size_t]),
+    "vx_group_gemm_tf32": (C.c_int32, [_P, _P, _P, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
+                                       C.c_size_t, C.POINTER(_P)]),
     "vx_reduce": (C.c_int32, [_P, C.c_int, C.c_int, C.c_int, _P, C.POINTER(VxShape), C.c_uint64, _P]),
     "vx_reduce_static": (C.c_int32, [C.c_int32, _P, C.c_int, C.c_int, _P, C.POINTER(VxShape), _P]),
     "vx_op_assign": (C.c_int32, [_P, C.c_int, _P, C.POINTER(VxShape), C.c_uint64, _P, C.POINTER(VxShape), C.c_uint64,

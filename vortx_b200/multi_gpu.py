@@ -412,3 +412,79 @@ class ShardedGemv:
         for r, part in enumerate(parts):
             r0, n = row_shard(self.rows, self.world, r)
             y_full[:, r0:r0 + n] = part[:, :n]
+
+
+class Group:
+    """vx_group of the C ABI: an NCCL communicator plus IPC-mapped peer buffers, with no torch on the path.
+
+    `Group.from_torch(backend)` only uses torch.distributed to carry rank 0's 128-byte unique id to the other
+    ranks; a host without torch passes the bytes by any other means and calls `Group(backend, world, rank, id)`."""
+
+    def __init__(self, backend, world: int, rank: int, unique_id: Optional[bytes]):
+        import ctypes as C
+        from . import _lib
+        h = C.c_void_p()
+        buf = (C.c_ubyte * 128).from_buffer_copy(unique_id) if unique_id else None
+        _lib.check(_lib.load().vx_group_create(backend._ctx, world, rank, buf, C.byref(h)))
+        self.backend, self.world, self.rank, self._h = backend, world, rank, h
+
+    @staticmethod
+    def unique_id() -> bytes:
+        import ctypes as C
+        from . import _lib
+        buf = (C.c_ubyte * 128)()
+        _lib.check(_lib.load().vx_group_unique_id(buf))
+        return bytes(buf)
+
+    @classmethod
+    def from_torch(cls, backend) -> "Group":
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(), dist.get_rank()
+        box = [cls.unique_id() if rank == 0 and world > 1 else None]
+        if world > 1:
+            dist.broadcast_object_list(box, src=0)
+        return cls(backend, world, rank, box[0])
+
+    def peer_alloc(self, nbytes: int) -> List[int]:
+        import ctypes as C
+        from . import _lib
+        ptrs = (C.c_void_p * self.world)()
+        _lib.check(_lib.load().vx_group_peer_alloc(self._h, nbytes, ptrs))
+        return [int(p or 0) for p in ptrs]
+
+    def peer_free(self, ptrs: List[int]) -> None:
+        import ctypes as C
+        from . import _lib
+        _lib.check(_lib.load().vx_group_peer_free(self._h, (C.c_void_p * self.world)(*ptrs)))
+
+    def all_gather(self, recv_ptr: int, bytes_per_rank: int, send_ptr: int = 0) -> None:
+        from . import _lib
+        _lib.check(_lib.load().vx_group_all_gather(self._h, send_ptr or None, recv_ptr, bytes_per_rank))
+
+    def broadcast(self, ptr: int, nbytes: int, root: int) -> None:
+        from . import _lib
+        _lib.check(_lib.load().vx_group_broadcast(self._h, ptr, nbytes, root))
+
+    def barrier(self) -> None:
+        from . import _lib
+        _lib.check(_lib.load().vx_group_barrier(self._h))
+
+    def gemv_q(self, slab, row0: int, x_ptr: int, y_all: List[int], y_offset: int = 0) -> None:
+        """Row-sharded GEMV: `slab` is this rank's QuantizedMatrix; the whole y lands on every GPU."""
+        import ctypes as C
+        from . import _lib
+        _lib.check(_lib.load().vx_group_gemv_q(self._h, slab._h, row0, x_ptr, (C.c_void_p * self.world)(*y_all), y_offset))
+
+    def gemm_tf32(self, a_ptr: int, b_panel_ptr: int, m: int, n: int, k: int, col0: int, ncols: int, b_stride: int,
+                  c_all: List[int]) -> None:
+        import ctypes as C
+        from . import _lib
+        _lib.check(_lib.load().vx_group_gemm_tf32(self._h, a_ptr, b_panel_ptr, m, n, k, col0, ncols, b_stride,
+                                                   (C.c_void_p * self.world)(*c_all)))
+
+    def close(self) -> None:
+        from . import _lib
+        if self._h:
+            self.backend.synchronize()
+            _lib.load().vx_group_destroy(self._h)
+        self._h = None
