@@ -81,6 +81,35 @@ def _worker(rank, world, port, out_dir):
             sg.dispatch(xt, yt)
             stream.synchronize()
         results[f"{name}_nccl"] = yt.cpu().numpy()
+    # the same sharded product through the C ABI's own group (vx_group_*: NCCL communicator + IPC peer buffers made
+    # by the library itself; torch only carries the 128-byte id), and the list form on group-allocated buffers
+    from vortx_b200.multi_gpu import Group
+    grp = Group.from_torch(be)
+    w = synth.normal_matrix(rows, cols, seed=21)
+    blocks = vb.quantize(vb.Q4_0, w)
+    mine = shard_blocks(blocks, rows, cols, 18, world, rank)
+    g2 = PeerScatterGemv(be, rows, cols, slots, vectors=0, vx_group=grp)
+    qm = vb.QuantizedMatrix(be, vb.Q4_0, mine, g2.nrows, cols)
+    xs = synth.normal_vectors(slots, cols, seed=22)
+    xd = be.init_buffer(xs.ravel())
+    for rep in range(2):
+        for s in range(slots):
+            grp.gemv_q(qm, g2.row0, xd.ptr + s * cols * 4, g2.y.ptrs, s * rows * 4)
+    be.synchronize()
+    y = np.empty(slots * rows, np.float32)
+    be.slow_read_buffer(g2.y.local, y.view(np.uint8))
+    results["q4_group"] = y.reshape(slots, rows)
+    gathered = be.init_buffer(np.zeros(world * 16, np.float32))
+    be.write_buffer(gathered, rank * 16, np.full(16, float(rank + 1), np.float32))
+    grp.all_gather(gathered.ptr, 64)
+    ag = np.empty(world * 16, np.float32)
+    be.slow_read_buffer(gathered, ag)
+    results["group_all_gather"] = ag
+    grp.barrier()
+    be.synchronize()
+    dist.barrier()
+    g2.close()
+    grp.close()
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **results)
     dist.barrier()
     be.close()
@@ -275,6 +304,9 @@ def test_peer_scatter_and_nccl_gemv(tmp_path, oracle, world):
             assert (np.abs(peer - y64) <= 2e-6 * absdot).all()
             assert np.array_equal(nccl[0].view(np.uint32), peer[0].view(np.uint32))   # same kernel, same rows
             assert np.array_equal(got[f"{name}_peer_list"].view(np.uint32), peer.view(np.uint32))
+            if name == "q4":
+                assert np.array_equal(got["q4_group"].view(np.uint32), peer.view(np.uint32))       # vx_group_gemv_q
+                assert np.array_equal(got["group_all_gather"], np.repeat(np.arange(1, world + 1, dtype=np.float32), 16))
 
 
 def _gemm_worker(rank, world, port, out_dir):

@@ -12,6 +12,8 @@ from typing import Callable, List, Optional, Tuple
 
 import numpy as np
 
+from .backend import GpuBuffer
+
 
 def row_shard(rows: int, world: int, rank: int) -> Tuple[int, int]:
     """Contiguous balanced slabs: the first rows % world ranks take one extra row."""
@@ -113,11 +115,18 @@ class PeerBuffers:
     this process reaches rank r's buffer (its own pointer for r == rank).  Handles travel through the
     process group (all_gather_object); the mapping is peer-store only by convention of its users."""
 
-    def __init__(self, backend, nbytes: int, group=None):
+    def __init__(self, backend, nbytes: int, group=None, vx_group: Optional["Group"] = None):
         import ctypes as C
-        import torch.distributed as dist
         from . import _lib
-        self.backend, self.group = backend, group
+        self.backend, self.group, self.vx_group = backend, group, vx_group
+        if vx_group is not None:
+            # the C ABI's own group: allocation, handle exchange (over NCCL) and mapping in one call, no torch
+            self.world, self.rank = vx_group.world, vx_group.rank
+            self.ptrs = vx_group.peer_alloc(nbytes)
+            self.local = GpuBuffer(backend, self.ptrs[self.rank], nbytes, np.uint8, owned=False)
+            self._mapped = []
+            return
+        import torch.distributed as dist
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         lib = _lib.load()
@@ -142,6 +151,11 @@ class PeerBuffers:
 
     def close(self) -> None:
         from . import _lib
+        if self.vx_group is not None:
+            if self.ptrs:
+                self.vx_group.peer_free(self.ptrs)
+            self.ptrs = []
+            return
         lib = _lib.load()
         for p in self._mapped:
             lib.vx_ipc_release(self.backend._ctx, p)
@@ -162,13 +176,17 @@ class PeerScatterGemv:
     `cyclic=True` deals the rows out in turn (rank r owns rows r, r + world, ...; its slab is still one
     contiguous block stream) instead of contiguous slabs; only the chained form supports it."""
 
-    def __init__(self, backend, rows: int, cols: int, slots: int, group=None, vectors: int = 2, cyclic: bool = False):
+    def __init__(self, backend, rows: int, cols: int, slots: int, group=None, vectors: int = 2, cyclic: bool = False,
+                 vx_group: Optional["Group"] = None):
         import ctypes as C
-        import torch.distributed as dist
         from . import _lib
         self.backend, self.rows, self.cols, self.slots = backend, rows, cols, slots
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        if vx_group is not None:
+            self.world, self.rank = vx_group.world, vx_group.rank
+        else:
+            import torch.distributed as dist
+            self.world = dist.get_world_size(group)
+            self.rank = dist.get_rank(group)
         if self.world > 8:
             raise ValueError("at most 8 GPUs of one node")
         self.cyclic = cyclic
@@ -176,14 +194,15 @@ class PeerScatterGemv:
             self.row0, self.nrows = self.rank, len(range(self.rank, rows, self.world))
         else:
             self.row0, self.nrows = row_shard(rows, self.world, self.rank)
-        self.y = PeerBuffers(backend, max(1, slots) * rows * 4, group)
-        self.flags = PeerBuffers(backend, 64 * 4, group)
-        self.vectors = [PeerBuffers(backend, _lib.load().vx_xvec_bytes(rows), group) for _ in range(vectors)]
+        self.y = PeerBuffers(backend, max(1, slots) * rows * 4, group, vx_group)
+        self.flags = PeerBuffers(backend, 64 * 4, group, vx_group)
+        self.vectors = [PeerBuffers(backend, _lib.load().vx_xvec_bytes(rows), group, vx_group) for _ in range(vectors)]
         self._others = [r for r in range(self.world) if r != self.rank]
         self._flags_all = (C.c_void_p * self.world)(*self.flags.ptrs)
         self._vec_peers = [(C.c_void_p * max(1, len(self._others)))(*[v.ptrs[r] for r in self._others])
                            for v in self.vectors]
-        dist.barrier(group=group)
+        if vx_group is None:
+            dist.barrier(group=group)
 
     def y_ptr(self, slot: int) -> int:
         return self.y.local.ptr + slot * self.rows * 4
