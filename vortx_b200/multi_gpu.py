@@ -338,8 +338,9 @@ class ShardedGemm:
         import ctypes as C
         from . import _lib
         sh = self._shapes(self.n, b_stride)
-        _lib.check(_lib.load().vx_gemm_tf32_scatter(self.backend._ctx, self.c.local.ptr + self.col0 * 4, a_ptr,
-                                                    b_panel_ptr, C.byref(sh), self._peer_c, len(self._others)))
+        if self.ncols:      # with fewer 32-column blocks than ranks, a rank may own no columns: it only takes part in the barrier
+            _lib.check(_lib.load().vx_gemm_tf32_scatter(self.backend._ctx, self.c.local.ptr + self.col0 * 4, a_ptr,
+                                                        b_panel_ptr, C.byref(sh), self._peer_c, len(self._others)))
         _lib.check(_lib.load().vx_peer_barrier(self.backend._ctx, self._flags_all, self.world, self.rank))
 
     def dispatch_nccl(self, a_ptr: int, b_panel_ptr: int, b_stride: int) -> None:
