@@ -30,6 +30,9 @@
 // 4 KB) of 4-row k groups (stride offset 512 B).
 #include <cuda.h>
 
+#include <atomic>
+#include <mutex>
+
 #include <algorithm>
 #include <cstring>
 
@@ -307,17 +310,17 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeFn encode_fn() {
+    // contexts of different devices may call from different threads: looked up once, under a lock
+    static std::once_flag once;
     static EncodeFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    std::call_once(once, [] {
         void* sym = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
             fn = reinterpret_cast<EncodeFn>(sym);
         (void)cudaGetLastError();
-    }
+    });
     return fn;
 }
 
@@ -347,10 +350,10 @@ vx_status launch_tiles(vx_context* ctx, const CUtensorMap& map_a, const CUtensor
     using C = Cfg<HALVES>;
     const size_t smem = (size_t)C::kStages * C::kStageBytes + 1024 + kXposeBytes + 1024;
     static_assert(sizeof(SharedTail) <= 1024, "barriers sit in the first KB after the ring, the staging boxes after it");
-    static bool attr_set[64] = {};
-    if (!attr_set[ctx->device & 63]) {
+    static std::atomic<bool> attr_set[64];
+    if (!attr_set[ctx->device & 63].load(std::memory_order_acquire)) {
         VX_CUDA(cudaFuncSetAttribute(gemm_tf32_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[ctx->device & 63] = true;
+        attr_set[ctx->device & 63].store(true, std::memory_order_release);
     }
     p.tiles_m = (p.m + C::BM - 1) / C::BM;
     p.tiles_n = (p.n + BN - 1) / BN;
