@@ -102,16 +102,21 @@ gemm_tiled_generic_kernel(float* __restrict__ out, const float* __restrict__ lhs
 }
 
 // ------------------------------------------------------------ vector path -----
-// Row-major operands (unit stride along w, rows and bases 16-byte aligned): 128x128 output
-// tile, K stepped by 8, 8x8 outputs per thread held as two 4-wide halves so that every
-// shared-memory read is a conflict-free 128-bit load.  Global tiles for step t+1 are
-// fetched into registers while step t is multiplied (one barrier per step).
-constexpr int V_BM = 128, V_BN = 128, V_BK = 8;
-constexpr int V_AS = V_BM + 4;  // padded row of the transposed A tile
+// Row-major operands (unit stride along w, rows and bases 16-byte aligned): BM x 128 output
+// tile (BM = 128, or 64 when 128-row tiles would leave SMs without work), K stepped by 8,
+// (BM / 16) x 8 outputs per thread held as 4-wide pieces so that every shared-memory read is a
+// conflict-free 128-bit load.  Global tiles for step t+1 are fetched into registers while step t is
+// multiplied (one barrier per step).  Every output element is still accumulated k ascending,
+// multiply then add: the tile shape does not change a bit of the result.
+constexpr int V_BN = 128, V_BK = 8;
 
+template <int V_BM>
 __global__ void __launch_bounds__(256, 2)
 gemm_tiled_vec_kernel(float* __restrict__ out, const float* __restrict__ lhs,
                       const float* __restrict__ rhs, const vx_shapes3 s) {
+    constexpr int V_AS = V_BM + 4;       // padded row of the transposed A tile
+    constexpr int RH = V_BM / 64;        // 4-row pieces per thread: rows ty*4.. and (RH = 2) 64 + ty*4..
+    constexpr int RT = 4 * RH;           // rows per thread
     __shared__ __align__(16) float sa[2][V_BK][V_AS];
     __shared__ __align__(16) float sb[2][V_BK][V_BN];
 
@@ -127,14 +132,16 @@ gemm_tiled_vec_kernel(float* __restrict__ out, const float* __restrict__ lhs,
     float* __restrict__ C = out + (size_t)n * s.out.n_stride + (size_t)c * s.out.c_stride;
     const size_t lda = s.lhs.h_stride, ldb = s.rhs.h_stride, ldc = s.out.h_stride;
 
-    // Loader roles: A tile 128 rows x 8 k = 256 float4 (one per thread); B tile 8 k x 128 = 256 float4.
+    // Loader roles: A tile BM rows x 8 k = 2 BM float4 (threads below 2 BM take one each); B tile 8 k x 128 =
+    // 256 float4 (one per thread).
+    const bool a_loader = tid < 2 * V_BM;
     const uint32_t a_row = tid / 2, a_k = (tid % 2) * 4;
     const uint32_t b_k = tid / 32, b_col = (tid % 32) * 4;
 
     auto load_a = [&](uint32_t k0) -> float4 {
         const uint32_t gr = tile_row + a_row, gk = k0 + a_k;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (gr < m) {
+        if (a_loader && gr < m) {
             const float* p = A + (size_t)gr * lda + gk;
             if (gk + 3 < k) {
                 v = *reinterpret_cast<const float4*>(p);
@@ -162,16 +169,18 @@ gemm_tiled_vec_kernel(float* __restrict__ out, const float* __restrict__ lhs,
         return v;
     };
     auto store_tiles = [&](int buf, const float4& va, const float4& vb) {
-        sa[buf][a_k + 0][a_row] = va.x;
-        sa[buf][a_k + 1][a_row] = va.y;
-        sa[buf][a_k + 2][a_row] = va.z;
-        sa[buf][a_k + 3][a_row] = va.w;
+        if (a_loader) {
+            sa[buf][a_k + 0][a_row] = va.x;
+            sa[buf][a_k + 1][a_row] = va.y;
+            sa[buf][a_k + 2][a_row] = va.z;
+            sa[buf][a_k + 3][a_row] = va.w;
+        }
         *reinterpret_cast<float4*>(&sb[buf][b_k][b_col]) = vb;
     };
 
-    float acc[8][8];
+    float acc[RT][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < RT; ++i)
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
 
@@ -188,14 +197,17 @@ gemm_tiled_vec_kernel(float* __restrict__ out, const float* __restrict__ lhs,
         }
 #pragma unroll
         for (int kk = 0; kk < V_BK; ++kk) {
-            const float4 a0 = *reinterpret_cast<const float4*>(&sa[buf][kk][ty * 4]);
-            const float4 a1 = *reinterpret_cast<const float4*>(&sa[buf][kk][64 + ty * 4]);
+            float a[RT];
+#pragma unroll
+            for (int h = 0; h < RH; ++h) {
+                const float4 av = *reinterpret_cast<const float4*>(&sa[buf][kk][h * 64 + ty * 4]);
+                a[4 * h + 0] = av.x; a[4 * h + 1] = av.y; a[4 * h + 2] = av.z; a[4 * h + 3] = av.w;
+            }
             const float4 b0 = *reinterpret_cast<const float4*>(&sb[buf][kk][tx * 4]);
             const float4 b1 = *reinterpret_cast<const float4*>(&sb[buf][kk][64 + tx * 4]);
-            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < RT; ++i)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], b[j]));
         }
@@ -207,8 +219,8 @@ gemm_tiled_vec_kernel(float* __restrict__ out, const float* __restrict__ lhs,
     }
 
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t r = tile_row + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    for (int i = 0; i < RT; ++i) {
+        const uint32_t r = tile_row + (i / 4) * 64 + ty * 4 + (i % 4);
         if (r >= m) continue;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -267,9 +279,13 @@ vx_status launch_gemm_simt_exact(vx_context* ctx, float* out, const float* lhs, 
     const bool vec = option(ctx, "gemm.simt.force_generic", 0) == 0 && vector_friendly(out, s.out) &&
                      vector_friendly(lhs, s.lhs) && vector_friendly(rhs, s.rhs);
     if (vec) {
-        dim3 grid((s.out.w + V_BN - 1) / V_BN, (s.out.h + V_BM - 1) / V_BM, (unsigned)batches);
+        // 128-row tiles unless they would leave SMs idle (1024^3: 64 tiles for 148 SMs): then 64-row tiles
+        const uint64_t tiles128 = (uint64_t)((s.out.w + V_BN - 1) / V_BN) * ((s.out.h + 127) / 128) * batches;
+        const int bm = tiles128 >= 2ull * (uint64_t)ctx->sm_count ? 128 : 64;
+        dim3 grid((s.out.w + V_BN - 1) / V_BN, (s.out.h + bm - 1) / bm, (unsigned)batches);
         VX_REQUIRE(grid.y <= 65535, VX_ERR_UNSUPPORTED, "too many rows (%u)", s.out.h);
-        gemm_tiled_vec_kernel<<<grid, 256, 0, ctx->stream>>>(out, lhs, rhs, s);
+        if (bm == 128) gemm_tiled_vec_kernel<128><<<grid, 256, 0, ctx->stream>>>(out, lhs, rhs, s);
+        else gemm_tiled_vec_kernel<64><<<grid, 256, 0, ctx->stream>>>(out, lhs, rhs, s);
         if (kernel) *kernel = 2;
     } else {
         dim3 grid((s.out.w + G_TN - 1) / G_TN, (s.out.h + G_TM - 1) / G_TM, (unsigned)batches);
