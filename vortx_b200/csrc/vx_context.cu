@@ -43,6 +43,8 @@ static const char* const kKnownOptions[] = {
     "gemv.block_threads", // CTA size of the GEMV kernels
     "gemv.ctas_per_sm",   // persistent grid = SMs x this
     "gemv.batch_mma",     // batches of vectors on the tensor cores: -1 (default) for 2 and more vectors, 0 never, 1 also for one vector
+    "gemv.mma_nbw",       // tensor-core batch GEMV: most 32-column blocks per warp and column tile (8, 4, 2 or 1; default 8)
+    "gemv.mma_max_stages",  // tensor-core batch GEMV: cap on the depth of the weight ring (default 8)
     "gemv.block_wait",    // flagged x in a list: 1 one warp waits for the block, 0 every thread for its own chunk, -1 (default) by tiles per block
     "gemm.simt.force_generic",  // 1: always take the generic-stride SIMT kernel
     "gemm.tf32.stages",   // TMA pipeline depth
@@ -139,8 +141,6 @@ vx_status vx_context_destroy(vx_context* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->reduce_scratch) cudaFree(ctx->reduce_scratch);
     if (ctx->mma_planes) cudaFree(ctx->mma_planes);
-    if (ctx->mma_partial) cudaFree(ctx->mma_partial);
-    if (ctx->mma_counters) cudaFree(ctx->mma_counters);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     (void)cudaGetLastError();

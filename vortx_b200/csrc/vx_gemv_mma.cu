@@ -23,18 +23,20 @@
 //     sum still fits 32 bits.  The slice sums are scaled by the slice's factor in f32.
 //   * The main kernel is persistent, one CTA per SM: producer thread (one tiled TMA load per 16-row tile,
 //     128-byte swizzle so that fragment loads hit 32 different banks), 8 consumer warps, epilogue warp.
-//     The columns are split over CS CTAs so that a CTA's share of the planes (25 bytes per column, 9 in the
-//     SINGLE form) stays resident in its shared memory; the 8 warps of a CTA split a tile's columns further
-//     and keep their B fragments in registers while they walk up to 4 row tiles.
-//   * Partial sums meet in shared memory (the 8 warps of a CTA, fixed order) and, when the columns are
-//     split over several CTAs, in scratch memory: the CTAs of a row tile run side by side; all but the
-//     first store their part as {value, launch serial} pairs, the first adds them in a fixed order and
-//     writes y.
+//     A CTA owns whole rows.  The planes (25 bytes per column, 9 in the SINGLE form) must sit in its shared
+//     memory, so wide matrices are walked in PHASES: the planes of one column part are loaded, the part is
+//     streamed for all the CTA's row tiles (at most `sg_units` of them at a time), their sums wait in shared
+//     memory, the next part's planes replace the first's, and so on; the last phase writes y.  No sums
+//     cross CTAs.  The 8 warps of a CTA split a tile's columns further and keep their B fragments in
+//     registers while they walk up to 4 row tiles.
+//   * Partial sums meet in shared memory: the 8 warps of a CTA and the phases, both in a fixed order.
 // Measured on B200 while building this (they shaped the design): an SM completes about one untiled bulk
 // copy per 75 cycles whatever its size, and one thread issues one per 450, so row-by-row copies of 1 KB
 // top out near 3 TB/s (hence one tiled load per tile); mma.sync m16n8k32 s8 has 20 cycles latency and a
-// rate of one per 8 cycles per SM sub-partition, far from limiting; a GPU-scope fence per row tile in the
-// column split doubled the kernel's time.  What limits the kernel now is the integer epilogue of every
+// rate of one per 8 cycles per SM sub-partition, far from limiting; splitting the columns over CTAs that
+// exchange sums through global memory cost a GPU-scope fence per row tile (it doubled the kernel's time) or,
+// with tagged 64-bit pairs instead of fences, CTAs that wait for each other and must start together (no
+// early start under the launch before).  What limits the kernel now is the integer epilogue of every
 // block (unpack, recombine, convert, scale): the consumers wait for data less than a tenth of their time.
 // All waits are bounded (see vx_sm100.cuh).
 #include <cuda.h>
@@ -52,14 +54,13 @@ using namespace sm100;
 
 constexpr int kVecs = 8;                 // vectors per pass (the MMA's n)
 constexpr int kUnitRows = 16;            // rows per tile (the MMA's m)
-constexpr int kGroup = 4;                // row tiles a warp walks with one set of B fragments
-constexpr int kRedSlots = 4;
+constexpr int kMaxRedSlots = 8;          // hand-off slots between the consumer warps and the epilogue warp
 constexpr int kRedStride = 20;           // floats between vectors in a reduction slot (16 rows + padding)
 constexpr int kRedWarp = kVecs * kRedStride;
 enum { SINGLE = 0, FULL = 1 };
 // Consumer warps per CTA.  (16 warps of 4 blocks each measured no faster than 8 warps of 8 in the FULL form:
 // 2.65 against 2.85 TB/s on 28672 x 4096 Q4_0.)
-__host__ __device__ constexpr int warps_of(int mode) { return 8; }
+constexpr int kWarps = 8;
 constexpr int kMaxStages = 8;
 // bytes of planes per 32 columns: 3 (FULL) or 1 (SINGLE) x 256, then 8 x int32
 __host__ __device__ constexpr uint32_t block_planes(int mode) { return mode == FULL ? 800u : 288u; }
@@ -71,18 +72,16 @@ struct MmaParams {
     uint32_t nb;                  // blocks per row
     uint64_t row0;
     uint32_t nrows;
-    uint32_t cs;                  // column parts
-    uint32_t kc_blocks;           // blocks per part
-    uint32_t nkt;                 // column tiles per part
-    uint32_t stages, stage_bytes, s_off;
+    uint32_t phases;              // column tiles of 32 NBW kWarps columns, walked one after the other
+    uint32_t slot_bytes;          // shared memory per slot of planes (a column tile's planes, then its slice factors)
+    uint32_t sg_units;            // row tiles whose sums wait in shared memory between phases
+    uint32_t stages, red_slots, stage_bytes, s_off;
     uint32_t ring_off;            // offset of the ring in shared memory (1024-byte aligned: the swizzle works on address bits)
     const uint8_t* planes;        // [nb][block_planes(MODE)]
     const float* sx;              // [slices][kVecs]: per column, the factor its slice sums are scaled by
     float* y;
     uint64_t y_stride;
     uint32_t batch;
-    uint64_t* partial;            // [cs - 1][kVecs][nrows16] pairs {f32 sum, u32 launch serial}
-    const uint32_t* serial;       // number of pre-pass kernels run so far on this context
     uint32_t nrows16;             // rows rounded up to whole tiles
     vx::DeviceStatus* status;
 };
@@ -115,15 +114,12 @@ __device__ __forceinline__ void mma_i8(int (&d)[4], const uint32_t (&a)[4], uint
 // and words 4..7 the second one (the MMA's k = 4 t + i and 16 + 4 t + i).
 template <int QT, int MODE>
 __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ x, uint64_t x_stride, uint32_t batch,
-                                                      uint32_t nbw, uint8_t* __restrict__ planes, float* __restrict__ sx,
-                                                      uint32_t* serial) {
+                                                      uint32_t nbw, uint8_t* __restrict__ planes, float* __restrict__ sx) {
     // Programmatic dependent launch on both sides: the main kernel may become resident and start streaming
     // weights while this one runs (it reads the planes only after this grid has completed), and this grid
     // may start under the tail of the kernel before it, whose output x may be and whose planes these are.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // one thread of the grid counts the launch: the main kernel tags its exchanged partial sums with the count
-    if (blockIdx.x == 0 && threadIdx.x == 0) *serial = *serial + 1;
     constexpr float kXMax = QT == 1 ? 4194302.0f : 524286.0f;
     constexpr uint32_t kBP = block_planes(MODE);
     const uint32_t slice = blockIdx.x, col = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -215,40 +211,41 @@ __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ 
 }
 
 // ------------------------------------------------------------------------ main kernel ----
-// Work of CTA c: column part c % cs; row tiles [u0, u1) of pair c / cs, in groups of kGroup.
+// Work of a CTA: row tiles [u0, u1), walked `sg_units` at a time; per such set every phase (column tile),
+// and inside a phase the set's row tiles.  Producer, consumers and epilogue walk the same order.
 __device__ __forceinline__ void my_units(const MmaParams& p, uint32_t* u0, uint32_t* u1) {
-    const uint32_t pairs = gridDim.x / p.cs, pair = blockIdx.x / p.cs;
     const uint32_t units = p.nrows16 / kUnitRows;
-    *u0 = (uint32_t)((uint64_t)units * pair / pairs);
-    *u1 = (uint32_t)((uint64_t)units * (pair + 1) / pairs);
+    *u0 = (uint32_t)((uint64_t)units * blockIdx.x / gridDim.x);
+    *u1 = (uint32_t)((uint64_t)units * (blockIdx.x + 1) / gridDim.x);
 }
 
 template <int QT, int NBW, int MODE>
-__global__ void __launch_bounds__(warps_of(MODE) * 32 + 64, 1)
+__global__ void __launch_bounds__(kWarps * 32 + 64, 1)
 gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUtensorMap map_q,
                 const __grid_constant__ CUtensorMap map_s) {
     constexpr int QB = QT == 1 ? 16 : 32;   // bytes of quants per block
-    constexpr int kWarps = warps_of(MODE);
     constexpr int NP = MODE == FULL ? 3 : 1;
     constexpr uint32_t kBP = block_planes(MODE);
-    constexpr bool S_SWZ = NBW * kWarps == 64;   // the scales of a tile are 128 bytes per row: swizzled like the quants
+    constexpr uint32_t kt_blocks = NBW * kWarps;             // blocks per column tile
+    constexpr uint32_t q_tile_bytes = kt_blocks * QB;        // quants per row and tile
+    constexpr uint32_t plane_bytes = kt_blocks * kBP;        // planes of a column tile
+    constexpr uint32_t sx_bytes = kWarps * kVecs * 4;        // [kWarps][kVecs] slice factors of a column tile
+    constexpr bool S_SWZ = kt_blocks == 64;   // the scales of a tile are 128 bytes per row: swizzled like the quants
     extern __shared__ __align__(128) uint8_t smem_raw[];
     // the swizzle of the tiled copies works on shared-memory address bits: start the layout on a 1024-byte boundary
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-    const uint32_t plane_bytes = p.kc_blocks * kBP;
-    uint8_t* s_planes = smem;
-    float* s_sx = reinterpret_cast<float*>(smem + plane_bytes);                       // [nkt * kWarps][kVecs]
+    // [2 slots of planes + slice factors][ring][reduction slots][sums between phases][barriers]
     uint8_t* ring = smem + p.ring_off;
-    float* red = reinterpret_cast<float*>(ring + (size_t)p.stages * p.stage_bytes);   // [kRedSlots][kWarps][kRedWarp]
-    float* s_acc = red + kRedSlots * kWarps * kRedWarp;                               // [kGroup][kWarps * 32] float4, if nkt > 1
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_acc + (p.nkt > 1 ? kGroup * kWarps * 32 * 4 : 0));
+    float* red = reinterpret_cast<float*>(ring + (size_t)p.stages * p.stage_bytes);   // [red_slots][kWarps][kRedWarp]
+    float* s_part = red + p.red_slots * kWarps * kRedWarp;                             // [sg_units][kVecs][16], if phases > 1
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_part + (p.phases > 1 ? p.sg_units * kVecs * kUnitRows : 0));
     const uint32_t bar0 = smem_addr(bars);
     auto full = [&](uint32_t s) { return bar0 + 8u * s; };
     auto empty = [&](uint32_t s) { return bar0 + 8u * (kMaxStages + s); };
     auto red_full = [&](uint32_t b) { return bar0 + 8u * (2 * kMaxStages + b); };
-    auto red_empty = [&](uint32_t b) { return bar0 + 8u * (2 * kMaxStages + kRedSlots + b); };
-    const uint32_t planes_bar = bar0 + 8u * (2 * kMaxStages + 2 * kRedSlots);
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 2 * kRedSlots + 1);
+    auto red_empty = [&](uint32_t b) { return bar0 + 8u * (2 * kMaxStages + kMaxRedSlots + b); };
+    auto planes_bar = [&](uint32_t slot) { return bar0 + 8u * (2 * kMaxStages + 2 * kMaxRedSlots + slot); };
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 2 * kMaxRedSlots + 2);
 
     const uint32_t tid = threadIdx.x;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -258,20 +255,18 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
             mbar_init(full(s), 1);
             mbar_init(empty(s), kWarps);
         }
-        for (uint32_t b = 0; b < kRedSlots; ++b) {
+        for (uint32_t b = 0; b < p.red_slots; ++b) {
             mbar_init(red_full(b), kWarps);
-            mbar_init(red_empty(b), 1);
+            mbar_init(red_empty(b), 1);      // used per half of the slots: [0] and [red_slots / 2]
         }
-        mbar_init(planes_bar, 1);
+        mbar_init(planes_bar(0), 1);
+        mbar_init(planes_bar(1), 1);
         mbar_init_fence();
     }
     __syncthreads();
 
     uint32_t u0, u1;
     my_units(p, &u0, &u1);
-    const uint32_t kpart = blockIdx.x % p.cs;
-    const uint32_t kt_blocks = NBW * kWarps;                 // blocks per column tile
-    const uint32_t q_tile_bytes = kt_blocks * QB;            // quants per row and tile
 
     if (tid >= kWarps * 32 + 32) {
         // ------------------------------------------------------------ epilogue warp ----
@@ -279,76 +274,55 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
         const uint32_t lane = tid & 31, r = lane & 15, half = lane >> 4;
         constexpr int NV = MODE == FULL ? kVecs / 2 : 1;     // vectors per lane
         asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the kernel before the pre-pass
-        const uint32_t serial = *(volatile const uint32_t*)p.serial;   // bumped by this launch's pre-pass kernel
-        uint32_t k = 0;
-        for (uint32_t u = u0; u < u1; ++u, ++k) {
-            const uint32_t b = k % kRedSlots;
-            if (!mbar_wait(red_full(b), (k / kRedSlots) & 1, abort_flag)) report(p.status, 44);
-            const float* slot = red + (size_t)b * kWarps * kRedWarp;
-            const uint32_t row = u * kUnitRows + r;
-            float sum[NV];
+        uint32_t b = 0, b_par = 0;                           // hand-off slot and the parity of its use
+        const uint32_t half_slots = p.red_slots / 2;
+        for (uint32_t sg0 = u0; sg0 < u1; sg0 += p.sg_units) {
+            const uint32_t sg1 = min(sg0 + p.sg_units, u1);
+            for (uint32_t ph = 0; ph < p.phases; ++ph) {
+                for (uint32_t u = sg0; u < sg1; ++u) {
+                    if (!mbar_wait(red_full(b), b_par, abort_flag)) report(p.status, 44);
+                    const float* slot = red + (size_t)b * kWarps * kRedWarp;
+                    const uint32_t row = u * kUnitRows + r;
+                    float sum[NV];
 #pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                const uint32_t v = 2 * i + half;
-                float s = 0.0f;
-                if (MODE == FULL) {
+                    for (int i = 0; i < NV; ++i) {
+                        const uint32_t v = 2 * i + half;
+                        float s = 0.0f;
+                        if (MODE == FULL) {
 #pragma unroll
-                    for (int w = 0; w < kWarps; ++w) s += slot[w * kRedWarp + v * kRedStride + r];
-                } else if (v < 2) {
-                    // the vector's three planes, each already weighted by 65536 / 256 / 1: high plane last
+                            for (int w = 0; w < kWarps; ++w) s += slot[w * kRedWarp + v * kRedStride + r];
+                        } else if (v < 2) {
+                            // the vector's three planes, each already weighted by 65536 / 256 / 1: high plane last
 #pragma unroll
-                    for (int pl = 2; pl >= 0; --pl) {
-                        float sp = 0.0f;
+                            for (int pl = 2; pl >= 0; --pl) {
+                                float sp = 0.0f;
 #pragma unroll
-                        for (int w = 0; w < kWarps; ++w) sp += slot[w * kRedWarp + (3 * v + pl) * kRedStride + r];
-                        s += sp;
-                    }
-                }
-                sum[i] = s;
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(red_empty(b));
-            if (p.cs == 1) {
-#pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    const uint32_t v = 2 * i + half;
-                    if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = sum[i];
-                }
-            } else if (kpart != 0) {
-                // Parts other than the first hand their sums to the first part's CTA through scratch memory:
-                // value and launch serial in ONE 64-bit store, so that no fence is needed (a GPU-scope fence
-                // stalls the SM's whole memory pipeline while its TMA loads are in flight: measured, the
-                // fence-and-counter form of this exchange doubled the kernel's time).
-#pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    const uint32_t v = 2 * i + half;
-                    const uint64_t pair = ((uint64_t)serial << 32) | __float_as_uint(sum[i]);
-                    st_relaxed_gpu_u64(p.partial + ((size_t)(kpart - 1) * kVecs + v) * p.nrows16 + row, pair);
-                }
-            } else {
-                // The first part adds the others' sums in a fixed order.  Their CTAs walk the same row tiles
-                // at the same time, so a pair that does not carry this launch's serial yet is about to; it is
-                // re-read for a bounded time.
-#pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    const uint32_t v = 2 * i + half;
-                    float s = sum[i];
-                    for (uint32_t kp = 1; kp < p.cs; ++kp) {
-                        const uint64_t* src = p.partial + ((size_t)(kp - 1) * kVecs + v) * p.nrows16 + row;
-                        uint64_t pair = ld_relaxed_gpu_u64(src);
-                        if ((uint32_t)(pair >> 32) != serial) {
-                            const long long start = clock64();
-                            while ((uint32_t)((pair = ld_relaxed_gpu_u64(src)) >> 32) != serial) {
-                                if (*abort_flag != 0u || clock64() - start > kWaitCycles) {
-                                    if (*abort_flag == 0u) report(p.status, 47);
-                                    *abort_flag = 1u;
-                                    break;
-                                }
+                                for (int w = 0; w < kWarps; ++w) sp += slot[w * kRedWarp + (3 * v + pl) * kRedStride + r];
+                                s += sp;
                             }
                         }
-                        s += __uint_as_float((uint32_t)pair);
+                        sum[i] = s;
                     }
-                    if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = s;
+                    __syncwarp();
+                    // the slots are given back half of them at a time (one wait per half for the consumers)
+                    ++b;
+                    if (b == half_slots) {
+                        if (lane == 0) mbar_arrive(red_empty(0));
+                    } else if (b == p.red_slots) {
+                        if (lane == 0) mbar_arrive(red_empty(half_slots));
+                        b = 0;
+                        b_par ^= 1u;
+                    }
+                    // the phases' sums are added in phase order; only this warp touches s_part
+                    float* part = s_part + (size_t)(u - sg0) * (kVecs * kUnitRows);
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        const uint32_t v = 2 * i + half;
+                        float s = sum[i];
+                        if (ph > 0) s += part[v * kUnitRows + r];
+                        if (ph + 1 < p.phases) part[v * kUnitRows + r] = s;
+                        else if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = s;
+                    }
                 }
             }
         }
@@ -364,26 +338,30 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
         if (tid == kWarps * 32) {
             tma_prefetch_desc(&map_q);
             tma_prefetch_desc(&map_s);
-            uint32_t k = 0;
-            for (uint32_t g0 = u0; g0 < u1; g0 += kGroup) {
-                const uint32_t g1 = min(g0 + kGroup, u1);
-                for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-                    const uint32_t blk0 = kpart * p.kc_blocks + kt * kt_blocks;       // first block of the tile in the row
-                    for (uint32_t u = g0; u < g1; ++u, ++k) {
-                        const uint32_t s = k % p.stages, use = k / p.stages;
+            uint32_t s = 0, use = 0;                         // ring stage and how often it has been filled before
+            for (uint32_t sg0 = u0; sg0 < u1; sg0 += p.sg_units) {
+                const uint32_t sg1 = min(sg0 + p.sg_units, u1);
+                for (uint32_t ph = 0; ph < p.phases; ++ph) {
+                    const uint32_t blk0 = ph * kt_blocks;                  // first block of the tile in the row
+                    for (uint32_t u = sg0; u < sg1; ++u) {
                         if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1, abort_flag)) report(p.status, 41);
                         const int32_t row = (int32_t)(p.row0 + (uint64_t)u * kUnitRows);
                         const uint32_t dst = smem_addr(ring + (size_t)s * p.stage_bytes);
                         mbar_arrive_expect_tx(full(s), kUnitRows * (q_tile_bytes + (S_SWZ ? 128u : kt_blocks * 2)));
                         tma_load_3d(dst, &map_q, 0, row, (int32_t)(blk0 * QB / 128), full(s));
                         tma_load_2d(dst + p.s_off, &map_s, (int32_t)(blk0 * 2), row, full(s));
+                        if (++s == p.stages) {
+                            s = 0;
+                            ++use;
+                        }
                     }
                 }
             }
-            // do not leave while copies into this CTA's shared memory may still be in flight
-            for (uint32_t s = 0; s < p.stages && s < k; ++s) {
-                const uint32_t last_k = ((k - 1 - s) / p.stages) * p.stages + s;
-                if (!mbar_wait(empty(s), (last_k / p.stages) & 1, abort_flag)) report(p.status, 42);
+            // do not leave while copies into this CTA's shared memory may still be in flight: stage i has been
+            // filled `use` times, once more if the last round reached it
+            for (uint32_t i = 0; i < p.stages; ++i) {
+                const uint32_t fills = use + (i < s ? 1u : 0u);
+                if (fills > 0 && !mbar_wait(empty(i), (fills - 1) & 1, abort_flag)) report(p.status, 42);
             }
         }
         return;
@@ -392,138 +370,147 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
     // ---------------------------------------------------------------- consumer warps ----
     const uint32_t lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
-    // the planes are the pre-pass kernel's output: wait for it, then one bulk copy of this part's share
+    // The planes of a phase sit in one of two slots; the next phase's are fetched while this one is worked on.
+    auto load_planes = [&](uint32_t ph, uint32_t slot) {
+        uint8_t* dst = smem + (size_t)slot * p.slot_bytes;
+        mbar_arrive_expect_tx(planes_bar(slot), plane_bytes + sx_bytes);
+        bulk_g2s(smem_addr(dst), p.planes + (size_t)ph * plane_bytes, plane_bytes, planes_bar(slot));
+        bulk_g2s(smem_addr(dst + plane_bytes), p.sx + (size_t)ph * (kWarps * kVecs), sx_bytes, planes_bar(slot));
+    };
+    // the planes are the pre-pass kernel's output: wait for it
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (tid == 0) {
-        const uint32_t sx_bytes = p.nkt * kWarps * kVecs * 4;
-        mbar_arrive_expect_tx(planes_bar, plane_bytes + sx_bytes);
-        bulk_g2s(smem_addr(s_planes), p.planes + (size_t)kpart * plane_bytes, plane_bytes, planes_bar);
-        bulk_g2s(smem_addr(s_sx), p.sx + (size_t)kpart * p.nkt * kWarps * kVecs, sx_bytes, planes_bar);
-    }
-    if (!mbar_wait(planes_bar, 0, abort_flag)) report(p.status, 45);
+    if (tid == 0 && u0 < u1) load_planes(0, 0);
 
-    // Sums of a group's row tiles between two passes over the columns: shared memory, one float4 per thread
-    // and tile (only touched when a part has more than one column tile).
-    float4* acc_sm = reinterpret_cast<float4*>(s_acc) + warp * 32 + lane;
-    uint32_t k = 0, kr = 0;
-    for (uint32_t g0 = u0; g0 < u1; g0 += kGroup) {
-        const uint32_t nu = min((uint32_t)kGroup, u1 - g0);
-        for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-            // this warp's B fragments for its NBW blocks of the tile, kept in registers over the row tiles
-            uint32_t B[NBW][NP][2];
-            int init[NBW][2];
-            const uint32_t blk_local = kt * kt_blocks + warp * NBW;      // within this part's planes
-#pragma unroll
-            for (int j = 0; j < NBW; ++j) {
-                const uint8_t* pb = s_planes + (size_t)(blk_local + j) * kBP;
-#pragma unroll
-                for (int pl = 0; pl < NP; ++pl) {
-                    const uint2 v = *reinterpret_cast<const uint2*>(pb + pl * 256 + lane * 8);
-                    B[j][pl][0] = v.x;
-                    B[j][pl][1] = v.y;
+    uint32_t k = 0, n = 0;              // tile visits, phases walked
+    uint32_t s = 0, s_par = 0;          // ring stage and the parity of its use
+    uint32_t b = 0, b_use = 0;          // hand-off slot and how often it has been used before
+    const uint32_t half_slots = p.red_slots / 2;
+    for (uint32_t sg0 = u0; sg0 < u1; sg0 += p.sg_units) {
+        const uint32_t sg1 = min(sg0 + p.sg_units, u1);
+        for (uint32_t ph = 0; ph < p.phases; ++ph, ++n) {
+            const uint32_t slot = n & 1;
+            if (p.phases > 1) {
+                // once every consumer warp has left the phase before, its slot takes the planes of the next one
+                asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+                if (tid == 0) {
+                    if (ph + 1 < p.phases) load_planes(ph + 1, slot ^ 1);
+                    else if (sg1 < u1) load_planes(0, slot ^ 1);
                 }
-                const int2 iv = *reinterpret_cast<const int2*>(pb + (kBP - 32) + t * 8);
-                init[j][0] = iv.x;
-                init[j][1] = iv.y;
             }
-            const float2 sxv = *reinterpret_cast<const float2*>(s_sx + (size_t)(kt * kWarps + warp) * kVecs + 2 * t);
-            const bool first_kt = kt == 0, last_kt = kt == p.nkt - 1;
-
-#pragma unroll 1
-            for (uint32_t i = 0; i < nu; ++i, ++k) {
-                const uint32_t s = k % p.stages;
-                if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 43);
-                const uint8_t* sq = ring + (size_t)s * p.stage_bytes;
-                const uint8_t* ss = sq + p.s_off;
-                // the NBW scales of rows g and g + 8 (rows of 2 NBW kWarps bytes; when that is 128, 16-byte group
-                // number n of a row sits at position n ^ row inside it)
-                __align__(16) __half dlo[NBW], dhi[NBW];
-                {
-                    const uint32_t srow = kt_blocks * 2;
-                    const uint32_t o = warp * NBW * 2;
-                    const uint32_t at = S_SWZ ? ((((o >> 4) ^ g) << 4) | (o & 15u)) : o;
-                    const uint8_t* a = ss + g * srow + at;
-                    const uint8_t* b = a + 8 * srow;
-                    if constexpr (NBW == 8) {
-                        *reinterpret_cast<uint4*>(dlo) = *reinterpret_cast<const uint4*>(a);
-                        *reinterpret_cast<uint4*>(dhi) = *reinterpret_cast<const uint4*>(b);
-                    } else if constexpr (NBW == 4) {
-                        *reinterpret_cast<uint2*>(dlo) = *reinterpret_cast<const uint2*>(a);
-                        *reinterpret_cast<uint2*>(dhi) = *reinterpret_cast<const uint2*>(b);
-                    } else if constexpr (NBW == 2) {
-                        *reinterpret_cast<uint32_t*>(dlo) = *reinterpret_cast<const uint32_t*>(a);
-                        *reinterpret_cast<uint32_t*>(dhi) = *reinterpret_cast<const uint32_t*>(b);
-                    } else {
-                        dlo[0] = *reinterpret_cast<const __half*>(a);
-                        dhi[0] = *reinterpret_cast<const __half*>(b);
-                    }
-                }
-                // row g of the tile: [chunk][row][128 bytes]; 16-byte group `sub` of a row sits at sub ^ (row & 7)
-                const uint8_t* qrow = sq + g * 128 + t * 4;
-                float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (!mbar_wait(planes_bar(slot), (n >> 1) & 1, abort_flag)) report(p.status, 45);
+            const uint8_t* s_planes = smem + (size_t)slot * p.slot_bytes;
+            const float2 sxv = *reinterpret_cast<const float2*>(s_planes + plane_bytes + (warp * kVecs + 2 * t) * 4);
+            {
+                // this warp's B fragments for its NBW blocks of the tile, kept in registers over the set's row tiles
+                uint32_t B[NBW][NP][2];
+                int init[NBW][2];
 #pragma unroll
                 for (int j = 0; j < NBW; ++j) {
-                    const uint32_t off = (warp * NBW + j) * QB;                       // byte offset of the block in the tile's row
-                    const uint8_t* qa = qrow + (off >> 7) * 2048 + ((((off >> 4) & 7) ^ g) << 4);
-                    const uint8_t* qb = qa + 1024;                                      // row g + 8: same swizzle
-                    uint32_t A[4];
-                    if constexpr (QT == 1) {
-                        const uint32_t wa = *reinterpret_cast<const uint32_t*>(qa);
-                        const uint32_t wb = *reinterpret_cast<const uint32_t*>(qb);
-                        A[0] = wa & 0x0F0F0F0Fu;
-                        A[1] = wb & 0x0F0F0F0Fu;
-                        A[2] = (wa >> 4) & 0x0F0F0F0Fu;
-                        A[3] = (wb >> 4) & 0x0F0F0F0Fu;
-                    } else {
-                        // the block's second 16 bytes: the next group of the row
-                        const uint8_t* qa2 = qrow + (off >> 7) * 2048 + (((((off >> 4) & 7) + 1) ^ g) << 4);
-                        A[0] = *reinterpret_cast<const uint32_t*>(qa);
-                        A[1] = *reinterpret_cast<const uint32_t*>(qb);
-                        A[2] = *reinterpret_cast<const uint32_t*>(qa2);
-                        A[3] = *reinterpret_cast<const uint32_t*>(qa2 + 1024);
-                    }
-                    const int c_init[4] = {init[j][0], init[j][1], init[j][0], init[j][1]};
-                    const float dl = __half2float(dlo[j]), dh = __half2float(dhi[j]);
-                    if constexpr (MODE == FULL) {
-                        const int zero[4] = {0, 0, 0, 0};
-                        int ca[4], cb[4], cc[4];
-                        mma_i8<QT == 0>(ca, A, B[j][0][0], B[j][0][1], zero);
-                        mma_i8<QT == 0>(cb, A, B[j][1][0], B[j][1][1], zero);
-                        mma_i8<QT == 0>(cc, A, B[j][2][0], B[j][2][1], c_init);
+                    const uint8_t* pb = s_planes + (size_t)(warp * NBW + j) * kBP;
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            // sum q X = 65536 sa + 256 sb + sc, exact in 32 bits by the bound on |X|
-                            const int tsum = ca[e] * 65536 + (cb[e] * 256 + cc[e]);
-                            sacc[e] = fmaf(e < 2 ? dl : dh, (float)tsum, sacc[e]);
-                        }
-                    } else {
-                        int c[4];
-                        mma_i8<QT == 0>(c, A, B[j][0][0], B[j][0][1], c_init);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) sacc[e] = fmaf(e < 2 ? dl : dh, (float)c[e], sacc[e]);
+                    for (int pl = 0; pl < NP; ++pl) {
+                        const uint2 v = *reinterpret_cast<const uint2*>(pb + pl * 256 + lane * 8);
+                        B[j][pl][0] = v.x;
+                        B[j][pl][1] = v.y;
                     }
+                    const int2 iv = *reinterpret_cast<const int2*>(pb + (kBP - 32) + t * 8);
+                    init[j][0] = iv.x;
+                    init[j][1] = iv.y;
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty(s));
-                float4 a4 = first_kt ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : acc_sm[i * (kWarps * 32)];
-                a4.x = fmaf(sxv.x, sacc[0], a4.x);
-                a4.y = fmaf(sxv.y, sacc[1], a4.y);
-                a4.z = fmaf(sxv.x, sacc[2], a4.z);
-                a4.w = fmaf(sxv.y, sacc[3], a4.w);
-                if (!last_kt) {
-                    acc_sm[i * (kWarps * 32)] = a4;
-                } else {
-                    // the tile is complete for this warp's columns: hand it to the epilogue warp
-                    const uint32_t b = kr % kRedSlots;
-                    if (kr >= kRedSlots && !mbar_wait(red_empty(b), ((kr / kRedSlots) - 1) & 1, abort_flag)) report(p.status, 46);
-                    float* slot = red + ((size_t)b * kWarps + warp) * kRedWarp;
-                    slot[(2 * t) * kRedStride + g] = a4.x;
-                    slot[(2 * t + 1) * kRedStride + g] = a4.y;
-                    slot[(2 * t) * kRedStride + g + 8] = a4.z;
-                    slot[(2 * t + 1) * kRedStride + g + 8] = a4.w;
+
+#pragma unroll 1
+                for (uint32_t u = sg0; u < sg1; ++u, ++k) {
+                    if (!mbar_wait(full(s), s_par, abort_flag)) report(p.status, 43);
+                    const uint8_t* sq = ring + (size_t)s * p.stage_bytes;
+                    const uint8_t* ss = sq + p.s_off;
+                    // the NBW scales of rows g and g + 8 (rows of 2 NBW kWarps bytes; when that is 128, 16-byte group
+                    // number n of a row sits at position n ^ row inside it)
+                    __align__(16) __half dlo[NBW], dhi[NBW];
+                    {
+                        const uint32_t srow = kt_blocks * 2;
+                        const uint32_t o = warp * NBW * 2;
+                        const uint32_t at = S_SWZ ? ((((o >> 4) ^ g) << 4) | (o & 15u)) : o;
+                        const uint8_t* a = ss + g * srow + at;
+                        const uint8_t* b = a + 8 * srow;
+                        if constexpr (NBW == 8) {
+                            *reinterpret_cast<uint4*>(dlo) = *reinterpret_cast<const uint4*>(a);
+                            *reinterpret_cast<uint4*>(dhi) = *reinterpret_cast<const uint4*>(b);
+                        } else if constexpr (NBW == 4) {
+                            *reinterpret_cast<uint2*>(dlo) = *reinterpret_cast<const uint2*>(a);
+                            *reinterpret_cast<uint2*>(dhi) = *reinterpret_cast<const uint2*>(b);
+                        } else if constexpr (NBW == 2) {
+                            *reinterpret_cast<uint32_t*>(dlo) = *reinterpret_cast<const uint32_t*>(a);
+                            *reinterpret_cast<uint32_t*>(dhi) = *reinterpret_cast<const uint32_t*>(b);
+                        } else {
+                            dlo[0] = *reinterpret_cast<const __half*>(a);
+                            dhi[0] = *reinterpret_cast<const __half*>(b);
+                        }
+                    }
+                    // row g of the tile: [chunk][row][128 bytes]; 16-byte group `sub` of a row sits at sub ^ (row & 7)
+                    const uint8_t* qrow = sq + g * 128 + t * 4;
+                    float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int j = 0; j < NBW; ++j) {
+                        const uint32_t off = (warp * NBW + j) * QB;                       // byte offset of the block in the tile's row
+                        const uint8_t* qa = qrow + (off >> 7) * 2048 + ((((off >> 4) & 7) ^ g) << 4);
+                        const uint8_t* qb = qa + 1024;                                      // row g + 8: same swizzle
+                        uint32_t A[4];
+                        if constexpr (QT == 1) {
+                            const uint32_t wa = *reinterpret_cast<const uint32_t*>(qa);
+                            const uint32_t wb = *reinterpret_cast<const uint32_t*>(qb);
+                            A[0] = wa & 0x0F0F0F0Fu;
+                            A[1] = wb & 0x0F0F0F0Fu;
+                            A[2] = (wa >> 4) & 0x0F0F0F0Fu;
+                            A[3] = (wb >> 4) & 0x0F0F0F0Fu;
+                        } else {
+                            // the block's second 16 bytes: the next group of the row
+                            const uint8_t* qa2 = qrow + (off >> 7) * 2048 + (((((off >> 4) & 7) + 1) ^ g) << 4);
+                            A[0] = *reinterpret_cast<const uint32_t*>(qa);
+                            A[1] = *reinterpret_cast<const uint32_t*>(qb);
+                            A[2] = *reinterpret_cast<const uint32_t*>(qa2);
+                            A[3] = *reinterpret_cast<const uint32_t*>(qa2 + 1024);
+                        }
+                        const int c_init[4] = {init[j][0], init[j][1], init[j][0], init[j][1]};
+                        const float dl = __half2float(dlo[j]), dh = __half2float(dhi[j]);
+                        if constexpr (MODE == FULL) {
+                            const int zero[4] = {0, 0, 0, 0};
+                            int ca[4], cb[4], cc[4];
+                            mma_i8<QT == 0>(ca, A, B[j][0][0], B[j][0][1], zero);
+                            mma_i8<QT == 0>(cb, A, B[j][1][0], B[j][1][1], zero);
+                            mma_i8<QT == 0>(cc, A, B[j][2][0], B[j][2][1], c_init);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                // sum q X = 65536 sa + 256 sb + sc, exact in 32 bits by the bound on |X|
+                                const int tsum = ca[e] * 65536 + (cb[e] * 256 + cc[e]);
+                                sacc[e] = fmaf(e < 2 ? dl : dh, (float)tsum, sacc[e]);
+                            }
+                        } else {
+                            int c[4];
+                            mma_i8<QT == 0>(c, A, B[j][0][0], B[j][0][1], c_init);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) sacc[e] = fmaf(e < 2 ? dl : dh, (float)c[e], sacc[e]);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty(s));
+                    if (++s == p.stages) {
+                        s = 0;
+                        s_par ^= 1u;
+                    }
+                    // this warp's columns of the tile are done: hand them to the epilogue warp
+                    if (b_use > 0 && (b == 0 || b == half_slots) && !mbar_wait(red_empty(b), (b_use - 1) & 1, abort_flag))
+                        report(p.status, 46);
+                    float* slot_out = red + ((size_t)b * kWarps + warp) * kRedWarp;
+                    slot_out[(2 * t) * kRedStride + g] = sxv.x * sacc[0];
+                    slot_out[(2 * t + 1) * kRedStride + g] = sxv.y * sacc[1];
+                    slot_out[(2 * t) * kRedStride + g + 8] = sxv.x * sacc[2];
+                    slot_out[(2 * t + 1) * kRedStride + g + 8] = sxv.y * sacc[3];
                     __syncwarp();
                     if (lane == 0) mbar_arrive(red_full(b));
-                    ++kr;
+                    if (++b == p.red_slots) {
+                        b = 0;
+                        ++b_use;
+                    }
                 }
             }
         }
@@ -531,41 +518,41 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
 }
 
 struct MmaConfig {
-    uint32_t cs, nbw, stages, stage_bytes, s_off, ring_off, kc_blocks, nkt;
+    uint32_t phases, nbw, stages, red_slots, stage_bytes, s_off, ring_off, slot_bytes, sg_units;
     int mode;
     size_t smem;
 };
 
-// false: the shape does not fit (columns not a multiple of 256 per part, or too many).
-bool choose(const vx_qweights* w, uint32_t batch, MmaConfig* c) {
+// false: the shape does not fit (columns not a multiple of 256).  `units_per_cta`: the most row tiles one
+// CTA will own.
+bool choose(const vx_qweights* w, uint32_t batch, uint32_t units_per_cta, uint32_t nbw_max, uint32_t max_stages, MmaConfig* c) {
     const uint32_t nb = (uint32_t)w->blocks_per_row;
     const uint32_t qb = w->type == VX_Q4_0 ? 16 : 32;
     c->mode = batch <= 2 ? SINGLE : FULL;
     const uint32_t bp = block_planes(c->mode);
-    const uint32_t kWarps = (uint32_t)warps_of(c->mode);
-    const uint32_t nbw_max = 8;
-    for (uint32_t cs = 1; cs <= 8; cs *= 2) {
-        if (nb % (cs * kWarps) != 0) continue;
-        const uint32_t kc_blocks = nb / cs;
-        if ((size_t)kc_blocks * bp > 104 * 1024) continue;
-        uint32_t nbw = nbw_max;
-        while (nbw > 1 && kc_blocks % (nbw * kWarps) != 0) nbw >>= 1;
-        const uint32_t kt_blocks = nbw * kWarps;
-        c->cs = cs;
-        c->nbw = nbw;
-        c->kc_blocks = kc_blocks;
-        c->nkt = kc_blocks / kt_blocks;
-        c->s_off = kUnitRows * kt_blocks * qb;                  // a multiple of 2048
-        c->stage_bytes = (c->s_off + kUnitRows * kt_blocks * 2 + 1023) & ~1023u;
-        const size_t head = (size_t)kc_blocks * bp + (size_t)c->nkt * kWarps * kVecs * 4;
-        c->ring_off = (uint32_t)((head + 1023) & ~(size_t)1023);
-        const size_t tail = (size_t)kRedSlots * kWarps * kRedWarp * 4 + (c->nkt > 1 ? (size_t)kGroup * kWarps * 32 * 16 : 0) +
-                            (2 * kMaxStages + 2 * kRedSlots + 2) * 8;
-        const size_t room = (size_t)227 * 1024 - 1024 - c->ring_off - tail;   // 1024: the dynamic window's own alignment
-        const uint32_t stages = (uint32_t)std::min<size_t>(kMaxStages, room / c->stage_bytes);
-        if (stages < 2) continue;
+    if (nb % kWarps != 0) return false;
+    uint32_t nbw = nbw_max;
+    while (nbw > 1 && nb % (nbw * kWarps) != 0) nbw >>= 1;
+    const uint32_t kt_blocks = nbw * kWarps;
+    c->nbw = nbw;
+    c->phases = nb / kt_blocks;
+    c->s_off = kUnitRows * kt_blocks * qb;                  // a multiple of 2048
+    c->stage_bytes = (c->s_off + kUnitRows * kt_blocks * 2 + 1023) & ~1023u;
+    c->slot_bytes = (kt_blocks * bp + kWarps * kVecs * 4 + 127) & ~127u;
+    c->ring_off = ((c->phases > 1 ? 2 : 1) * c->slot_bytes + 1023) & ~1023u;
+    // Sums waiting between phases: 512 bytes per row tile; room for all of a CTA's tiles up to 48.
+    c->sg_units = c->phases > 1 ? std::min(std::max(units_per_cta, 1u), 48u) : 0x7FFFFFFFu;
+    const size_t part = c->phases > 1 ? (size_t)c->sg_units * kVecs * kUnitRows * 4 : 0;
+    // Hand-off slots: 8 when three ring stages still fit beside them (deeper rings measured no faster), else 4.
+    for (uint32_t red_slots : {(uint32_t)kMaxRedSlots, 4u}) {
+        const size_t tail = (size_t)red_slots * kWarps * kRedWarp * 4 + part + (2 * kMaxStages + 2 * kMaxRedSlots + 4) * 8;
+        const size_t fixed = (size_t)c->ring_off + tail + 1024;              // 1024: the dynamic window's own alignment
+        if (fixed + 2 * (size_t)c->stage_bytes > (size_t)227 * 1024) continue;
+        const uint32_t stages = (uint32_t)std::min<size_t>(max_stages, ((size_t)227 * 1024 - fixed) / c->stage_bytes);
+        if (stages < 3 && red_slots > 4) continue;
         c->stages = stages;
-        c->smem = c->ring_off + (size_t)stages * c->stage_bytes + tail + 1024;
+        c->red_slots = red_slots;
+        c->smem = fixed + (size_t)stages * c->stage_bytes;
         return true;
     }
     return false;
@@ -596,7 +583,7 @@ bool make_maps(const vx_qweights* w, const MmaConfig& c, CUtensorMap* map_q, CUt
     EncodeFn fn = encode_fn();
     if (!fn) return false;
     const uint32_t qb = w->type == VX_Q4_0 ? 16 : 32;
-    const uint32_t kt_blocks = c.nbw * (uint32_t)warps_of(c.mode);
+    const uint32_t kt_blocks = c.nbw * (uint32_t)kWarps;
     const cuuint32_t ones[3] = {1, 1, 1};
     {
         const cuuint64_t dims[3] = {128, w->rows, w->quant_row_bytes / 128};
@@ -630,7 +617,7 @@ vx_status launch_main(vx_context* ctx, const MmaParams& p, const CUtensorMap& mq
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(warps_of(MODE) * 32 + 64);
+    cfg.blockDim = dim3(kWarps * 32 + 64);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -678,24 +665,21 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
                           size_t x_stride, float* y, size_t y_stride, uint32_t batch, bool* eligible) {
     *eligible = false;
     MmaConfig c;
-    if (batch < 1 || batch > (uint32_t)kVecs || !choose(w, batch, &c)) return VX_OK;
+    const uint32_t nrows16 = (nrows + kUnitRows - 1) / kUnitRows * kUnitRows;
+    const uint32_t units = nrows16 / kUnitRows;
+    const uint32_t grid = std::max(1u, std::min((uint32_t)ctx->sm_count, units));
+    if (batch < 1 || batch > (uint32_t)kVecs || !choose(w, batch, (units + grid - 1) / grid, (uint32_t)vx::option(ctx, "gemv.mma_nbw", 8),
+                (uint32_t)std::min<int64_t>(kMaxStages, vx::option(ctx, "gemv.mma_max_stages", kMaxStages)), &c))
+        return VX_OK;
     CUtensorMap map_q, map_s;
     if (!make_maps(w, c, &map_q, &map_s)) return VX_OK;
     const uint32_t nb = (uint32_t)w->blocks_per_row;
-    const uint32_t nrows16 = (nrows + kUnitRows - 1) / kUnitRows * kUnitRows;
     const uint32_t slices = nb / c.nbw;
     const size_t planes_bytes = ((size_t)nb * block_planes(c.mode) + 255) & ~(size_t)255;
     vx_status st = ensure(ctx, &ctx->mma_planes, &ctx->mma_planes_bytes, planes_bytes + (size_t)slices * kVecs * 4);
     if (st != VX_OK) return st;
-    st = ensure(ctx, &ctx->mma_counters, &ctx->mma_counters_bytes, 256);
-    if (st != VX_OK) return st;
-    if (c.cs > 1) {
-        st = ensure(ctx, &ctx->mma_partial, &ctx->mma_partial_bytes, (size_t)(c.cs - 1) * kVecs * nrows16 * 8);
-        if (st != VX_OK) return st;
-    }
     uint8_t* planes = static_cast<uint8_t*>(ctx->mma_planes);
     float* sx = reinterpret_cast<float*>(planes + planes_bytes);
-    uint32_t* serial = static_cast<uint32_t*>(ctx->mma_counters);
 
     const bool q4 = w->type == VX_Q4_0;
     {
@@ -709,11 +693,8 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        // Early start only without a column split: with one, the CTAs of a row tile wait for each other's sums
-        // and must start together, which they do when the grid starts on an idle GPU (measured: 20 % slower
-        // when the CTAs of a launch trickle in under the tail of the launch before).
-        cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 && c.cs == 1 ? 1 : 0;
-        VX_CUDA(cudaLaunchKernelEx(&cfg, pre, x, (uint64_t)x_stride, batch, c.nbw, planes, sx, serial));
+        cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 ? 1 : 0;
+        VX_CUDA(cudaLaunchKernelEx(&cfg, pre, x, (uint64_t)x_stride, batch, c.nbw, planes, sx));
     }
     VX_CUDA(cudaGetLastError());
     ctx->launches++;
@@ -725,10 +706,11 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
     p.nb = nb;
     p.row0 = row0;
     p.nrows = nrows;
-    p.cs = c.cs;
-    p.kc_blocks = c.kc_blocks;
-    p.nkt = c.nkt;
+    p.phases = c.phases;
+    p.sg_units = c.sg_units;
+    p.slot_bytes = c.slot_bytes;
     p.stages = c.stages;
+    p.red_slots = c.red_slots;
     p.stage_bytes = c.stage_bytes;
     p.s_off = c.s_off;
     p.ring_off = c.ring_off;
@@ -737,13 +719,8 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
     p.y = y;
     p.y_stride = y_stride;
     p.batch = batch;
-    p.partial = static_cast<uint64_t*>(ctx->mma_partial);
-    p.serial = serial;
     p.nrows16 = nrows16;
     p.status = ctx->d_status;
-    const uint32_t units = nrows16 / kUnitRows;
-    const uint32_t pairs = std::max(1u, std::min((uint32_t)ctx->sm_count / c.cs, units));
-    const uint32_t grid = pairs * c.cs;
     if (c.mode == FULL)
         st = q4 ? launch_nbw<1, FULL>(ctx, c.nbw, p, map_q, map_s, grid, c.smem) : launch_nbw<0, FULL>(ctx, c.nbw, p, map_q, map_s, grid, c.smem);
     else

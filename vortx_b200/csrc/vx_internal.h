@@ -72,14 +72,9 @@ struct vx_context {
     bool status_dirty = false;             // a kernel that may write d_status ran since the last check
     bool weights_fresh = false;            // a kernel of this stream has written quantised weights since the last GEMV launch
     void* reduce_scratch = nullptr;        // per-block partials of the wide reduction (device)
-    // scratch of the tensor-core batch GEMV (device, grown on demand): x as fixed-point planes, the parts
-    // of a column split, the count of launches (word 0 of mma_counters)
+    // scratch of the tensor-core batch GEMV (device, grown on demand): x as fixed-point planes
     void* mma_planes = nullptr;
     size_t mma_planes_bytes = 0;
-    void* mma_partial = nullptr;
-    size_t mma_partial_bytes = 0;
-    void* mma_counters = nullptr;
-    size_t mma_counters_bytes = 0;
     std::map<std::string, int64_t> options;
 };
 

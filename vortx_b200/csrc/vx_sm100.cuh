@@ -82,11 +82,6 @@ __device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void* src, uin
         : "memory");
 }
 
-// Asks for `bytes` (a multiple of 16, from a 16-byte aligned address) to be brought into L2; nothing waits for it.
-__device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
-
 // --------------------------------------------------------- tiled TMA (tensor map) ----
 // x is the innermost coordinate; x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int32_t x, int32_t y, uint32_t bar) {
@@ -217,14 +212,6 @@ __device__ __forceinline__ int dp4a_ss(uint32_t a_signed, uint32_t b_signed, int
 // has stored since.
 __device__ __forceinline__ void st_relaxed_sys_u64(uint64_t* ptr, uint64_t v) {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(ptr), "l"(v) : "memory");
-}
-__device__ __forceinline__ void st_relaxed_gpu_u64(uint64_t* ptr, uint64_t v) {
-    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(ptr), "l"(v) : "memory");
-}
-__device__ __forceinline__ uint64_t ld_relaxed_gpu_u64(const uint64_t* ptr) {
-    uint64_t v;
-    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ptr) : "memory");
-    return v;
 }
 __device__ __forceinline__ void ld_volatile_v2_u64(const uint64_t* ptr, uint64_t& a, uint64_t& b) {
     asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(ptr) : "memory");
