@@ -50,6 +50,7 @@ METRIC = "q4_0_gemv_hbm_bandwidth"
 UNIT = "GB/s"
 WORKLOAD = "q4_0_gemv_28672x8192_x32"
 CHECKED_PRODUCTS = (0, 13, 31)
+E2E_STAGES = 4     # the end-to-end step runs as this many list launches, copies overlapped with their neighbours
 # DRAM traffic of one 28672 x 8192 product inside a list launch: ncu dram__bytes_read + write of a list of 8
 # (1060.5 MB, second captured launch) / 8, from profiles/gemv_stream_list_q4_0_28672x8192_x8.md
 NCU_TRAFFIC_PER_PRODUCT = 132_560_000
@@ -258,10 +259,11 @@ def run_ours(args):
         if n > 1:
             _lib.check(lib.vx_peer_barrier(be._ctx, flags_arr, n, rank))
 
-    def gather_list(x_ptrs):
-        """The step as ONE list launch: product l reads x_ptrs[l]; its rows go into y[l] here and on every peer."""
+    def gather_list(x_ptrs, lo=0, hi=LAYERS):
+        """Products lo .. hi - 1 of the step as ONE list launch: product l reads x_ptrs[l]; its rows go into y[l]
+        here and on every peer."""
         entries = []
-        for l in range(LAYERS):
+        for l in range(lo, hi):
             off = (l * ROWS + row0) * 4
             entries.append({"w": layers[l], "nrows": shard, "x": x_ptrs[l], "y": y_local + off,
                             "peer_y": [y_ptrs[r] + off for r in others]})
@@ -477,24 +479,31 @@ def run_ours(args):
     check["ok"] = check["ok"] and check["weights_intact"]
     note("kernel-only timing done")
 
-    # ---- end to end through the public API with host buffers: the step's 32 x vectors (all different) go up from
-    # pinned host memory in one copy, the step runs (fused gather + barrier at N > 1), and the products come back:
-    # rank 0's host reads every product whole, the other ranks' hosts the rows their GPU computed.
+    # ---- end to end through the public API with host buffers (vx_gemv_batch_run_host): the step's 32 x vectors
+    # (all different) come from pinned host memory and every product goes back to it — rank 0's host reads every
+    # product whole, the other ranks' hosts the rows their GPU computed.  The step is cut into E2E_STAGES stages
+    # (a list launch each, + barrier at N > 1) so that a stage's copies run beside its neighbours' kernels.
     xs_pin = torch.from_numpy(xs_host).pin_memory()
     ys_pin = torch.empty(LAYERS, ROWS, dtype=torch.float32).pin_memory()
     xs_dev = torch.empty(LAYERS, COLS, device=dev, dtype=torch.float32)
-    e2e_batch = gather_list([xs_dev[l].data_ptr() for l in range(LAYERS)])
+    x_ptrs_e2e = [xs_dev[l].data_ptr() for l in range(LAYERS)]
+    e2e_batches, e2e_stages = [], []
+    per_stage = LAYERS // E2E_STAGES
+    for i in range(E2E_STAGES):
+        lo, hi = i * per_stage, (i + 1) * per_stage
+        e2e_batches.append(gather_list(x_ptrs_e2e, lo, hi))
+        first, width = (0, ROWS) if rank == 0 else (row0, shard)
+        off = (lo * ROWS + first) * 4
+        stage = {"batch": e2e_batches[-1],
+                 "up": (xs_dev.data_ptr() + lo * COLS * 4, xs_pin.data_ptr() + lo * COLS * 4, per_stage * COLS * 4),
+                 "down": (ys_pin.data_ptr() + off, ROWS * 4, y_local + off, ROWS * 4, width * 4, per_stage)}
+        if n > 1:
+            stage["barrier"] = (flag_ptrs, rank)
+        e2e_stages.append(stage)
+    e2e_run = vb.HostStages(be, e2e_stages)
 
     def step_e2e():
-        _lib.check(lib.vx_upload(be._ctx, xs_dev.data_ptr(), xs_pin.data_ptr(), LAYERS * COLS * 4))
-        e2e_batch.launch()
-        finish()
-        if rank == 0:
-            _lib.check(lib.vx_download(be._ctx, ys_pin.data_ptr(), y_local, LAYERS * ROWS * 4))
-        else:
-            # this rank's slab of every product (strided in y): one 2-D copy
-            _lib.check(lib.vx_download_2d(be._ctx, ys_pin.data_ptr() + row0 * 4, ROWS * 4, y_local + row0 * 4, ROWS * 4,
-                                          shard * 4, LAYERS))
+        e2e_run.run()
 
     for _ in range(3):
         step_e2e()
@@ -592,8 +601,10 @@ def run_ours(args):
             "check": check,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": LAYERS * COLS * 4, "d2h_bytes_per_step": LAYERS * ROWS * 4,
-                    "what": "per step: 32 x vectors up from pinned memory, the list launch"
-                            + (" + barrier kernel" if n > 1 else "") + ", every product down to rank 0's host"
+                    "stages": E2E_STAGES,
+                    "what": f"per step, in {E2E_STAGES} stages whose copies overlap the neighbouring stages' kernels: "
+                            "32 x vectors up from pinned memory, the list launches"
+                            + (" + barrier kernels" if n > 1 else "") + ", every product down to rank 0's host"
                             + (" (the other ranks read back the rows they computed)" if n > 1 else "")},
             "gpu_launches": launches_per_step * args.steps * len(per_step),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -616,7 +627,7 @@ def run_ours(args):
     # ---- leave cleanly: lists and graphs first (a CUDA graph that captured work keeps references alive), then the
     # IPC mappings, then a last barrier with nothing in flight.  The process group is not torn down collectively:
     # every rank is past the barrier, has nothing in flight and holds no NVLS binding, and simply exits.
-    for b in (value_batch, chain_batch, plain_batch, e2e_batch):
+    for b in [value_batch, chain_batch, plain_batch] + e2e_batches:
         b.free()
     graphs.clear()
     graph = chain_graph = None

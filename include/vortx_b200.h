@@ -245,6 +245,32 @@ VX_API vx_status vx_gemv_batch_create(vx_context* ctx, const vx_gemv_op* ops, si
                                       vx_gemv_batch** out);
 VX_API vx_status vx_gemv_batch_launch(vx_context* ctx, const vx_gemv_batch* batch);
 VX_API vx_status vx_gemv_batch_free(vx_context* ctx, vx_gemv_batch* batch);
+/* Lists with HOST buffers, copies overlapped with the kernels.  The reference's callers keep their data in
+ * host memory around a dispatch (tensors built from host matrices, `slow_read_buffer` after `synchronize`,
+ * src/linalg/gemm.rs:378-426); a step is cut into stages so that the copies hide behind the kernels:
+ *   stage i   copy up_bytes from up_host to up_device (skipped when 0), run the list, then, if barrier_flags
+ *             is not NULL, a vx_peer_barrier over (barrier_flags, world, rank), then copy down_rows rows of
+ *             down_width_bytes from down_device (rows down_device_pitch apart) to down_host (rows
+ *             down_host_pitch apart; skipped when either count is 0).
+ * Stage i + 1's copy up and stage i - 1's copy down run beside stage i's kernels, on two streams of the
+ * context's own.  Host buffers should be page-locked (vx_host_alloc), or the copies do not overlap.
+ * Returns when every stage's results are in host memory; work given to the context's stream before the call
+ * is waited for first.  The lists must not be launched by anyone else meanwhile. */
+typedef struct vx_host_stage {
+    const vx_gemv_batch* batch;
+    void* up_device;
+    const void* up_host;
+    size_t up_bytes;
+    void* down_host;
+    size_t down_host_pitch;
+    const void* down_device;
+    size_t down_device_pitch;
+    size_t down_width_bytes;
+    size_t down_rows;
+    uint32_t* const* barrier_flags;
+    size_t world, rank;
+} vx_host_stage;
+VX_API vx_status vx_gemv_batch_run_host(vx_context* ctx, const vx_host_stage* stages, size_t n_stages);
 /* Column-sharded GEMM: this rank's panel of C = A * B (out, lhs, rhs and shapes as for vx_gemm_f32
  * with VX_GEMM_TF32; out already advanced to the panel's first column, its row stride the full
  * width of C) computed by the tensor-core kernel, whose epilogue sends every 32 x 32 block of the

@@ -71,6 +71,26 @@ def _worker(rank, world, port, out_dir):
         results[f"{name}_peer_list"] = y2.reshape(slots, rows)
         batch.free()
         dist.barrier()
+        # the same products with HOST buffers, one stage per product: x up from pinned memory, list launch,
+        # barrier, the whole gathered y down to pinned memory, the copies beside the neighbouring stages' kernels
+        vb._lib.check(lib.vx_memset(be._ctx, g.y.local.ptr, 0xFF, slots * rows * 4))
+        be.synchronize()
+        dist.barrier()
+        xs_pin = torch.from_numpy(xs.copy()).pin_memory()
+        ys_pin = torch.full((slots, rows), float("nan")).pin_memory()
+        x_up = be.init_buffer(np.zeros(slots * cols, np.float32))
+        singles = [g.scatter_batch([qm], [x_up.ptr + s * cols * 4], first_slot=s) for s in range(slots)]
+        stages = [{"batch": singles[s],
+                   "up": (x_up.ptr + s * cols * 4, xs_pin.data_ptr() + s * cols * 4, cols * 4),
+                   "down": (ys_pin.data_ptr() + s * rows * 4, rows * 4, g.y.local.ptr + s * rows * 4, rows * 4, rows * 4, 1),
+                   "barrier": (list(g.flags.ptrs), rank)} for s in range(slots)]
+        run = vb.HostStages(be, stages)
+        run.run()
+        run.run()
+        results[f"{name}_peer_host"] = ys_pin.numpy().copy()
+        for b in singles:
+            b.free()
+        dist.barrier()
         g.close()
         # NCCL form through torch tensors on the same stream
         sg = ShardedGemv.for_backend(be, qt, mine, rows, cols)
@@ -304,6 +324,7 @@ def test_peer_scatter_and_nccl_gemv(tmp_path, oracle, world):
             assert (np.abs(peer - y64) <= 2e-6 * absdot).all()
             assert np.array_equal(nccl[0].view(np.uint32), peer[0].view(np.uint32))   # same kernel, same rows
             assert np.array_equal(got[f"{name}_peer_list"].view(np.uint32), peer.view(np.uint32))
+            assert np.array_equal(got[f"{name}_peer_host"].view(np.uint32), peer.view(np.uint32))   # vx_gemv_batch_run_host
             if name == "q4":
                 assert np.array_equal(got["q4_group"].view(np.uint32), peer.view(np.uint32))       # vx_group_gemv_q
                 assert np.array_equal(got["group_all_gather"], np.repeat(np.arange(1, world + 1, dtype=np.float32), 16))

@@ -9,13 +9,13 @@ from .backend import Backend, BufferUsages, GpuBuffer, GpuBufferSlice, GpuEncode
 from .shapes import GGML_IDS, TensorLayout, TensorLayoutBuffers
 from .tensor import Tensor, TensorBuilder, TensorMut, TensorRef
 from .weights_file import WeightFile, write_gguf
-from .linalg import (Contiguous, Gemm, Gemv, GemvBatch, MatrixMode, N, OpAssign, OpAssignVariant, Q4_0, Q8_0, QuantizedMatrix,
+from .linalg import (Contiguous, Gemm, Gemv, GemvBatch, HostStages, MatrixMode, N, OpAssign, OpAssignVariant, Q4_0, Q8_0, QuantizedMatrix,
                      Reduce, ReduceVariant, Repeat, T, dequantize_host, quantize)
 
 __all__ = [
     "Backend", "BufferUsages", "GpuBuffer", "GpuBufferSlice", "GpuEncoder", "GpuPass",
     "GGML_IDS", "TensorLayout", "TensorLayoutBuffers", "Tensor", "TensorBuilder", "TensorMut",
-    "TensorRef", "Gemm", "Gemv", "GemvBatch", "Reduce", "ReduceVariant", "OpAssign", "OpAssignVariant", "Contiguous", "Repeat",
+    "TensorRef", "Gemm", "Gemv", "GemvBatch", "HostStages", "Reduce", "ReduceVariant", "OpAssign", "OpAssignVariant", "Contiguous", "Repeat",
     "MatrixMode", "N", "T", "Q4_0", "Q8_0", "QuantizedMatrix",
     "quantize", "dequantize_host", "WeightFile", "write_gguf", "LayoutError", "ShapeMismatch", "VortxError", "load", "LIB_PATH",
 ]

@@ -58,6 +58,15 @@ class VxGemvOp(C.Structure):
                 ("x_seg_len", C.c_size_t), ("x_seg_stride", C.c_size_t), ("x_seg_first", C.c_size_t)]
 
 
+class VxHostStage(C.Structure):
+    """vx_host_stage: one stage of vx_gemv_batch_run_host."""
+
+    _fields_ = [("batch", C.c_void_p), ("up_device", C.c_void_p), ("up_host", C.c_void_p), ("up_bytes", C.c_size_t),
+                ("down_host", C.c_void_p), ("down_host_pitch", C.c_size_t), ("down_device", C.c_void_p),
+                ("down_device_pitch", C.c_size_t), ("down_width_bytes", C.c_size_t), ("down_rows", C.c_size_t),
+                ("barrier_flags", C.POINTER(C.c_void_p)), ("world", C.c_size_t), ("rank", C.c_size_t)]
+
+
 class VortxError(RuntimeError):
     """A non-zero vx_status; `.status` holds the code."""
 
@@ -125,6 +134,7 @@ SIGNATURES = {
     "vx_gemv_batch_create": (C.c_int32, [_P, _P, C.c_size_t, C.POINTER(_P)]),
     "vx_gemv_batch_launch": (C.c_int32, [_P, _P]),
     "vx_gemv_batch_free": (C.c_int32, [_P, _P]),
+    "vx_gemv_batch_run_host": (C.c_int32, [_P, _P, C.c_size_t]),
     "vx_gemm_tf32_scatter": (C.c_int32, [_P, _P, _P, _P, C.POINTER(VxShapes3), C.POINTER(_P), C.c_size_t]),
     "vx_peer_barrier": (C.c_int32, [_P, C.POINTER(_P), C.c_size_t, C.c_size_t]),
     "vx_group_unique_id": (C.c_int32, [_P]),

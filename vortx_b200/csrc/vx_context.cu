@@ -140,6 +140,7 @@ vx_status vx_context_destroy(vx_context* ctx) {
     vx::DeviceGuard guard(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->reduce_scratch) cudaFree(ctx->reduce_scratch);
+    vx::host_streams_free(ctx);
     if (ctx->mma_planes) cudaFree(ctx->mma_planes);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);

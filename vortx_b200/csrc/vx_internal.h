@@ -75,6 +75,7 @@ struct vx_context {
     // scratch of the tensor-core batch GEMV (device, grown on demand): x as fixed-point planes
     void* mma_planes = nullptr;
     size_t mma_planes_bytes = 0;
+    void* host_streams = nullptr;          // vx::HostStreams of vx_gemv_batch_run_host, made on first use
     std::map<std::string, int64_t> options;
 };
 
@@ -93,6 +94,9 @@ struct vx_qweights {
 namespace vx {
 
 int64_t option(const vx_context* ctx, const char* key, int64_t fallback);
+
+// Frees the copy streams and events of vx_gemv_batch_run_host (vx_host_stages.cu), if any were made.
+void host_streams_free(vx_context* ctx);
 
 // Budget of the device-side waits on exchange vectors and peer barriers, in SM clocks: the option
 // "wait_cycles", or about 0.2 s.

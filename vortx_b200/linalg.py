@@ -344,6 +344,41 @@ class GemvBatch:
             pass
 
 
+class HostStages:
+    """A step with HOST buffers cut into stages whose copies hide behind the kernels (vx_gemv_batch_run_host).
+
+    Each stage is a dict: batch (GemvBatch) and optionally up = (device_ptr, host_ptr, bytes), down =
+    (host_ptr, host_pitch, device_ptr, device_pitch, width_bytes, rows), barrier = (flag pointers of every rank,
+    rank): a peer barrier between the list and the copy down.  Host pointers should be page-locked.  Pointers
+    are captured at construction; `run()` returns when every stage's results are in host memory."""
+
+    def __init__(self, backend: Backend, stages):
+        n = len(stages)
+        self._arr = (_lib.VxHostStage * max(1, n))()
+        self._keep = []
+        for i, s in enumerate(stages):
+            a = self._arr[i]
+            a.batch = s["batch"]._h
+            self._keep.append(s["batch"])
+            up = s.get("up")
+            if up:
+                a.up_device, a.up_host, a.up_bytes = up
+            down = s.get("down")
+            if down:
+                (a.down_host, a.down_host_pitch, a.down_device, a.down_device_pitch, a.down_width_bytes,
+                 a.down_rows) = down
+            bar = s.get("barrier")
+            if bar:
+                flags, rank = bar
+                fa = (C.c_void_p * len(flags))(*flags)
+                self._keep.append(fa)
+                a.barrier_flags, a.world, a.rank = fa, len(flags), rank
+        self.backend, self.n = backend, n
+
+    def run(self) -> None:
+        _lib.check(_lib.load().vx_gemv_batch_run_host(self.backend._ctx, self._arr, self.n))
+
+
 def _ptr_len(t):
     """Device pointer (with view offset) and remaining length of a Tensor / view / buffer / raw int."""
     if isinstance(t, int):

@@ -238,15 +238,16 @@ class PeerScatterGemv:
                                                self.vectors[y_vec].local.ptr, self._vec_peers[y_vec],
                                                len(self._others), self.row0, self.world if self.cyclic else 1))
 
-    def scatter_batch(self, weights_list, x_ptrs):
+    def scatter_batch(self, weights_list, x_ptrs, first_slot: int = 0):
         """Independent products as ONE persistent launch per GPU: product l reads the plain x_ptrs[l] and stores
-        its rows into y[l] here and on every peer.  After `launch()`, one `finish()` completes all of them."""
+        its rows into y[first_slot + l] here and on every peer.  After `launch()`, one `finish()` completes all
+        of them."""
         from .linalg import GemvBatch
         if self.cyclic:
             raise ValueError("plain peer rows take contiguous slabs")
         entries = []
         for l, w in enumerate(weights_list):
-            off = (l * self.rows + self.row0) * 4
+            off = ((first_slot + l) * self.rows + self.row0) * 4
             entries.append({"w": w, "nrows": self.nrows, "x": x_ptrs[l], "y": self.y.local.ptr + off,
                             "peer_y": [self.y.ptrs[r] + off for r in self._others]})
         return GemvBatch(self.backend, entries)
