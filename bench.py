@@ -50,7 +50,10 @@ METRIC = "q4_0_gemv_hbm_bandwidth"
 UNIT = "GB/s"
 WORKLOAD = "q4_0_gemv_28672x8192_x32"
 CHECKED_PRODUCTS = (0, 13, 31)
-E2E_STAGES = 4     # the end-to-end step runs as this many list launches, copies overlapped with their neighbours
+# The end-to-end step runs as this many list launches, copies overlapped with their neighbours: 4 on one GPU; 2 on
+# several, where every further stage costs a barrier kernel across the GPUs (measured at N = 2: 0.463 ms with 2
+# stages, 0.482 with 4, 0.487 with 1).
+E2E_STAGES_1GPU, E2E_STAGES_MULTI = 4, 2
 # DRAM traffic of one 28672 x 8192 product inside a list launch: ncu dram__bytes_read + write of a list of 8
 # (1060.5 MB, second captured launch) / 8, from profiles/gemv_stream_list_q4_0_28672x8192_x8.md
 NCU_TRAFFIC_PER_PRODUCT = 132_560_000
@@ -488,6 +491,7 @@ def run_ours(args):
     xs_dev = torch.empty(LAYERS, COLS, device=dev, dtype=torch.float32)
     x_ptrs_e2e = [xs_dev[l].data_ptr() for l in range(LAYERS)]
     e2e_batches, e2e_stages = [], []
+    E2E_STAGES = E2E_STAGES_1GPU if n == 1 else E2E_STAGES_MULTI
     per_stage = LAYERS // E2E_STAGES
     for i in range(E2E_STAGES):
         lo, hi = i * per_stage, (i + 1) * per_stage

@@ -76,20 +76,23 @@ vx_status vx_gemv_batch_run_host(vx_context* ctx, const vx_host_stage* stages, s
     VX_CUDA(cudaStreamWaitEvent(h->down, start, 0));
     for (size_t i = 0; i < n_stages; ++i) {
         const vx_host_stage& s = stages[i];
-        if (s.up_bytes) VX_CUDA(cudaMemcpyAsync(s.up_device, s.up_host, s.up_bytes, cudaMemcpyHostToDevice, h->up));
-        VX_CUDA(cudaEventRecord(up_done[i], h->up));
+        if (s.up_bytes) {
+            VX_CUDA(cudaMemcpyAsync(s.up_device, s.up_host, s.up_bytes, cudaMemcpyHostToDevice, h->up));
+            VX_CUDA(cudaEventRecord(up_done[i], h->up));
+        }
     }
     for (size_t i = 0; i < n_stages; ++i) {
         const vx_host_stage& s = stages[i];
-        VX_CUDA(cudaStreamWaitEvent(ctx->stream, up_done[i], 0));
+        if (s.up_bytes) VX_CUDA(cudaStreamWaitEvent(ctx->stream, up_done[i], 0));
         st = vx_gemv_batch_launch(ctx, s.batch);
         if (st == VX_OK && s.barrier_flags) st = vx_peer_barrier(ctx, s.barrier_flags, s.world, s.rank);
         if (st != VX_OK) break;
-        VX_CUDA(cudaEventRecord(run_done[i], ctx->stream));
-        VX_CUDA(cudaStreamWaitEvent(h->down, run_done[i], 0));
-        if (s.down_width_bytes != 0 && s.down_rows != 0)
+        if (s.down_width_bytes != 0 && s.down_rows != 0) {
+            VX_CUDA(cudaEventRecord(run_done[i], ctx->stream));
+            VX_CUDA(cudaStreamWaitEvent(h->down, run_done[i], 0));
             VX_CUDA(cudaMemcpy2DAsync(s.down_host, s.down_host_pitch, s.down_device, s.down_device_pitch, s.down_width_bytes,
                                       s.down_rows, cudaMemcpyDeviceToHost, h->down));
+        }
     }
     // everything of this call is over before it returns, also after an error part-way
     const cudaError_t e1 = cudaStreamSynchronize(h->up);
