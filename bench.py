@@ -901,7 +901,99 @@ PROFILE_CASES = {
     "gemm_simt_exact_1024": ("gemm", 1024, 1024, "SIMT", 0),
     "gemm_tf32_4096": ("gemm", 4096, 4096, "TF32", 0),
     "gemm_tf32_8192": ("gemm", 8192, 8192, "TF32", 0),
+    # not for ncu: the chained list with the kernel's own %globaltimer stamps (a library built with
+    # `python -m vortx_b200.build --timeline`); runs on 1 GPU or, under torchrun, on N
+    "gemv_chain_timeline": ("chain_timeline", ROWS, COLS, "Q4_0", LAYERS),
 }
+
+
+def run_chain_timeline():
+    """Where a chained product's time goes, per thread block, from the list kernel's own %globaltimer stamps:
+    the bench's chain (32 dependent 28672 x 8192 Q4_0 products, rows split over the ranks, x of a product = the
+    rows every rank computed last in the one before), launched four times; the last launch is stamped."""
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch
+    import torch.distributed as dist
+    rank, n = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    if n > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=n, device_id=torch.device("cuda", local))
+    import vortx_b200 as vb
+    from vortx_b200 import _lib, synth
+    from vortx_b200.multi_gpu import PeerBuffers
+    lib = _lib.load()
+    be = vb.Backend(local)
+    shard, row0 = ROWS // n, rank * (ROWS // n)
+    blocks = vb.quantize(vb.Q4_0, slab_matrix(shard, seed=100 + rank))
+    layers = [vb.QuantizedMatrix(be, vb.Q4_0, blocks, shard, COLS) for _ in range(LAYERS)]
+    x_dev = torch.from_numpy(synth.normal_vectors(1, COLS, seed=1)[0]).cuda()
+    if n > 1:
+        vecs = [PeerBuffers(be, lib.vx_xvec_bytes(ROWS)) for _ in range(2)]
+        vec_ptrs = [v.ptrs for v in vecs]
+    else:
+        bufs = [torch.zeros(lib.vx_xvec_bytes(ROWS), device="cuda", dtype=torch.uint8) for _ in range(2)]
+        vec_ptrs = [[b.data_ptr()] for b in bufs]
+    others = [r for r in range(n) if r != rank]
+    seg_len, seg_stride = COLS // n, ROWS // n
+    entries = []
+    for l in range(LAYERS):
+        e = {"w": layers[l], "nrows": shard, "y_xvec": vec_ptrs[l % 2][rank],
+             "peers": [vec_ptrs[l % 2][r] for r in others], "y_row0": row0, "y_stride": 1}
+        if l == 0:
+            e["x"] = x_dev.data_ptr()
+        else:
+            e["x_xvec"] = vec_ptrs[(l - 1) % 2][rank]
+            e["x_seg_len"], e["x_seg_stride"], e["x_seg_first"] = seg_len, seg_stride, seg_stride - seg_len
+        entries.append(e)
+    chain = vb.GemvBatch(be, entries)
+    sms = torch.cuda.get_device_properties(local).multi_processor_count
+    stamps = torch.zeros(sms * LAYERS * 8, dtype=torch.int64, device="cuda")
+
+    def sync():
+        be.synchronize()
+        if n > 1:
+            dist.barrier()
+
+    for it in range(4):
+        sync()
+        be.set_option("debug.timeline_ptr", stamps.data_ptr() if it == 3 else 0)
+        chain.launch()
+    sync()
+    d = stamps.cpu().numpy().reshape(sms, LAYERS, 8).astype(np.float64)
+    d = d[d[:, 1, 0] > 0]
+    if d.shape[0] == 0:
+        text = f"rank {rank}: no stamps — the library was not built with `python -m vortx_b200.build --timeline`"
+    else:
+        def stat(a):
+            return f"{np.median(a) / 1e3:6.2f} (min {a.min() / 1e3:5.2f}, max {a.max() / 1e3:5.2f})"
+        o = slice(4, LAYERS)
+        begin, waited, conv, first, last, st_last = (d[:, o, i] for i in range(6))
+        prev_last = d[:, 3:LAYERS - 1, 4]
+        prev_store = d[:, 3:LAYERS - 1, 5].max(axis=0, keepdims=True)
+        spread = d[:, o, 5].max(axis=0) - d[:, o, 5].min(axis=0)
+        text = "\n".join([
+            f"rank {rank} of {n}: {d.shape[0]} thread blocks, products 4..{LAYERS - 1}, per block, microseconds: median (min, max)",
+            f"  product period (last tile to last tile)              {stat(last - prev_last)}",
+            f"  last tile of product l-1 -> product l begins         {stat(begin - prev_last)}",
+            f"  the block's wait for x (block-wait form only)        {stat(waited - begin)}",
+            f"  x read (the threads' own waits included), converted  {stat(conv - waited)}",
+            f"  this GPU's last store of l-1 -> x converted here     {stat(conv - prev_store)}",
+            f"  first tile present after the conversion              {stat(first - conv)}",
+            f"  first tile -> last tile computed                     {stat(last - first)}",
+            f"  last tile computed -> its rows stored                {stat(st_last - last)}",
+            f"  spread of the blocks' last stores of a product       {np.median(spread) / 1e3:6.2f} (max {spread.max() / 1e3:5.2f})"])
+    if n > 1:
+        gathered = [None] * n
+        dist.all_gather_object(gathered, text)
+        if rank == 0:
+            print("\n".join(gathered), flush=True)
+    else:
+        print(text, flush=True)
+    chain.free()
+    sync()
+    sys.stdout.flush()
+    os._exit(0)   # past the final barrier with nothing in flight; no communicator teardown
 
 
 def run_profile_case(name: str):
@@ -911,6 +1003,8 @@ def run_profile_case(name: str):
     import vortx_b200 as vb
     from vortx_b200 import _lib
     kind, rows, cols, what, copies = PROFILE_CASES[name]
+    if kind == "chain_timeline":
+        return run_chain_timeline()
     be = vb.Backend(0)
     lib = _lib.load()
     rng = np.random.Generator(np.random.Philox(1))

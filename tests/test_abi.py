@@ -60,6 +60,7 @@ def test_error_paths_and_messages():
     assert lib.vx_quantize(5, w.ctypes.data, 2, 64, out.ctypes.data) == _lib.VX_ERR_INVALID_ARGUMENT
     assert lib.vx_gemm_f32(None, 0, None, None, None, None, 0, 0, 0) == _lib.VX_ERR_INVALID_ARGUMENT
     assert lib.vx_free(None, None) == _lib.VX_ERR_INVALID_ARGUMENT
+    assert lib.vx_gemv_batch_run_host(None, None, 1) == _lib.VX_ERR_INVALID_ARGUMENT
     assert lib.vx_context_destroy(None) == _lib.VX_OK
 
 

@@ -48,21 +48,29 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, timeline: bool = False) -> Path:
+    """Compiles what is out of date and links the library.  `timeline`: the list GEMV kernel with its
+    %globaltimer stamps compiled in (-DVX_TIMELINE, for `bench.py --profile-case gemv_chain_timeline`); the next
+    build without it compiles that file again, so the product never carries the stamps by accident."""
     nvcc = _nvcc()
     OBJ.mkdir(exist_ok=True)
     headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
     jobs = []
     for src in _sources():
         obj = OBJ / (src.stem + ".o")
-        if force or _stale(obj, [src, Path(__file__)] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-x", "cu", "-c", str(src), "-o", str(obj)]
+        extra = ["-DVX_TIMELINE"] if timeline and src.name == "vx_gemv_stream.cu" else []
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-x", "cu", "-c", str(src), "-o", str(obj)]
+        line = OBJ / (src.stem + ".cmd")            # the command the object was made with
+        same_cmd = line.exists() and line.read_text() == " ".join(cmd)
+        if force or not same_cmd or _stale(obj, [src, Path(__file__)] + headers):
             jobs.append((src, obj, cmd))
 
     def run(job):
         src, obj, cmd = job
         r = subprocess.run(cmd, capture_output=True, text=True)
         (OBJ / (src.stem + ".log")).write_text(r.stdout + r.stderr)
+        if r.returncode == 0:
+            (OBJ / (src.stem + ".cmd")).write_text(" ".join(cmd))
         return src, r
 
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
@@ -87,5 +95,7 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--timeline", action="store_true",
+                    help="compile the list GEMV kernel with its %%globaltimer stamps (profiling builds only)")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.timeline))

@@ -94,6 +94,9 @@ struct StreamParams {
     uint32_t block_wait;     // flagged x: one warp waits for the block (see the consumers)
     uint32_t n_vec;
     long long wait_cycles;   // budget of the flagged-x waits, in SM clocks
+#ifdef VX_TIMELINE
+    unsigned long long* timeline;   // [block][entry][8] globaltimer stamps, or null (option "debug.timeline_ptr")
+#endif
     const OpParams* ops;
     uint32_t* vec_hdr[kMaxVecs];   // headers of the exchange vectors the list touches (own memory)
     uint32_t vec_writes[kMaxVecs]; // how often the list writes each of them
@@ -144,6 +147,23 @@ __device__ __forceinline__ uint32_t first_tile(uint32_t op, uint32_t tiles) {
 // NCW: consumer warps, 8 everywhere.  (The plain kernel gets 16 warps per SM from two CTAs.  A flagged
 // CTA of 16 consumer warps, x held twice, measured slower than 8: 17.9 against 15.2 us per chained
 // 14336 x 8192 product.)
+// Timeline build (nvcc -DVX_TIMELINE, `python -m vortx_b200.build --timeline`): thread 0 of the consumers and
+// lane 0 of the epilogue warp stamp %globaltimer (nanoseconds; it ticks every 256 ns here) per list entry:
+//   [0] entry begins  [1] after the block's wait for x (the block-wait form; else = [0])  [2] x read (the threads'
+//   own waits included) and converted  [3] first tile present
+//   [4] last tile computed  [5] rows of the last tile stored  [6] rows of the first tile stored
+// The product build carries none of this.
+#ifdef VX_TIMELINE
+#define VX_TL(...) do { __VA_ARGS__; } while (0)
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#else
+#define VX_TL(...) do { } while (0)
+#endif
+
 template <int QT, int CPT, int RP, int TR, bool XCH, int NCW>
 __global__ void __launch_bounds__(NCW * 32 + 64, 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
@@ -208,6 +228,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
             const uint32_t stride = XCH ? op.y_pair_stride : 1;
             // Generation this GEMV writes.
             const uint32_t gen = XCH && y_pairs ? *(volatile const uint32_t*)p.vec_hdr[op.y_vec] + op.y_gen_add : 0;
+#ifdef VX_TIMELINE
+            bool tl_first_store = true;
+#endif
             for (; t < tiles; t += gridDim.x, ++k) {
                 const uint32_t b = k % kRedBufs;
                 if (!mbar_wait(red_full(b), (k / kRedBufs) & 1, abort_flag)) report(p.status, 14);
@@ -227,6 +250,13 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(red_empty(b));
+                VX_TL(if (p.timeline && lane == 0) {
+                    unsigned long long* d = p.timeline + ((size_t)blockIdx.x * p.n_ops + o) * 8;
+                    const unsigned long long now = gtime();
+                    d[5] = now;
+                    if (tl_first_store) d[6] = now;
+                    tl_first_store = false;
+                });
             }
         }
         if (XCH && p.n_vec > 0 && lane == 0) {
@@ -300,6 +330,11 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         if (t >= tiles) continue;
         const uint64_t* const x_pairs = XCH && op.x_vec >= 0 ? op.x_pairs : nullptr;
         const float* const x = op.x;
+#ifdef VX_TIMELINE
+        unsigned long long* const tl = p.timeline && tid == 0 ? p.timeline + ((size_t)blockIdx.x * p.n_ops + o) * 8 : nullptr;
+        bool tl_first = true;
+#endif
+        VX_TL(if (tl) tl[0] = gtime());
         if (x_pairs || x != held_x) {
             held_x = x_pairs ? nullptr : x;
             const uint32_t x_gen = x_pairs ? *(volatile const uint32_t*)p.vec_hdr[op.x_vec] + op.x_gen_add : 0;
@@ -340,6 +375,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
             }
+            VX_TL(if (tl) tl[1] = gtime());
 #pragma unroll
             for (int j = 0; j < CPT; ++j) {
                 const uint32_t c = tc + j * p.tpr;
@@ -435,11 +471,13 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 initC[j] = QT == 1 ? -8 * sc : 0;
             }
         }
+        VX_TL(if (tl) tl[2] = gtime());
 
         const uint64_t row0 = op.row0;
         for (; t < tiles; t += gridDim.x, ++k) {
             const uint32_t s = k % p.stages;
             if (!mbar_wait(full(s), (k / p.stages) & 1, abort_flag)) report(p.status, 13);
+            VX_TL(if (tl && tl_first) { tl[3] = gtime(); tl_first = false; });
             const uint8_t* sq = smem + (size_t)s * p.stage_bytes;
             const uint64_t soff = (row0 + (uint64_t)t * TR) * p.nb * 2;
             const uint8_t* ss = sq + p.q_stage_bytes + (uint32_t)(soff & 15);
@@ -514,6 +552,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(red_full(b));
+            VX_TL(if (tl) tl[4] = gtime());
         }
     }
 }
@@ -962,6 +1001,9 @@ vx_status vx_gemv_batch_launch(vx_context* ctx, const vx_gemv_batch* b) {
     StreamParams p = b->params;
     p.status = ctx->d_status;
     p.wait_cycles = vx::wait_cycles(ctx);
+#ifdef VX_TIMELINE
+    p.timeline = reinterpret_cast<unsigned long long*>(vx::option(ctx, "debug.timeline_ptr", 0));
+#endif
     const StreamConfig& c = b->cfg;
     const vx_status st = b->flagged ? launch_tr<true>(ctx, b->qtype, c, p, b->grid) : launch_tr<false>(ctx, b->qtype, c, p, b->grid);
     if (st != VX_OK) return st;
