@@ -87,6 +87,43 @@ def test_one_and_two_vectors_on_tensor_cores(backend, oracle, qt, batch, rows, c
     qm.free()
 
 
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("batch", [2, 5])
+def test_many_column_phases(backend, oracle, qt, batch):
+    """65536 columns: 32 phases of 2048 columns, the planes of a phase loaded while the one before is worked on."""
+    rows, cols = 40, 65536
+    w = synth.normal_matrix(rows, cols, seed=8)
+    x = synth.normal_vectors(batch, cols, seed=9)
+    blocks = oracle.quantize(qt, w)
+    qm = vb.QuantizedMatrix(backend, qt, blocks, rows, cols)
+    y64, absdot = oracle.gemv_f64(qt, blocks, rows, cols, x)
+    got, launches = _run(backend, qm, x)
+    assert launches == 2
+    _check(got, y64, absdot)
+    qm.free()
+
+
+@pytest.mark.parametrize("batch", [2, 8])
+def test_more_row_tiles_per_block_than_wait_between_phases(backend, oracle, batch):
+    """120000 rows: 51 row tiles per thread block, more than the 48 whose sums wait in shared memory between two
+    phases, so a block walks its rows in two sets and re-walks the phases for each ("gemv.mma_nbw" = 1 makes two
+    phases out of 512 columns)."""
+    rows, cols = 120000, 512
+    w = synth.normal_matrix(rows, cols, seed=10)
+    x = synth.normal_vectors(batch, cols, seed=11)
+    blocks = oracle.quantize(vb.Q4_0, w)
+    qm = vb.QuantizedMatrix(backend, vb.Q4_0, blocks, rows, cols)
+    y64, absdot = oracle.gemv_f64(vb.Q4_0, blocks, rows, cols, x)
+    backend.set_option("gemv.mma_nbw", 1)
+    try:
+        got, launches = _run(backend, qm, x)
+    finally:
+        backend.set_option("gemv.mma_nbw", 8)
+    assert launches == 2
+    _check(got, y64, absdot)
+    qm.free()
+
+
 def test_batch_gemv_slabs_strides_and_unaligned_x(backend, oracle):
     rows, cols, batch = 700, 2048, 5
     w = synth.normal_matrix(rows, cols, seed=1)
