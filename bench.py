@@ -504,7 +504,8 @@ def run_ours(args):
         if n > 1:
             stage["barrier"] = (flag_ptrs, rank)
         e2e_stages.append(stage)
-    e2e_run = vb.HostStages(be, e2e_stages)
+    barrier()
+    e2e_run = vb.HostStages(be, e2e_stages, recorded=True)     # vx_host_pipeline: the step recorded once, replayed per step
 
     def step_e2e():
         e2e_run.run()
@@ -631,6 +632,7 @@ def run_ours(args):
     # ---- leave cleanly: lists and graphs first (a CUDA graph that captured work keeps references alive), then the
     # IPC mappings, then a last barrier with nothing in flight.  The process group is not torn down collectively:
     # every rank is past the barrier, has nothing in flight and holds no NVLS binding, and simply exits.
+    e2e_run.free()
     for b in [value_batch, chain_batch, plain_batch] + e2e_batches:
         b.free()
     graphs.clear()

@@ -21,9 +21,10 @@ def _pinned(n_floats):
     return p, arr
 
 
+@pytest.mark.parametrize("recorded", [False, True])
 @pytest.mark.parametrize("qt", [vb.Q4_0, vb.Q8_0])
 @pytest.mark.parametrize("n_stages", [1, 3, 6])
-def test_staged_lists_match_the_plain_launch(backend, oracle, qt, n_stages):
+def test_staged_lists_match_the_plain_launch(backend, oracle, qt, n_stages, recorded):
     lib = _lib.load()
     rows, cols, products = 300, 512, 6
     w = synth.normal_matrix(rows, cols, seed=31)
@@ -45,9 +46,15 @@ def test_staged_lists_match_the_plain_launch(backend, oracle, qt, n_stages):
         stages.append({"batch": batches[-1],
                        "up": (xd.ptr + lo * cols * 4, xp.value + lo * cols * 4, per * cols * 4),
                        "down": (yp.value + lo * rows * 4, rows * 4, yd.ptr + lo * rows * 4, rows * 4, rows * 4, per)})
-    run = vb.HostStages(backend, stages)
+    run = vb.HostStages(backend, stages, recorded=recorded)     # recorded: one CUDA graph replayed per step
     for rep in range(3):                          # streams and events are reused from the second call on
         y_host[:] = np.nan
+        if rep == 2:                              # new inputs in the same host buffers: nothing is baked in but pointers
+            x_host[:] = xs.ravel()[::-1].copy()
+            run.run()
+            flipped = y_host.reshape(products, rows).copy()
+            x_host[:] = xs.ravel()
+            y_host[:] = np.nan
         run.run()
         got = y_host.reshape(products, rows).copy()
         assert np.abs(got - y64).max() / np.abs(y64).max() <= 1e-4
@@ -59,6 +66,9 @@ def test_staged_lists_match_the_plain_launch(backend, oracle, qt, n_stages):
         b.launch()
     backend.slow_read_buffer(yd, plain)
     assert np.array_equal(plain.view(np.uint32), got.ravel().view(np.uint32))
+    y64f, absdotf = oracle.gemv_f64(qt, blocks, rows, cols, xs.ravel()[::-1].copy().reshape(products, cols))
+    assert (np.abs(flipped - y64f) <= 2e-6 * absdotf).all()
+    run.free()
     for b in batches:
         b.free()
     qm.free()
@@ -91,5 +101,14 @@ def test_stages_without_copies_and_bad_stages(backend, oracle):
     bad[1].down_host_pitch, bad[1].down_device_pitch, bad[1].down_width_bytes, bad[1].down_rows = 4, 256, 256, 1
     assert lib.vx_gemv_batch_run_host(backend._ctx, bad, 2) == 1      # host pitch shorter than a row
     assert backend.launch_count() == before
+    # a recorded step refuses pageable host memory (its copies could not be recorded)
+    pageable = np.zeros(cols, np.float32)
+    stage = (_lib.VxHostStage * 1)()
+    stage[0].batch = batch._h
+    stage[0].up_device, stage[0].up_host, stage[0].up_bytes = xd.ptr, pageable.ctypes.data, cols * 4
+    h = C.c_void_p()
+    assert lib.vx_host_pipeline_create(backend._ctx, stage, 1, C.byref(h)) == 1 and not h.value
+    assert b"page-locked" in lib.vx_last_error()
+    assert lib.vx_host_pipeline_run(None) == 1 and lib.vx_host_pipeline_free(None) == 0
     batch.free()
     qm.free()

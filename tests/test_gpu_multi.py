@@ -88,6 +88,13 @@ def _worker(rank, world, port, out_dir):
         run.run()
         run.run()
         results[f"{name}_peer_host"] = ys_pin.numpy().copy()
+        ys_pin.fill_(float("nan"))
+        dist.barrier()
+        rec = vb.HostStages(be, stages, recorded=True)        # the step as one CUDA graph, barriers included
+        rec.run()
+        rec.run()
+        results[f"{name}_peer_host_recorded"] = ys_pin.numpy().copy()
+        rec.free()
         for b in singles:
             b.free()
         dist.barrier()
@@ -325,6 +332,7 @@ def test_peer_scatter_and_nccl_gemv(tmp_path, oracle, world):
             assert np.array_equal(nccl[0].view(np.uint32), peer[0].view(np.uint32))   # same kernel, same rows
             assert np.array_equal(got[f"{name}_peer_list"].view(np.uint32), peer.view(np.uint32))
             assert np.array_equal(got[f"{name}_peer_host"].view(np.uint32), peer.view(np.uint32))   # vx_gemv_batch_run_host
+            assert np.array_equal(got[f"{name}_peer_host_recorded"].view(np.uint32), peer.view(np.uint32))   # vx_host_pipeline
             if name == "q4":
                 assert np.array_equal(got["q4_group"].view(np.uint32), peer.view(np.uint32))       # vx_group_gemv_q
                 assert np.array_equal(got["group_all_gather"], np.repeat(np.arange(1, world + 1, dtype=np.float32), 16))

@@ -135,6 +135,9 @@ SIGNATURES = {
     "vx_gemv_batch_launch": (C.c_int32, [_P, _P]),
     "vx_gemv_batch_free": (C.c_int32, [_P, _P]),
     "vx_gemv_batch_run_host": (C.c_int32, [_P, _P, C.c_size_t]),
+    "vx_host_pipeline_create": (C.c_int32, [_P, _P, C.c_size_t, C.POINTER(_P)]),
+    "vx_host_pipeline_run": (C.c_int32, [_P]),
+    "vx_host_pipeline_free": (C.c_int32, [_P]),
     "vx_gemm_tf32_scatter": (C.c_int32, [_P, _P, _P, _P, C.POINTER(VxShapes3), C.POINTER(_P), C.c_size_t]),
     "vx_peer_barrier": (C.c_int32, [_P, C.POINTER(_P), C.c_size_t, C.c_size_t]),
     "vx_group_unique_id": (C.c_int32, [_P]),

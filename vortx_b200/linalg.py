@@ -350,9 +350,11 @@ class HostStages:
     Each stage is a dict: batch (GemvBatch) and optionally up = (device_ptr, host_ptr, bytes), down =
     (host_ptr, host_pitch, device_ptr, device_pitch, width_bytes, rows), barrier = (flag pointers of every rank,
     rank): a peer barrier between the list and the copy down.  Host pointers should be page-locked.  Pointers
-    are captured at construction; `run()` returns when every stage's results are in host memory."""
+    are captured at construction; `run()` returns when every stage's results are in host memory.  With
+    `recorded=True` the step is recorded once as a CUDA graph (vx_host_pipeline: the step runs once at
+    construction, the host buffers must be page-locked) and `run()` replays it with one runtime call."""
 
-    def __init__(self, backend: Backend, stages):
+    def __init__(self, backend: Backend, stages, recorded: bool = False):
         n = len(stages)
         self._arr = (_lib.VxHostStage * max(1, n))()
         self._keep = []
@@ -374,9 +376,29 @@ class HostStages:
                 self._keep.append(fa)
                 a.barrier_flags, a.world, a.rank = fa, len(flags), rank
         self.backend, self.n = backend, n
+        self._pipe = None
+        if recorded:
+            h = C.c_void_p()
+            _lib.check(_lib.load().vx_host_pipeline_create(backend._ctx, self._arr, n, C.byref(h)))
+            self._pipe = h
 
     def run(self) -> None:
-        _lib.check(_lib.load().vx_gemv_batch_run_host(self.backend._ctx, self._arr, self.n))
+        lib = _lib.load()
+        if self._pipe:
+            _lib.check(lib.vx_host_pipeline_run(self._pipe))
+        else:
+            _lib.check(lib.vx_gemv_batch_run_host(self.backend._ctx, self._arr, self.n))
+
+    def free(self) -> None:
+        if self._pipe and self.backend._ctx:
+            _lib.check(_lib.load().vx_host_pipeline_free(self._pipe))
+        self._pipe = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
 
 
 def _ptr_len(t):
