@@ -906,6 +906,9 @@ PROFILE_CASES = {
     # not for ncu: the chained list with the kernel's own %globaltimer stamps (a library built with
     # `python -m vortx_b200.build --timeline`); runs on 1 GPU or, under torchrun, on N
     "gemv_chain_timeline": ("chain_timeline", ROWS, COLS, "Q4_0", LAYERS),
+    # the same stamps for single launches back to back (12 weight copies in one CUDA graph), one GPU
+    "gemv_single_timeline_q4_0_8192x8192": ("single_timeline", 8192, 8192, "Q4_0", 12),
+    "gemv_single_timeline_q8_0_4096x4096": ("single_timeline", 4096, 4096, "Q8_0", 24),
 }
 
 
@@ -998,6 +1001,69 @@ def run_chain_timeline():
     os._exit(0)   # past the final barrier with nothing in flight; no communicator teardown
 
 
+def run_single_timeline(rows: int, cols: int, what: str, copies: int):
+    """Where a single-launch GEMV's time goes: `copies` launches (one weight copy each) in one CUDA graph, every
+    launch stamping its own buffer; times are relative to the last store of the launch before."""
+    import torch
+    import vortx_b200 as vb
+    from vortx_b200 import _lib, synth
+    lib = _lib.load()
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    be = vb.Backend(0, stream=stream.cuda_stream)
+    qt = vb.Q4_0 if what == "Q4_0" else vb.Q8_0
+    blocks = vb.quantize(qt, synth.normal_matrix(rows, cols, seed=0))
+    ws = [vb.QuantizedMatrix(be, qt, blocks, rows, cols) for _ in range(copies)]
+    x = torch.randn(1, cols, device="cuda")
+    y = torch.empty(1, rows, device="cuda")
+    max_blocks = 4 * torch.cuda.get_device_properties(0).multi_processor_count
+    bufs = [torch.zeros(max_blocks * 8, dtype=torch.int64, device="cuda") for _ in range(copies)]
+    for pdl in (1, 0):
+        be.set_option("gemv.pdl", pdl)
+
+        def fn():
+            for i, w in enumerate(ws):
+                be.set_option("debug.timeline_ptr", bufs[i].data_ptr())
+                _lib.check(lib.vx_gemv_q_rows(be._ctx, w._h, 0, rows, x.data_ptr(), cols, y.data_ptr(), rows, 1))
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        for _ in range(4):
+            g.replay()
+        torch.cuda.synchronize()
+        for bf in bufs:
+            bf.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        g.replay()
+        b.record(stream)
+        torch.cuda.synchronize()
+        per = a.elapsed_time(b) * 1e3 / copies
+        d = [bf.cpu().numpy().reshape(max_blocks, 8).astype(np.float64) for bf in bufs]
+        d = [t[t[:, 7] > 0] for t in d]
+        if d[0].shape[0] == 0:
+            print("no stamps — the library was not built with `python -m vortx_b200.build --timeline`", flush=True)
+            break
+        table = []
+        for l in range(3, copies - 1):
+            end = d[l - 1][:, 5].max()
+            t = d[l]
+            table.append([np.median(t[:, 7]) - end, np.median(t[:, 0]) - end, np.median(t[:, 2]) - end,
+                          np.median(t[:, 3]) - end, np.median(t[:, 4]) - end, t[:, 5].min() - end, t[:, 5].max() - end])
+        m = np.median(np.array(table), axis=0) / 1e3
+        print(f"{what} {rows} x {cols}, programmatic dependent launch {'on' if pdl else 'off'}: {per:.2f} us per launch, "
+              f"{d[4].shape[0]} thread blocks; microseconds after the last store of the launch before (median block, "
+              f"median launch): block starts {m[0]:.2f}, past griddepcontrol.wait {m[1]:.2f}, x converted {m[2]:.2f}, "
+              f"first tile present {m[3]:.2f}, last tile computed {m[4]:.2f}, first block's last store {m[5]:.2f}, "
+              f"last block's last store {m[6]:.2f}", flush=True)
+    g = None
+    for w in ws:
+        w.free()
+    be.synchronize()
+
+
 def run_profile_case(name: str):
     """A handful of plain launches of one kernel on a small footprint, for `ncu` captures.
     Prints what it ran; nothing printed here is a benchmark value."""
@@ -1007,6 +1073,8 @@ def run_profile_case(name: str):
     kind, rows, cols, what, copies = PROFILE_CASES[name]
     if kind == "chain_timeline":
         return run_chain_timeline()
+    if kind == "single_timeline":
+        return run_single_timeline(rows, cols, what, copies)
     be = vb.Backend(0)
     lib = _lib.load()
     rng = np.random.Generator(np.random.Philox(1))

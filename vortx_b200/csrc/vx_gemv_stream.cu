@@ -150,7 +150,7 @@ __device__ __forceinline__ uint32_t first_tile(uint32_t op, uint32_t tiles) {
 // Timeline build (nvcc -DVX_TIMELINE, `python -m vortx_b200.build --timeline`): thread 0 of the consumers and
 // lane 0 of the epilogue warp stamp %globaltimer (nanoseconds; it ticks every 256 ns here) per list entry:
 //   [0] entry begins  [1] after the block's wait for x (the block-wait form; else = [0])  [2] x read (the threads'
-//   own waits included) and converted  [3] first tile present
+//   own waits included) and converted  [3] first tile present  ([7] of entry 0: the thread block starts)
 //   [4] last tile computed  [5] rows of the last tile stored  [6] rows of the first tile stored
 // The product build carries none of this.
 #ifdef VX_TIMELINE
@@ -187,6 +187,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * 16 + 2 * kRedBufs);
 
     const uint32_t tid = threadIdx.x;
+    VX_TL(if (p.timeline && tid == 0) p.timeline[(size_t)blockIdx.x * p.n_ops * 8 + 7] = gtime());
     // Programmatic dependent launch: let the next kernel in the stream start its own prologue
     // as soon as this grid's CTAs are all under way.  Nothing here depends on that kernel.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -689,6 +690,9 @@ void fill_common(StreamParams* p, const StreamConfig& c, uint32_t nchunks, uint3
     p->q_stage_bytes = c.q_stage;
     p->status = ctx->d_status;
     p->wait_cycles = vx::wait_cycles(ctx);
+#ifdef VX_TIMELINE
+    p->timeline = reinterpret_cast<unsigned long long*>(vx::option(ctx, "debug.timeline_ptr", 0));
+#endif
 }
 
 // Which rows of a producing entry a reading entry waits for, and whether that covers every thread block.
