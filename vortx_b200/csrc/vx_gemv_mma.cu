@@ -22,14 +22,17 @@
 //     (256 for the usual shapes): |X| < 2^22 for Q4_0 and < 2^19 for Q8_0, so that a block's recombined
 //     sum still fits 32 bits.  The slice sums are scaled by the slice's factor in f32.
 //   * The main kernel is persistent, one CTA per SM: producer thread (one tiled TMA load per 16-row tile,
-//     128-byte swizzle so that fragment loads hit 32 different banks), 8 consumer warps, epilogue warp.
+//     128-byte swizzle so that fragment loads hit 32 different banks) and 8 consumer warps.
 //     A CTA owns whole rows.  The planes (25 bytes per column, 9 in the SINGLE form) must sit in its shared
 //     memory, so wide matrices are walked in PHASES: the planes of one column part are loaded, the part is
 //     streamed for all the CTA's row tiles (at most `sg_units` of them at a time), their sums wait in shared
 //     memory, the next part's planes replace the first's, and so on; the last phase writes y.  No sums
 //     cross CTAs.  The 8 warps of a CTA split a tile's columns further and keep their B fragments in
 //     registers while they walk up to 4 row tiles.
-//   * Partial sums meet in shared memory: the 8 warps of a CTA and the phases, both in a fixed order.
+//   * Partial sums meet in shared memory: every consumer thread leaves its four sums of a row tile there (its
+//     own 16 bytes, no synchronisation per tile); at the end of a pass over the set's row tiles the warps add
+//     them up, the 8 warps of a CTA and then the phases, both in a fixed order.  (A hand-off of every tile to an
+//     epilogue warp through barriers cost a fifth of a tile visit.)
 // Measured on B200 while building this (they shaped the design): an SM completes about one untiled bulk
 // copy per 75 cycles whatever its size, and one thread issues one per 450, so row-by-row copies of 1 KB
 // top out near 3 TB/s (hence one tiled load per tile); mma.sync m16n8k32 s8 has 20 cycles latency and a
@@ -54,9 +57,8 @@ using namespace sm100;
 
 constexpr int kVecs = 8;                 // vectors per pass (the MMA's n)
 constexpr int kUnitRows = 16;            // rows per tile (the MMA's m)
-constexpr int kMaxRedSlots = 8;          // hand-off slots between the consumer warps and the epilogue warp
-constexpr int kRedStride = 20;           // floats between vectors in a reduction slot (16 rows + padding)
-constexpr int kRedWarp = kVecs * kRedStride;
+constexpr uint32_t kAccUnit = 8 * 32 * 16;   // bytes of partial sums per row tile: a float4 per consumer thread
+constexpr uint32_t kPartUnit = 32 * 16;      // bytes of sums between phases per row tile: a float4 per lane
 enum { SINGLE = 0, FULL = 1 };
 // Consumer warps per CTA.  (16 warps of 4 blocks each measured no faster than 8 warps of 8 in the FULL form:
 // 2.65 against 2.85 TB/s on 28672 x 4096 Q4_0.)
@@ -75,7 +77,7 @@ struct MmaParams {
     uint32_t phases;              // column tiles of 32 NBW kWarps columns, walked one after the other
     uint32_t slot_bytes;          // shared memory per slot of planes (a column tile's planes, then its slice factors)
     uint32_t sg_units;            // row tiles whose sums wait in shared memory between phases
-    uint32_t stages, red_slots, stage_bytes, s_off;
+    uint32_t stages, stage_bytes, s_off;
     uint32_t ring_off;            // offset of the ring in shared memory (1024-byte aligned: the swizzle works on address bits)
     const uint8_t* planes;        // [nb][block_planes(MODE)]
     const float* sx;              // [slices][kVecs]: per column, the factor its slice sums are scaled by
@@ -212,7 +214,7 @@ __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ 
 
 // ------------------------------------------------------------------------ main kernel ----
 // Work of a CTA: row tiles [u0, u1), walked `sg_units` at a time; per such set every phase (column tile),
-// and inside a phase the set's row tiles.  Producer, consumers and epilogue walk the same order.
+// and inside a phase the set's row tiles.  Producer and consumers walk the same order.
 __device__ __forceinline__ void my_units(const MmaParams& p, uint32_t* u0, uint32_t* u1) {
     const uint32_t units = p.nrows16 / kUnitRows;
     *u0 = (uint32_t)((uint64_t)units * blockIdx.x / gridDim.x);
@@ -220,7 +222,7 @@ __device__ __forceinline__ void my_units(const MmaParams& p, uint32_t* u0, uint3
 }
 
 template <int QT, int NBW, int MODE>
-__global__ void __launch_bounds__(kWarps * 32 + 64, 1)
+__global__ void __launch_bounds__(kWarps * 32 + 32, 1)
 gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUtensorMap map_q,
                 const __grid_constant__ CUtensorMap map_s) {
     constexpr int QB = QT == 1 ? 16 : 32;   // bytes of quants per block
@@ -234,18 +236,16 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
     extern __shared__ __align__(128) uint8_t smem_raw[];
     // the swizzle of the tiled copies works on shared-memory address bits: start the layout on a 1024-byte boundary
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-    // [2 slots of planes + slice factors][ring][reduction slots][sums between phases][barriers]
+    // [2 slots of planes + slice factors][ring][partial sums of the set's row tiles][sums between phases][barriers]
     uint8_t* ring = smem + p.ring_off;
-    float* red = reinterpret_cast<float*>(ring + (size_t)p.stages * p.stage_bytes);   // [red_slots][kWarps][kRedWarp]
-    float* s_part = red + p.red_slots * kWarps * kRedWarp;                             // [sg_units][kVecs][16], if phases > 1
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_part + (p.phases > 1 ? p.sg_units * kVecs * kUnitRows : 0));
+    float4* s_acc = reinterpret_cast<float4*>(ring + (size_t)p.stages * p.stage_bytes);   // [sg_units][kWarps][32]
+    float4* s_part = s_acc + (size_t)p.sg_units * kWarps * 32;                             // [sg_units][32], if phases > 1
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_part + (p.phases > 1 ? (size_t)p.sg_units * 32 : 0));
     const uint32_t bar0 = smem_addr(bars);
     auto full = [&](uint32_t s) { return bar0 + 8u * s; };
     auto empty = [&](uint32_t s) { return bar0 + 8u * (kMaxStages + s); };
-    auto red_full = [&](uint32_t b) { return bar0 + 8u * (2 * kMaxStages + b); };
-    auto red_empty = [&](uint32_t b) { return bar0 + 8u * (2 * kMaxStages + kMaxRedSlots + b); };
-    auto planes_bar = [&](uint32_t slot) { return bar0 + 8u * (2 * kMaxStages + 2 * kMaxRedSlots + slot); };
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 2 * kMaxRedSlots + 2);
+    auto planes_bar = [&](uint32_t slot) { return bar0 + 8u * (2 * kMaxStages + slot); };
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 2);
 
     const uint32_t tid = threadIdx.x;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -254,10 +254,6 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
         for (uint32_t s = 0; s < p.stages; ++s) {
             mbar_init(full(s), 1);
             mbar_init(empty(s), kWarps);
-        }
-        for (uint32_t b = 0; b < p.red_slots; ++b) {
-            mbar_init(red_full(b), kWarps);
-            mbar_init(red_empty(b), 1);      // used per half of the slots: [0] and [red_slots / 2]
         }
         mbar_init(planes_bar(0), 1);
         mbar_init(planes_bar(1), 1);
@@ -268,66 +264,6 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
     uint32_t u0, u1;
     my_units(p, &u0, &u1);
 
-    if (tid >= kWarps * 32 + 32) {
-        // ------------------------------------------------------------ epilogue warp ----
-        // Lanes 0..15 take the tile's 16 rows for one vector, lanes 16..31 for the next one.
-        const uint32_t lane = tid & 31, r = lane & 15, half = lane >> 4;
-        constexpr int NV = MODE == FULL ? kVecs / 2 : 1;     // vectors per lane
-        asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the kernel before the pre-pass
-        uint32_t b = 0, b_par = 0;                           // hand-off slot and the parity of its use
-        const uint32_t half_slots = p.red_slots / 2;
-        for (uint32_t sg0 = u0; sg0 < u1; sg0 += p.sg_units) {
-            const uint32_t sg1 = min(sg0 + p.sg_units, u1);
-            for (uint32_t ph = 0; ph < p.phases; ++ph) {
-                for (uint32_t u = sg0; u < sg1; ++u) {
-                    if (!mbar_wait(red_full(b), b_par, abort_flag)) report(p.status, 44);
-                    const float* slot = red + (size_t)b * kWarps * kRedWarp;
-                    const uint32_t row = u * kUnitRows + r;
-                    float sum[NV];
-#pragma unroll
-                    for (int i = 0; i < NV; ++i) {
-                        const uint32_t v = 2 * i + half;
-                        float s = 0.0f;
-                        if (MODE == FULL) {
-#pragma unroll
-                            for (int w = 0; w < kWarps; ++w) s += slot[w * kRedWarp + v * kRedStride + r];
-                        } else if (v < 2) {
-                            // the vector's three planes, each already weighted by 65536 / 256 / 1: high plane last
-#pragma unroll
-                            for (int pl = 2; pl >= 0; --pl) {
-                                float sp = 0.0f;
-#pragma unroll
-                                for (int w = 0; w < kWarps; ++w) sp += slot[w * kRedWarp + (3 * v + pl) * kRedStride + r];
-                                s += sp;
-                            }
-                        }
-                        sum[i] = s;
-                    }
-                    __syncwarp();
-                    // the slots are given back half of them at a time (one wait per half for the consumers)
-                    ++b;
-                    if (b == half_slots) {
-                        if (lane == 0) mbar_arrive(red_empty(0));
-                    } else if (b == p.red_slots) {
-                        if (lane == 0) mbar_arrive(red_empty(half_slots));
-                        b = 0;
-                        b_par ^= 1u;
-                    }
-                    // the phases' sums are added in phase order; only this warp touches s_part
-                    float* part = s_part + (size_t)(u - sg0) * (kVecs * kUnitRows);
-#pragma unroll
-                    for (int i = 0; i < NV; ++i) {
-                        const uint32_t v = 2 * i + half;
-                        float s = sum[i];
-                        if (ph > 0) s += part[v * kUnitRows + r];
-                        if (ph + 1 < p.phases) part[v * kUnitRows + r] = s;
-                        else if (v < p.batch && row < p.nrows) p.y[(size_t)v * p.y_stride + row] = s;
-                    }
-                }
-            }
-        }
-        return;
-    }
     if (tid >= kWarps * 32) {
         // ------------------------------------------------------------ producer warp ----
         // One thread, two tiled TMA loads per stage: the tile's quants as a box of 128 bytes x 16 rows x the
@@ -381,23 +317,25 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0 && u0 < u1) load_planes(0, 0);
 
-    uint32_t k = 0, n = 0;              // tile visits, phases walked
+    uint32_t n = 0;                     // passes walked (a set of row tiles x a phase)
     uint32_t s = 0, s_par = 0;          // ring stage and the parity of its use
-    uint32_t b = 0, b_use = 0;          // hand-off slot and how often it has been used before
-    const uint32_t half_slots = p.red_slots / 2;
     for (uint32_t sg0 = u0; sg0 < u1; sg0 += p.sg_units) {
         const uint32_t sg1 = min(sg0 + p.sg_units, u1);
         for (uint32_t ph = 0; ph < p.phases; ++ph, ++n) {
-            const uint32_t slot = n & 1;
+            // Every consumer warp has left the pass before: its planes' slot may take the planes of the next
+            // phase, and the partial sums it left in shared memory have been added up.
+            if (n > 0) asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+            uint32_t slot = 0;
             if (p.phases > 1) {
-                // once every consumer warp has left the phase before, its slot takes the planes of the next one
-                asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+                slot = n & 1;
                 if (tid == 0) {
                     if (ph + 1 < p.phases) load_planes(ph + 1, slot ^ 1);
                     else if (sg1 < u1) load_planes(0, slot ^ 1);
                 }
+                if (!mbar_wait(planes_bar(slot), (n >> 1) & 1, abort_flag)) report(p.status, 45);
+            } else if (n == 0) {
+                if (!mbar_wait(planes_bar(0), 0, abort_flag)) report(p.status, 45);    // one phase: its planes stay
             }
-            if (!mbar_wait(planes_bar(slot), (n >> 1) & 1, abort_flag)) report(p.status, 45);
             const uint8_t* s_planes = smem + (size_t)slot * p.slot_bytes;
             const float2 sxv = *reinterpret_cast<const float2*>(s_planes + plane_bytes + (warp * kVecs + 2 * t) * 4);
             {
@@ -419,7 +357,7 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
                 }
 
 #pragma unroll 1
-                for (uint32_t u = sg0; u < sg1; ++u, ++k) {
+                for (uint32_t u = sg0; u < sg1; ++u) {
                     if (!mbar_wait(full(s), s_par, abort_flag)) report(p.status, 43);
                     const uint8_t* sq = ring + (size_t)s * p.stage_bytes;
                     const uint8_t* ss = sq + p.s_off;
@@ -497,19 +435,72 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
                         s = 0;
                         s_par ^= 1u;
                     }
-                    // this warp's columns of the tile are done: hand them to the epilogue warp
-                    if (b_use > 0 && (b == 0 || b == half_slots) && !mbar_wait(red_empty(b), (b_use - 1) & 1, abort_flag))
-                        report(p.status, 46);
-                    float* slot_out = red + ((size_t)b * kWarps + warp) * kRedWarp;
-                    slot_out[(2 * t) * kRedStride + g] = sxv.x * sacc[0];
-                    slot_out[(2 * t + 1) * kRedStride + g] = sxv.y * sacc[1];
-                    slot_out[(2 * t) * kRedStride + g + 8] = sxv.x * sacc[2];
-                    slot_out[(2 * t + 1) * kRedStride + g + 8] = sxv.y * sacc[3];
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(red_full(b));
-                    if (++b == p.red_slots) {
-                        b = 0;
-                        ++b_use;
+                    // this warp's columns of the tile are done: its sums wait in shared memory for the pass's end
+                    s_acc[((size_t)(u - sg0) * kWarps + warp) * 32 + lane] =
+                        make_float4(sxv.x * sacc[0], sxv.y * sacc[1], sxv.x * sacc[2], sxv.y * sacc[3]);
+                }
+            }
+            // ---- the pass's end: add the 8 warps' sums of every row tile (warp w takes tiles w, w + 8, ..), in
+            // warp order, then the phases in phase order; the last phase writes y
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+            const uint32_t n_units = sg1 - sg0;
+            const bool last_phase = ph + 1 == p.phases;
+            for (uint32_t uu = warp; uu < n_units; uu += kWarps) {
+                const float4* src = s_acc + (size_t)uu * kWarps * 32 + lane;
+                float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) {
+                    const float4 v = src[w * 32];
+                    r.x += v.x;
+                    r.y += v.y;
+                    r.z += v.z;
+                    r.w += v.w;
+                }
+                // r: rows g (x, y) and g + 8 (z, w) of the tile, MMA columns 2 t and 2 t + 1
+                uint32_t v0 = 2 * t, v1 = 2 * t + 1;
+                bool writer = true;
+                if constexpr (MODE == SINGLE) {
+                    // the columns are (vector, plane) pairs, column 3 v + pl: collect a vector's three planes from
+                    // the lanes of the quad and add them, each already weighted by 65536 / 256 / 1, high plane last
+                    const uint32_t base = lane & ~3u;
+                    float lo[6], hi[6];
+#pragma unroll
+                    for (int q = 0; q < 3; ++q) {
+                        lo[2 * q] = __shfl_sync(0xffffffffu, r.x, base + q);
+                        lo[2 * q + 1] = __shfl_sync(0xffffffffu, r.y, base + q);
+                        hi[2 * q] = __shfl_sync(0xffffffffu, r.z, base + q);
+                        hi[2 * q + 1] = __shfl_sync(0xffffffffu, r.w, base + q);
+                    }
+                    r.x = (lo[2] + lo[1]) + lo[0];
+                    r.y = (lo[5] + lo[4]) + lo[3];
+                    r.z = (hi[2] + hi[1]) + hi[0];
+                    r.w = (hi[5] + hi[4]) + hi[3];
+                    v0 = 0;
+                    v1 = 1;
+                    writer = t == 0;
+                }
+                if (writer) {
+                    if (p.phases > 1) {
+                        float4* part = s_part + (size_t)uu * 32 + lane;      // only this thread touches it
+                        if (ph > 0) {
+                            const float4 q = *part;
+                            r.x += q.x;
+                            r.y += q.y;
+                            r.z += q.z;
+                            r.w += q.w;
+                        }
+                        if (!last_phase) *part = r;
+                    }
+                    if (last_phase) {
+                        const uint32_t row_lo = (sg0 + uu) * kUnitRows + g, row_hi = row_lo + 8;
+                        if (v0 < p.batch) {
+                            if (row_lo < p.nrows) p.y[(size_t)v0 * p.y_stride + row_lo] = r.x;
+                            if (row_hi < p.nrows) p.y[(size_t)v0 * p.y_stride + row_hi] = r.z;
+                        }
+                        if (v1 < p.batch) {
+                            if (row_lo < p.nrows) p.y[(size_t)v1 * p.y_stride + row_lo] = r.y;
+                            if (row_hi < p.nrows) p.y[(size_t)v1 * p.y_stride + row_hi] = r.w;
+                        }
                     }
                 }
             }
@@ -518,7 +509,7 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
 }
 
 struct MmaConfig {
-    uint32_t phases, nbw, stages, red_slots, stage_bytes, s_off, ring_off, slot_bytes, sg_units;
+    uint32_t phases, nbw, stages, stage_bytes, s_off, ring_off, slot_bytes, sg_units;
     int mode;
     size_t smem;
 };
@@ -531,29 +522,37 @@ bool choose(const vx_qweights* w, uint32_t batch, uint32_t units_per_cta, uint32
     c->mode = batch <= 2 ? SINGLE : FULL;
     const uint32_t bp = block_planes(c->mode);
     if (nb % kWarps != 0) return false;
-    uint32_t nbw = nbw_max;
-    while (nbw > 1 && nb % (nbw * kWarps) != 0) nbw >>= 1;
-    const uint32_t kt_blocks = nbw * kWarps;
-    c->nbw = nbw;
-    c->phases = nb / kt_blocks;
-    c->s_off = kUnitRows * kt_blocks * qb;                  // a multiple of 2048
-    c->stage_bytes = (c->s_off + kUnitRows * kt_blocks * 2 + 1023) & ~1023u;
-    c->slot_bytes = (kt_blocks * bp + kWarps * kVecs * 4 + 127) & ~127u;
-    c->ring_off = ((c->phases > 1 ? 2 : 1) * c->slot_bytes + 1023) & ~1023u;
-    // Sums waiting between phases: 512 bytes per row tile; room for all of a CTA's tiles up to 48.
-    c->sg_units = c->phases > 1 ? std::min(std::max(units_per_cta, 1u), 48u) : 0x7FFFFFFFu;
-    const size_t part = c->phases > 1 ? (size_t)c->sg_units * kVecs * kUnitRows * 4 : 0;
-    // Hand-off slots: 8 when three ring stages still fit beside them (deeper rings measured no faster), else 4.
-    for (uint32_t red_slots : {(uint32_t)kMaxRedSlots, 4u}) {
-        const size_t tail = (size_t)red_slots * kWarps * kRedWarp * 4 + part + (2 * kMaxStages + 2 * kMaxRedSlots + 4) * 8;
-        const size_t fixed = (size_t)c->ring_off + tail + 1024;              // 1024: the dynamic window's own alignment
-        if (fixed + 2 * (size_t)c->stage_bytes > (size_t)227 * 1024) continue;
-        const uint32_t stages = (uint32_t)std::min<size_t>(max_stages, ((size_t)227 * 1024 - fixed) / c->stage_bytes);
-        if (stages < 3 && red_slots > 4) continue;
-        c->stages = stages;
-        c->red_slots = red_slots;
-        c->smem = fixed + (size_t)stages * c->stage_bytes;
-        return true;
+    units_per_cta = std::max(units_per_cta, 1u);
+    // Shared memory: the planes' slots, the ring, and per row tile of a set 4 KB of partial sums (+ 512 B of
+    // sums between phases).  Wanted: three ring stages (deeper rings measured no faster) and room for all of
+    // a CTA's row tiles, or at least 8, in one set (every further set walks the phases again); column tiles
+    // of fewer blocks per warp make that room when the widest ones do not.
+    const size_t limit = (size_t)227 * 1024 - 1024;         // 1024: the dynamic window's own alignment
+    for (int pass = 0; pass < 2; ++pass) {
+        for (uint32_t nbw = nbw_max; nbw >= 1; nbw >>= 1) {
+            if (nb % (nbw * kWarps) != 0) continue;
+            const uint32_t kt_blocks = nbw * kWarps;
+            c->nbw = nbw;
+            c->phases = nb / kt_blocks;
+            c->s_off = kUnitRows * kt_blocks * qb;              // a multiple of 2048
+            c->stage_bytes = (c->s_off + kUnitRows * kt_blocks * 2 + 1023) & ~1023u;
+            c->slot_bytes = (kt_blocks * bp + kWarps * kVecs * 4 + 127) & ~127u;
+            c->ring_off = ((c->phases > 1 ? 2 : 1) * c->slot_bytes + 1023) & ~1023u;
+            const size_t per_unit = kAccUnit + (c->phases > 1 ? kPartUnit : 0);
+            const size_t bars = (2 * kMaxStages + 4) * 8;
+            const uint32_t want_stages = pass == 0 ? 3 : 2;
+            const size_t fixed = c->ring_off + (size_t)want_stages * c->stage_bytes + bars;
+            if (fixed + per_unit > limit) continue;
+            const uint32_t fit = (uint32_t)std::min<size_t>((limit - fixed) / per_unit, 0x10000);
+            const uint32_t sg = std::min(units_per_cta, fit);
+            if (pass == 0 && sg < std::min(units_per_cta, 8u)) continue;
+            c->sg_units = sg;
+            const size_t rest = limit - c->ring_off - bars - (size_t)sg * per_unit;
+            c->stages = (uint32_t)std::min<size_t>(std::min<uint32_t>(max_stages, 4), rest / c->stage_bytes);
+            if (c->stages < 2) continue;
+            c->smem = c->ring_off + (size_t)c->stages * c->stage_bytes + (size_t)sg * per_unit + bars + 1024;
+            return true;
+        }
     }
     return false;
 }
@@ -617,7 +616,7 @@ vx_status launch_main(vx_context* ctx, const MmaParams& p, const CUtensorMap& mq
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kWarps * 32 + 64);
+    cfg.blockDim = dim3(kWarps * 32 + 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -710,7 +709,6 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
     p.sg_units = c.sg_units;
     p.slot_bytes = c.slot_bytes;
     p.stages = c.stages;
-    p.red_slots = c.red_slots;
     p.stage_bytes = c.stage_bytes;
     p.s_off = c.s_off;
     p.ring_off = c.ring_off;
