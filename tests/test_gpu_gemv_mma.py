@@ -118,7 +118,7 @@ def test_more_row_tiles_per_block_than_wait_between_phases(backend, oracle, batc
     try:
         got, launches = _run(backend, qm, x)
     finally:
-        backend.set_option("gemv.mma_nbw", 8)
+        backend.set_option("gemv.mma_nbw", -1)
     assert launches == 2
     _check(got, y64, absdot)
     qm.free()

@@ -548,7 +548,7 @@ bool choose(const vx_qweights* w, uint32_t batch, uint32_t units_per_cta, uint32
             if (pass == 0 && sg < std::min(units_per_cta, 8u)) continue;
             c->sg_units = sg;
             const size_t rest = limit - c->ring_off - bars - (size_t)sg * per_unit;
-            c->stages = (uint32_t)std::min<size_t>(std::min<uint32_t>(max_stages, 4), rest / c->stage_bytes);
+            c->stages = (uint32_t)std::min<size_t>(std::min<uint32_t>(max_stages, 6), rest / c->stage_bytes);
             if (c->stages < 2) continue;
             c->smem = c->ring_off + (size_t)c->stages * c->stage_bytes + (size_t)sg * per_unit + bars + 1024;
             return true;
@@ -667,8 +667,14 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
     const uint32_t nrows16 = (nrows + kUnitRows - 1) / kUnitRows * kUnitRows;
     const uint32_t units = nrows16 / kUnitRows;
     const uint32_t grid = std::max(1u, std::min((uint32_t)ctx->sm_count, units));
-    if (batch < 1 || batch > (uint32_t)kVecs || !choose(w, batch, (units + grid - 1) / grid, (uint32_t)vx::option(ctx, "gemv.mma_nbw", 8),
-                (uint32_t)std::min<int64_t>(kMaxStages, vx::option(ctx, "gemv.mma_max_stages", kMaxStages)), &c))
+    // blocks per warp and column tile: 8, or what "gemv.mma_nbw" asks for (a power of two up to 8); Q8_0 with three
+    // and more vectors does better with 4 (7.2 against 8.2 us at 4096 x 4096: its stages are twice the bytes)
+    const int64_t nbw_opt = vx::option(ctx, "gemv.mma_nbw", 0);
+    uint32_t nbw_max = w->type == VX_Q8_0 && batch > 2 ? 4 : 8;
+    if (nbw_opt > 0) nbw_max = nbw_opt >= 8 ? 8 : nbw_opt >= 4 ? 4 : nbw_opt >= 2 ? 2 : 1;
+    if (batch < 1 || batch > (uint32_t)kVecs ||
+        !choose(w, batch, (units + grid - 1) / grid, nbw_max,
+                (uint32_t)std::min<int64_t>(kMaxStages, std::max<int64_t>(2, vx::option(ctx, "gemv.mma_max_stages", kMaxStages))), &c))
         return VX_OK;
     CUtensorMap map_q, map_s;
     if (!make_maps(w, c, &map_q, &map_s)) return VX_OK;
