@@ -783,6 +783,18 @@ def side_configs(be, lib, torch, stream):
                     us = time_graph(batch.launch, copies)
                     out[f"{name}_b1_list_hot_l2"] = {"us_per_gemv": us, "GB/s_weights_from_l2": byts / us / 1e3}
                     batch.free()
+            if b == 8 and len(ws) >= 8:
+                # eight of the matrices times the same eight vectors in one call (vx_gemv_q_multi): the planes of x
+                # are made once, one launch walks the matrices
+                ys8 = [torch.empty(b, rows, device="cuda") for _ in range(8)]
+                gemv = vb.Gemv()
+
+                def fn8():
+                    gemv.dispatch_multi(be, None, [t.data_ptr() for t in ys8], ws[:8], x.data_ptr(), batch=b,
+                                        x_stride=cols, y_stride=rows)
+                us = time_graph(fn8, 8)
+                out[f"{name}_b8_multi_of_8"] = {"us_per_matrix": us, "GB/s": byts / us / 1e3,
+                                                "frac_of_measured_hbm": byts / us / 1e3 / peak}
         for w in ws:
             w.free()
 

@@ -166,6 +166,13 @@ VX_API vx_status vx_gemv_q(vx_context* ctx, const vx_qweights* w, const float* x
 VX_API vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t row0, size_t nrows,
                                 const float* x, size_t x_stride, float* y, size_t y_stride,
                                 size_t batch);
+/* Several matrices times the SAME vectors in one pass (the Q, K and V, or the gate and up projections of a
+ * decoder layer; no reference counterpart): ys[i][v*y_stride + r] = sum_c ws[i][r, c] * x[v*x_stride + c].  The
+ * matrices share type and column count.  With a column count that is a multiple of 256 the vectors' fixed-point
+ * planes are made once and one persistent launch of the tensor-core batch kernel walks up to 8 matrices (also for
+ * one vector); otherwise it is one vx_gemv_q_rows per matrix.  Same arithmetic and results as the single calls. */
+VX_API vx_status vx_gemv_q_multi(vx_context* ctx, const vx_qweights* const* ws, size_t n_matrices, const float* x,
+                                 size_t x_stride, float* const* ys, size_t y_stride, size_t batch);
 
 /* ------------------------------------------------- several GPUs, one process each ---- */
 /* No reference counterpart (vortx knows one device ordinal, src/linalg/gemm.rs:353).

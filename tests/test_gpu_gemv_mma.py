@@ -104,10 +104,9 @@ def test_many_column_phases(backend, oracle, qt, batch):
 
 
 @pytest.mark.parametrize("batch", [2, 8])
-def test_more_row_tiles_per_block_than_wait_between_phases(backend, oracle, batch):
-    """120000 rows: 51 row tiles per thread block, more than the 48 whose sums wait in shared memory between two
-    phases, so a block walks its rows in two sets and re-walks the phases for each ("gemv.mma_nbw" = 1 makes two
-    phases out of 512 columns)."""
+def test_more_row_tiles_than_one_launch_takes(backend, oracle, batch):
+    """120000 rows: 51 row tiles per thread block, more than a launch gives a block (14): the matrix is walked
+    by four launches after one pre-pass ("gemv.mma_nbw" = 1 makes two phases out of 512 columns)."""
     rows, cols = 120000, 512
     w = synth.normal_matrix(rows, cols, seed=10)
     x = synth.normal_vectors(batch, cols, seed=11)
@@ -119,7 +118,9 @@ def test_more_row_tiles_per_block_than_wait_between_phases(backend, oracle, batc
         got, launches = _run(backend, qm, x)
     finally:
         backend.set_option("gemv.mma_nbw", -1)
-    assert launches == 2
+    import torch
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert launches == 1 + -(-(-(-rows // 16)) // (14 * sms))       # pre-pass + one launch per 14 row tiles per SM
     _check(got, y64, absdot)
     qm.free()
 
@@ -183,3 +184,62 @@ def test_batch_gemv_nan_inf_outliers(backend, oracle, qt):
     y64t, _ = oracle.gemv_f64(qt, blocks, rows, cols, x[6:7])
     assert np.abs(got[6] - y64t[0]).max() / np.abs(y64t[0]).max() <= 1e-3
     qm.free()
+
+
+@pytest.mark.parametrize("qt", [vb.Q8_0, vb.Q4_0])
+@pytest.mark.parametrize("batch", [1, 2, 8, 11])
+def test_several_matrices_share_the_vectors(backend, oracle, qt, batch):
+    """vx_gemv_q_multi: matrices of different row counts, one column count, times the same vectors: the planes
+    of x are made once per group of eight vectors and one launch walks the matrices.  Bit-identical to the single
+    calls through the same kernel."""
+    cols = 2048
+    rows_of = [300, 16, 1000, 77, 513, 64, 200, 31, 129, 48]          # ten: two launches per group of vectors
+    x = synth.normal_vectors(batch, cols, seed=40)
+    qms, refs = [], []
+    for i, rows in enumerate(rows_of):
+        blocks = oracle.quantize(qt, synth.normal_matrix(rows, cols, seed=50 + i))
+        qms.append(vb.QuantizedMatrix(backend, qt, blocks, rows, cols))
+        refs.append(oracle.gemv_f64(qt, blocks, rows, cols, x))
+    ys_stride = max(rows_of) + 5
+    xd = backend.init_buffer(x.ravel())
+    yds = [backend.init_buffer(np.full(batch * ys_stride, np.nan, np.float32)) for _ in rows_of]
+    before = backend.launch_count()
+    vb.Gemv().dispatch_multi(backend, None, yds, qms, xd, batch=batch, y_stride=ys_stride)
+    launches = backend.launch_count() - before
+    assert launches == 3 * -(-batch // 8)              # pre-pass + two main launches (8 + 2 matrices) per 8 vectors
+    backend.set_option("gemv.batch_mma", 1)            # the single calls through the same kernel, also for one vector
+    try:
+        for qm, yd, rows, (y64, absdot) in zip(qms, yds, rows_of, refs):
+            got = np.empty(batch * ys_stride, np.float32)
+            backend.slow_read_buffer(yd, got)
+            got = got.reshape(batch, ys_stride)
+            assert np.isnan(got[:, rows:]).all()           # nothing outside the rows is written
+            _check(got[:, :rows], y64, absdot)
+            single, _ = _run(backend, qm, x)
+            assert np.array_equal(single.view(np.uint32), got[:, :rows].view(np.uint32))
+    finally:
+        backend.set_option("gemv.batch_mma", -1)
+    for qm in qms:
+        qm.free()
+
+
+def test_several_matrices_fall_back_and_refuse(backend, oracle):
+    cols = 1056                                            # not a multiple of 256: one streaming call per matrix
+    x = synth.normal_vectors(3, cols, seed=41)
+    qms, refs = [], []
+    for i, rows in enumerate((40, 100)):
+        blocks = oracle.quantize(vb.Q4_0, synth.normal_matrix(rows, cols, seed=60 + i))
+        qms.append(vb.QuantizedMatrix(backend, vb.Q4_0, blocks, rows, cols))
+        refs.append(oracle.gemv_f64(vb.Q4_0, blocks, rows, cols, x))
+    xd = backend.init_buffer(x.ravel())
+    yds = [backend.init_buffer(np.zeros(3 * 100, np.float32)) for _ in qms]
+    vb.Gemv().dispatch_multi(backend, None, yds, qms, xd, batch=3)
+    for qm, yd, (y64, absdot) in zip(qms, yds, refs):
+        got = np.empty(300, np.float32)
+        backend.slow_read_buffer(yd, got)
+        _check(got.reshape(3, 100)[:, :qm.rows], y64, absdot)
+    other = vb.QuantizedMatrix(backend, vb.Q4_0, oracle.quantize(vb.Q4_0, synth.normal_matrix(8, 512, seed=1)), 8, 512)
+    with pytest.raises(vb.VortxError):                     # column counts differ
+        vb.Gemv().dispatch_multi(backend, None, [yds[0], yds[1]], [qms[0], other], xd, batch=1)
+    for qm in qms + [other]:
+        qm.free()

@@ -123,6 +123,7 @@ SIGNATURES = {
     "vx_gemv_q": (C.c_int32, [_P, _P, _P, C.c_size_t, _P, C.c_size_t, C.c_size_t]),
     "vx_gemv_q_rows": (C.c_int32, [_P, _P, C.c_size_t, C.c_size_t, _P, C.c_size_t, _P,
                                    C.c_size_t, C.c_size_t]),
+    "vx_gemv_q_multi": (C.c_int32, [_P, C.POINTER(_P), C.c_size_t, _P, C.c_size_t, C.POINTER(_P), C.c_size_t, C.c_size_t]),
     "vx_ipc_export": (C.c_int32, [_P, _P, _P]),
     "vx_ipc_import": (C.c_int32, [_P, _P, C.POINTER(_P)]),
     "vx_ipc_release": (C.c_int32, [_P, _P]),

@@ -47,6 +47,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <vector>
 
 #include "vx_internal.h"
 #include "vx_sm100.cuh"
@@ -67,13 +68,25 @@ constexpr int kMaxStages = 8;
 // bytes of planes per 32 columns: 3 (FULL) or 1 (SINGLE) x 256, then 8 x int32
 __host__ __device__ constexpr uint32_t block_planes(int mode) { return mode == FULL ? 800u : 288u; }
 
-struct MmaParams {
-    const uint8_t* quants;
-    const uint8_t* scales;        // f16 plane, in bytes
-    uint32_t row_bytes;           // quants per row, bytes
-    uint32_t nb;                  // blocks per row
-    uint64_t row0;
+constexpr int kMaxMats = 8;              // matrices one launch walks (they share the vectors)
+
+// The matrices of a launch: their row tiles are numbered through, matrix after matrix.
+struct MmaMat {
+    float* y;
+    uint32_t row0;                // first row of the slab inside its matrix
     uint32_t nrows;
+    uint32_t unit0;               // number of the slab's first row tile
+};
+
+struct MmaMaps {
+    CUtensorMap q[kMaxMats], s[kMaxMats];
+};
+
+struct MmaParams {
+    MmaMat mat[kMaxMats];
+    uint32_t n_mats;
+    uint32_t units;               // row tiles of all the matrices
+    uint32_t nb;                  // blocks per row
     uint32_t phases;              // column tiles of 32 NBW kWarps columns, walked one after the other
     uint32_t slot_bytes;          // shared memory per slot of planes (a column tile's planes, then its slice factors)
     uint32_t sg_units;            // row tiles whose sums wait in shared memory between phases
@@ -81,10 +94,8 @@ struct MmaParams {
     uint32_t ring_off;            // offset of the ring in shared memory (1024-byte aligned: the swizzle works on address bits)
     const uint8_t* planes;        // [nb][block_planes(MODE)]
     const float* sx;              // [slices][kVecs]: per column, the factor its slice sums are scaled by
-    float* y;
     uint64_t y_stride;
     uint32_t batch;
-    uint32_t nrows16;             // rows rounded up to whole tiles
     vx::DeviceStatus* status;
 };
 
@@ -216,15 +227,19 @@ __global__ void __launch_bounds__(256) xplanes_kernel(const float* __restrict__ 
 // Work of a CTA: row tiles [u0, u1), walked `sg_units` at a time; per such set every phase (column tile),
 // and inside a phase the set's row tiles.  Producer and consumers walk the same order.
 __device__ __forceinline__ void my_units(const MmaParams& p, uint32_t* u0, uint32_t* u1) {
-    const uint32_t units = p.nrows16 / kUnitRows;
-    *u0 = (uint32_t)((uint64_t)units * blockIdx.x / gridDim.x);
-    *u1 = (uint32_t)((uint64_t)units * (blockIdx.x + 1) / gridDim.x);
+    *u0 = (uint32_t)((uint64_t)p.units * blockIdx.x / gridDim.x);
+    *u1 = (uint32_t)((uint64_t)p.units * (blockIdx.x + 1) / gridDim.x);
+}
+// The matrix row tile `u` belongs to (tiles are numbered matrix after matrix).
+__device__ __forceinline__ uint32_t mat_of(const MmaParams& p, uint32_t u) {
+    uint32_t m = 0;
+    while (m + 1 < p.n_mats && u >= p.mat[m + 1].unit0) ++m;
+    return m;
 }
 
 template <int QT, int NBW, int MODE>
 __global__ void __launch_bounds__(kWarps * 32 + 32, 1)
-gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUtensorMap map_q,
-                const __grid_constant__ CUtensorMap map_s) {
+gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ MmaMaps maps) {
     constexpr int QB = QT == 1 ? 16 : 32;   // bytes of quants per block
     constexpr int NP = MODE == FULL ? 3 : 1;
     constexpr uint32_t kBP = block_planes(MODE);
@@ -272,8 +287,10 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
         // the matrix read as zeros.  (Row-by-row bulk copies of 1 KB do not keep up: an SM completes about
         // one bulk copy per 75 cycles whatever its size.)
         if (tid == kWarps * 32) {
-            tma_prefetch_desc(&map_q);
-            tma_prefetch_desc(&map_s);
+            for (uint32_t m = 0; m < p.n_mats; ++m) {
+                tma_prefetch_desc(&maps.q[m]);
+                tma_prefetch_desc(&maps.s[m]);
+            }
             uint32_t s = 0, use = 0;                         // ring stage and how often it has been filled before
             for (uint32_t sg0 = u0; sg0 < u1; sg0 += p.sg_units) {
                 const uint32_t sg1 = min(sg0 + p.sg_units, u1);
@@ -281,11 +298,12 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
                     const uint32_t blk0 = ph * kt_blocks;                  // first block of the tile in the row
                     for (uint32_t u = sg0; u < sg1; ++u) {
                         if (use > 0 && !mbar_wait(empty(s), (use - 1) & 1, abort_flag)) report(p.status, 41);
-                        const int32_t row = (int32_t)(p.row0 + (uint64_t)u * kUnitRows);
+                        const uint32_t m = mat_of(p, u);
+                        const int32_t row = (int32_t)(p.mat[m].row0 + (u - p.mat[m].unit0) * kUnitRows);
                         const uint32_t dst = smem_addr(ring + (size_t)s * p.stage_bytes);
                         mbar_arrive_expect_tx(full(s), kUnitRows * (q_tile_bytes + (S_SWZ ? 128u : kt_blocks * 2)));
-                        tma_load_3d(dst, &map_q, 0, row, (int32_t)(blk0 * QB / 128), full(s));
-                        tma_load_2d(dst + p.s_off, &map_s, (int32_t)(blk0 * 2), row, full(s));
+                        tma_load_3d(dst, &maps.q[m], 0, row, (int32_t)(blk0 * QB / 128), full(s));
+                        tma_load_2d(dst + p.s_off, &maps.s[m], (int32_t)(blk0 * 2), row, full(s));
                         if (++s == p.stages) {
                             s = 0;
                             ++use;
@@ -492,14 +510,15 @@ gemv_mma_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ CUt
                         if (!last_phase) *part = r;
                     }
                     if (last_phase) {
-                        const uint32_t row_lo = (sg0 + uu) * kUnitRows + g, row_hi = row_lo + 8;
+                        const MmaMat& mt = p.mat[mat_of(p, sg0 + uu)];
+                        const uint32_t row_lo = (sg0 + uu - mt.unit0) * kUnitRows + g, row_hi = row_lo + 8;
                         if (v0 < p.batch) {
-                            if (row_lo < p.nrows) p.y[(size_t)v0 * p.y_stride + row_lo] = r.x;
-                            if (row_hi < p.nrows) p.y[(size_t)v0 * p.y_stride + row_hi] = r.z;
+                            if (row_lo < mt.nrows) mt.y[(size_t)v0 * p.y_stride + row_lo] = r.x;
+                            if (row_hi < mt.nrows) mt.y[(size_t)v0 * p.y_stride + row_hi] = r.z;
                         }
                         if (v1 < p.batch) {
-                            if (row_lo < p.nrows) p.y[(size_t)v1 * p.y_stride + row_lo] = r.y;
-                            if (row_hi < p.nrows) p.y[(size_t)v1 * p.y_stride + row_hi] = r.w;
+                            if (row_lo < mt.nrows) mt.y[(size_t)v1 * p.y_stride + row_lo] = r.y;
+                            if (row_hi < mt.nrows) mt.y[(size_t)v1 * p.y_stride + row_hi] = r.w;
                         }
                     }
                 }
@@ -605,8 +624,7 @@ bool make_maps(const vx_qweights* w, const MmaConfig& c, CUtensorMap* map_q, CUt
 }
 
 template <int QT, int NBW, int MODE>
-vx_status launch_main(vx_context* ctx, const MmaParams& p, const CUtensorMap& mq, const CUtensorMap& ms, uint32_t grid,
-                      size_t smem) {
+vx_status launch_main(vx_context* ctx, const MmaParams& p, const MmaMaps& maps, uint32_t grid, size_t smem) {
     auto kernel = gemv_mma_kernel<QT, NBW, MODE>;
     static std::atomic<size_t> granted[64];
     const int dev = ctx->device & 63;
@@ -626,18 +644,17 @@ vx_status launch_main(vx_context* ctx, const MmaParams& p, const CUtensorMap& mq
     // the weights may have been written by a kernel of this stream (device quantiser): then no early start
     cfg.numAttrs = vx::option(ctx, "gemv.pdl", 1) != 0 && !ctx->weights_fresh ? 1 : 0;
     ctx->weights_fresh = false;
-    VX_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, mq, ms));
+    VX_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, maps));
     return VX_OK;
 }
 
 template <int QT, int MODE>
-vx_status launch_nbw(vx_context* ctx, uint32_t nbw, const MmaParams& p, const CUtensorMap& mq, const CUtensorMap& ms,
-                     uint32_t grid, size_t smem) {
+vx_status launch_nbw(vx_context* ctx, uint32_t nbw, const MmaParams& p, const MmaMaps& maps, uint32_t grid, size_t smem) {
     switch (nbw) {
-        case 8: return launch_main<QT, 8, MODE>(ctx, p, mq, ms, grid, smem);
-        case 4: return launch_main<QT, 4, MODE>(ctx, p, mq, ms, grid, smem);
-        case 2: return launch_main<QT, 2, MODE>(ctx, p, mq, ms, grid, smem);
-        default: return launch_main<QT, 1, MODE>(ctx, p, mq, ms, grid, smem);
+        case 8: return launch_main<QT, 8, MODE>(ctx, p, maps, grid, smem);
+        case 4: return launch_main<QT, 4, MODE>(ctx, p, maps, grid, smem);
+        case 2: return launch_main<QT, 2, MODE>(ctx, p, maps, grid, smem);
+        default: return launch_main<QT, 1, MODE>(ctx, p, maps, grid, smem);
     }
 }
 
@@ -658,26 +675,78 @@ vx_status ensure(vx_context* ctx, void** buf, size_t* have, size_t want) {
 
 namespace vx {
 
-// `batch` vectors (1..8) in one pass over rows [row0, row0 + nrows).  *eligible = false (nothing launched)
-// when the shape does not fit this kernel; the caller then takes the streaming kernel.
-vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows, const float* x,
-                          size_t x_stride, float* y, size_t y_stride, uint32_t batch, bool* eligible) {
+// `batch` vectors (1..8) times `n_mats` slabs (rows [row0[i], row0[i] + nrows[i]) of ws[i]; all of one type and
+// column count) in one pass: the vectors' planes are made once, then one persistent launch per kMaxMats slabs
+// walks their row tiles.  *eligible = false (nothing launched) when the shape does not fit this kernel; the
+// caller then takes the streaming kernel.
+vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* const* ws_in, const size_t* row0_in, const uint32_t* nrows_in,
+                          float* const* ys_in, size_t n_in, const float* x, size_t x_stride, size_t y_stride,
+                          uint32_t batch, bool* eligible) {
     *eligible = false;
+    if (n_in == 0) return VX_OK;
+    const vx_qweights* w = ws_in[0];
+    for (size_t i = 1; i < n_in; ++i)
+        if (ws_in[i]->type != w->type || ws_in[i]->cols != w->cols) return VX_OK;
     MmaConfig c;
-    const uint32_t nrows16 = (nrows + kUnitRows - 1) / kUnitRows * kUnitRows;
-    const uint32_t units = nrows16 / kUnitRows;
-    const uint32_t grid = std::max(1u, std::min((uint32_t)ctx->sm_count, units));
     // blocks per warp and column tile: 8, or what "gemv.mma_nbw" asks for (a power of two up to 8); Q8_0 with three
     // and more vectors does better with 4 (7.2 against 8.2 us at 4096 x 4096: its stages are twice the bytes)
     const int64_t nbw_opt = vx::option(ctx, "gemv.mma_nbw", 0);
     uint32_t nbw_max = w->type == VX_Q8_0 && batch > 2 ? 4 : 8;
     if (nbw_opt > 0) nbw_max = nbw_opt >= 8 ? 8 : nbw_opt >= 4 ? 4 : nbw_opt >= 2 ? 2 : 1;
-    if (batch < 1 || batch > (uint32_t)kVecs ||
-        !choose(w, batch, (units + grid - 1) / grid, nbw_max,
-                (uint32_t)std::min<int64_t>(kMaxStages, std::max<int64_t>(2, vx::option(ctx, "gemv.mma_max_stages", kMaxStages))), &c))
-        return VX_OK;
-    CUtensorMap map_q, map_s;
-    if (!make_maps(w, c, &map_q, &map_s)) return VX_OK;
+    const uint32_t max_stages =
+        (uint32_t)std::min<int64_t>(kMaxStages, std::max<int64_t>(2, vx::option(ctx, "gemv.mma_max_stages", kMaxStages)));
+    if (batch < 1 || batch > (uint32_t)kVecs) return VX_OK;
+    // How many row tiles per CTA fit one set (their sums wait in shared memory over the phases)?  A launch takes
+    // up to kMaxMats slabs, and no more of them than keep its CTAs within one set where that is possible:
+    // measured, a launch whose CTAs walk several sets is slower per matrix than several launches of one set each
+    // (28672 x 8192 Q4_0, 8 vectors: 38.8 us per matrix with eight matrices in one launch, 33.9 with two).
+    if (!choose(w, batch, 0x10000, nbw_max, max_stages, &c)) return VX_OK;
+    // (and no more than 14 row tiles per CTA and launch: with one or two vectors, whose planes leave room for far
+    // larger sets, 8192 x 8192 Q4_0 takes 8.7 us per matrix at 10 tiles per CTA and 10.6 us at 28)
+    const uint64_t set_units = (uint64_t)std::min(c.sg_units, 14u) * (uint32_t)ctx->sm_count;
+    // slabs taller than that are cut into pieces of that many row tiles, each a slab of its own
+    std::vector<const vx_qweights*> ws;
+    std::vector<size_t> row0;
+    std::vector<uint32_t> nrows;
+    std::vector<float*> ys;
+    for (size_t i = 0; i < n_in; ++i) {
+        const uint64_t piece_rows = set_units * kUnitRows;
+        for (uint64_t done = 0; done < nrows_in[i]; done += piece_rows) {
+            ws.push_back(ws_in[i]);
+            row0.push_back(row0_in[i] + (size_t)done);
+            nrows.push_back((uint32_t)std::min<uint64_t>(piece_rows, nrows_in[i] - done));
+            ys.push_back(ys_in[i] + done);
+        }
+    }
+    const size_t n_mats = ws.size();
+    if (n_mats == 0) return VX_OK;
+    std::vector<size_t> first;            // first slab of every launch
+    uint32_t most_units = 0;              // the most row tiles a CTA owns in any of the launches
+    {
+        uint64_t units = 0;
+        size_t count = 0;
+        for (size_t i = 0; i <= n_mats; ++i) {
+            const uint64_t u = i < n_mats ? (nrows[i] + kUnitRows - 1) / kUnitRows : 0;
+            if (i == n_mats || (count > 0 && (count == (size_t)kMaxMats || units + u > set_units))) {
+                const uint32_t grid = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count, units));
+                most_units = std::max(most_units, (uint32_t)((units + grid - 1) / grid));
+                units = 0;
+                count = 0;
+            }
+            if (i == n_mats) break;
+            if (count == 0) first.push_back(i);
+            units += u;
+            ++count;
+        }
+    }
+    if (!choose(w, batch, most_units, nbw_max, max_stages, &c)) return VX_OK;
+    // every slab's tensor maps first: nothing is launched unless all of them can be made
+    std::vector<MmaMaps> all_maps(first.size());
+    for (size_t l = 0; l < first.size(); ++l) {
+        const size_t end = l + 1 < first.size() ? first[l + 1] : n_mats;
+        for (size_t i = first[l]; i < end; ++i)
+            if (!make_maps(ws[i], c, &all_maps[l].q[i - first[l]], &all_maps[l].s[i - first[l]])) return VX_OK;
+    }
     const uint32_t nb = (uint32_t)w->blocks_per_row;
     const uint32_t slices = nb / c.nbw;
     const size_t planes_bytes = ((size_t)nb * block_planes(c.mode) + 255) & ~(size_t)255;
@@ -704,33 +773,41 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, ui
     VX_CUDA(cudaGetLastError());
     ctx->launches++;
 
-    MmaParams p{};
-    p.quants = w->d_quants;
-    p.scales = reinterpret_cast<const uint8_t*>(w->d_scales);
-    p.row_bytes = (uint32_t)w->quant_row_bytes;
-    p.nb = nb;
-    p.row0 = row0;
-    p.nrows = nrows;
-    p.phases = c.phases;
-    p.sg_units = c.sg_units;
-    p.slot_bytes = c.slot_bytes;
-    p.stages = c.stages;
-    p.stage_bytes = c.stage_bytes;
-    p.s_off = c.s_off;
-    p.ring_off = c.ring_off;
-    p.planes = planes;
-    p.sx = sx;
-    p.y = y;
-    p.y_stride = y_stride;
-    p.batch = batch;
-    p.nrows16 = nrows16;
-    p.status = ctx->d_status;
-    if (c.mode == FULL)
-        st = q4 ? launch_nbw<1, FULL>(ctx, c.nbw, p, map_q, map_s, grid, c.smem) : launch_nbw<0, FULL>(ctx, c.nbw, p, map_q, map_s, grid, c.smem);
-    else
-        st = q4 ? launch_nbw<1, SINGLE>(ctx, c.nbw, p, map_q, map_s, grid, c.smem) : launch_nbw<0, SINGLE>(ctx, c.nbw, p, map_q, map_s, grid, c.smem);
-    if (st != VX_OK) return st;
-    ctx->launches++;
+    for (size_t l = 0; l < first.size(); ++l) {
+        const size_t m0 = first[l];
+        MmaParams p{};
+        p.n_mats = (uint32_t)((l + 1 < first.size() ? first[l + 1] : n_mats) - m0);
+        uint32_t units = 0;
+        for (uint32_t i = 0; i < p.n_mats; ++i) {
+            p.mat[i].y = ys[m0 + i];
+            p.mat[i].row0 = (uint32_t)row0[m0 + i];
+            p.mat[i].nrows = nrows[m0 + i];
+            p.mat[i].unit0 = units;
+            units += (nrows[m0 + i] + kUnitRows - 1) / kUnitRows;
+        }
+        p.units = units;
+        p.nb = nb;
+        p.phases = c.phases;
+        p.sg_units = c.sg_units;
+        p.slot_bytes = c.slot_bytes;
+        p.stages = c.stages;
+        p.stage_bytes = c.stage_bytes;
+        p.s_off = c.s_off;
+        p.ring_off = c.ring_off;
+        p.planes = planes;
+        p.sx = sx;
+        p.y_stride = y_stride;
+        p.batch = batch;
+        p.status = ctx->d_status;
+        const uint32_t grid = std::max(1u, std::min((uint32_t)ctx->sm_count, units));
+        const MmaMaps& maps = all_maps[l];
+        if (c.mode == FULL)
+            st = q4 ? launch_nbw<1, FULL>(ctx, c.nbw, p, maps, grid, c.smem) : launch_nbw<0, FULL>(ctx, c.nbw, p, maps, grid, c.smem);
+        else
+            st = q4 ? launch_nbw<1, SINGLE>(ctx, c.nbw, p, maps, grid, c.smem) : launch_nbw<0, SINGLE>(ctx, c.nbw, p, maps, grid, c.smem);
+        if (st != VX_OK) return st;
+        ctx->launches++;
+    }
     ctx->status_dirty = true;
     *eligible = true;
     return VX_OK;

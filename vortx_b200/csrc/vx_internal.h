@@ -153,9 +153,11 @@ vx_status launch_gemv_stream(vx_context* ctx, const vx_qweights* w, size_t row0,
                              const Exchange* xch, bool* eligible, uint32_t batch = 1, size_t x_stride = 0,
                              size_t y_stride = 0);
 
-// Tensor-core batch GEMV (vx_gemv_mma.cu): up to 8 vectors per pass over the weights.  *eligible = false
-// (nothing launched) when the column count does not fit it.
-vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* w, size_t row0, uint32_t nrows, const float* x,
-                          size_t x_stride, float* y, size_t y_stride, uint32_t batch, bool* eligible);
+// Tensor-core batch GEMV (vx_gemv_mma.cu): up to 8 vectors per pass over the weights of `n_mats` slabs (rows
+// [row0[i], row0[i] + nrows[i]) of ws[i] into ys[i]; one type, one column count) that share the vectors.
+// *eligible = false (nothing launched) when the shape does not fit it.
+vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* const* ws, const size_t* row0, const uint32_t* nrows,
+                          float* const* ys, size_t n_mats, const float* x, size_t x_stride, size_t y_stride,
+                          uint32_t batch, bool* eligible);
 
 }  // namespace vx

@@ -683,6 +683,61 @@ vx_status vx_dequantize(vx_context* ctx, const vx_qweights* w, float* device_out
     return VX_OK;
 }
 
+vx_status vx_gemv_q_multi(vx_context* ctx, const vx_qweights* const* ws, size_t n, const float* x, size_t x_stride,
+                          float* const* ys, size_t y_stride, size_t batch) {
+    VX_REQUIRE(ctx, VX_ERR_INVALID_ARGUMENT, "vx_gemv_q_multi: null context");
+    if (n == 0 || batch == 0) return VX_OK;
+    VX_REQUIRE(ws && ys && x, VX_ERR_INVALID_ARGUMENT, "vx_gemv_q_multi: null argument");
+    size_t most_rows = 0;
+    for (size_t i = 0; i < n; ++i) {
+        VX_REQUIRE(ws[i] && ys[i], VX_ERR_INVALID_ARGUMENT, "vx_gemv_q_multi: matrix %zu or its y is null", i);
+        VX_REQUIRE(ws[i]->device == ctx->device, VX_ERR_INVALID_ARGUMENT, "weights %zu live on device %d, context on %d", i,
+                   ws[i]->device, ctx->device);
+        VX_REQUIRE(ws[i]->type == ws[0]->type && ws[i]->cols == ws[0]->cols, VX_ERR_SHAPE,
+                   "matrix %zu (type %d, %zu columns) does not match matrix 0 (type %d, %zu columns)", i, (int)ws[i]->type,
+                   ws[i]->cols, (int)ws[0]->type, ws[0]->cols);
+        most_rows = std::max(most_rows, ws[i]->rows);
+    }
+    VX_REQUIRE(batch == 1 || (x_stride >= ws[0]->cols && y_stride >= most_rows), VX_ERR_INVALID_ARGUMENT,
+               "batch strides (x %zu, y %zu) shorter than the vectors (%zu, %zu)", x_stride, y_stride, ws[0]->cols, most_rows);
+    vx::DeviceGuard guard(ctx->device);
+    if (vx::option(ctx, "gemv.variant", 2) == 2 && vx::option(ctx, "gemv.batch_mma", -1) != 0) {
+        std::vector<size_t> row0(n, 0);
+        std::vector<uint32_t> nrows(n);
+        bool any = false;
+        for (size_t i = 0; i < n; ++i) {
+            nrows[i] = (uint32_t)ws[i]->rows;
+            any = any || nrows[i] != 0;
+        }
+        if (!any) return VX_OK;
+        size_t v = 0;
+        while (v < batch) {
+            const uint32_t take = (uint32_t)std::min<size_t>(8, batch - v);
+            std::vector<float*> yv(n);
+            for (size_t i = 0; i < n; ++i) yv[i] = ys[i] + v * y_stride;
+            bool eligible = false;
+            vx_status st = vx::launch_gemv_mma(ctx, ws, row0.data(), nrows.data(), yv.data(), n, x + v * x_stride, x_stride,
+                                               y_stride, take, &eligible);
+            if (st != VX_OK) return st;
+            if (!eligible) break;
+            v += take;
+        }
+        if (v == batch) return VX_OK;
+        x += v * x_stride;
+        batch -= v;
+        for (size_t i = 0; i < n; ++i) {
+            vx_status st = vx_gemv_q_rows(ctx, ws[i], 0, ws[i]->rows, x, x_stride, ys[i] + v * y_stride, y_stride, batch);
+            if (st != VX_OK) return st;
+        }
+        return VX_OK;
+    }
+    for (size_t i = 0; i < n; ++i) {
+        vx_status st = vx_gemv_q_rows(ctx, ws[i], 0, ws[i]->rows, x, x_stride, ys[i], y_stride, batch);
+        if (st != VX_OK) return st;
+    }
+    return VX_OK;
+}
+
 vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t row0, size_t nrows,
                          const float* x, size_t x_stride, float* y, size_t y_stride, size_t batch) {
     VX_REQUIRE(ctx && w, VX_ERR_INVALID_ARGUMENT, "vx_gemv_q: null context or weights");
@@ -709,8 +764,10 @@ vx_status vx_gemv_q_rows(vx_context* ctx, const vx_qweights* w, size_t row0, siz
             while (v < batch) {
                 const uint32_t take = (uint32_t)std::min<size_t>(8, batch - v);
                 bool eligible = false;
-                vx_status st = vx::launch_gemv_mma(ctx, w, row0, (uint32_t)nrows, x + v * x_stride, x_stride,
-                                                   y + v * y_stride, y_stride, take, &eligible);
+                const uint32_t nr = (uint32_t)nrows;
+                float* yv = y + v * y_stride;
+                vx_status st = vx::launch_gemv_mma(ctx, &w, &row0, &nr, &yv, 1, x + v * x_stride, x_stride, y_stride,
+                                                   take, &eligible);
                 if (st != VX_OK) return st;
                 if (!eligible) break;
                 v += take;

@@ -284,6 +284,30 @@ class Gemv:
             raise IndexError("y is shorter than batch * rows")
         _lib.check(_lib.load().vx_gemv_q_rows(backend._ctx, w._h, row0, nrows, xp, xs, yp, ys, batch))
 
+    def dispatch_multi(self, backend: Backend, pass_: Optional[GpuPass], ys, ws, x, batch: int = 1,
+                       x_stride: Optional[int] = None, y_stride: Optional[int] = None) -> None:
+        """Several matrices (one type, one column count) times the same vectors in one pass (vx_gemv_q_multi):
+        ys[i] = ws[i] x.  y_stride (elements between the vectors of every y) defaults to the largest row count."""
+        n = len(ws)
+        if n != len(ys):
+            raise ValueError("as many outputs as matrices")
+        if n == 0:
+            return
+        xs = ws[0].cols if x_stride is None else x_stride
+        yst = max(w.rows for w in ws) if y_stride is None else y_stride
+        xp, xl = _ptr_len(x)
+        if xl is not None and batch and (batch - 1) * xs + ws[0].cols > xl:
+            raise IndexError("x is shorter than batch * cols")
+        yps = []
+        for w, y in zip(ws, ys):
+            yp, yl = _ptr_len(y)
+            if yl is not None and batch and (batch - 1) * yst + w.rows > yl:
+                raise IndexError("a y is shorter than batch * rows")
+            yps.append(yp)
+        wa = (C.c_void_p * n)(*[w._h.value if hasattr(w._h, "value") else w._h for w in ws])
+        ya = (C.c_void_p * n)(*yps)
+        _lib.check(_lib.load().vx_gemv_q_multi(backend._ctx, wa, n, xp, xs, ya, yst, batch))
+
 
 class GemvBatch:
     """A fixed list of GEMVs run by ONE persistent launch (vx_gemv_batch): one weight stream, one prologue.
