@@ -44,6 +44,7 @@ static const char* const kKnownOptions[] = {
     "gemv.ctas_per_sm",   // persistent grid = SMs x this
     "gemv.batch_mma",     // batches of vectors on the tensor cores: -1 (default) for 2 and more vectors, 0 never, 1 also for one vector
     "debug.timeline_ptr", // timeline build only (-DVX_TIMELINE): device buffer [blocks][entries][8] u64 for the list kernel's stamps
+    "gemv.mma_units_per_cta",  // tensor-core batch GEMV: most 16-row tiles a launch gives one thread block (default 14)
     "gemv.mma_nbw",       // tensor-core batch GEMV: most 32-column blocks per warp and column tile (8, 4, 2 or 1; 0 or less = default: 8, 4 for Q8_0 with three and more vectors)
     "gemv.mma_max_stages",  // tensor-core batch GEMV: cap on the depth of the weight ring (default 8)
     "gemv.block_wait",    // flagged x in a list: 1 one warp waits for the block, 0 every thread for its own chunk, -1 (default) by tiles per block

@@ -703,7 +703,8 @@ vx_status launch_gemv_mma(vx_context* ctx, const vx_qweights* const* ws_in, cons
     if (!choose(w, batch, 0x10000, nbw_max, max_stages, &c)) return VX_OK;
     // (and no more than 14 row tiles per CTA and launch: with one or two vectors, whose planes leave room for far
     // larger sets, 8192 x 8192 Q4_0 takes 8.7 us per matrix at 10 tiles per CTA and 10.6 us at 28)
-    const uint64_t set_units = (uint64_t)std::min(c.sg_units, 14u) * (uint32_t)ctx->sm_count;
+    const uint32_t units_cap = (uint32_t)std::max<int64_t>(1, vx::option(ctx, "gemv.mma_units_per_cta", 14));
+    const uint64_t set_units = (uint64_t)std::min(c.sg_units, units_cap) * (uint32_t)ctx->sm_count;
     // slabs taller than that are cut into pieces of that many row tiles, each a slab of its own
     std::vector<const vx_qweights*> ws;
     std::vector<size_t> row0;
