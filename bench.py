@@ -898,6 +898,42 @@ def side_configs(be, lib, torch, stream):
         sweep.append(row)
         del A, B, Cm
     out["gemm_bench_sweep"] = {"protocol": "3 warm-up + 10 timed calls, synchronise after each, wall clock", "rows": sweep}
+
+    # The kernels around the matmul path (reductions, OpAssign / Contiguous / Repeat) on 8192 x 8192 f32 operands
+    # (268 MB each, beyond L2), against the HBM copy peak; algorithmic bytes = every operand element read or
+    # written once.
+    D = 8192
+    A = torch.rand(D * D, device="cuda")
+    B = torch.rand(D * D, device="cuda") + 1.0
+    O = torch.empty(D * D, device="cuda")
+    res = torch.zeros(4, device="cuda")
+
+    def shp(n, c, h, w, ns, cs, hs, ws_):
+        s_ = _lib.VxShape()
+        s_.n, s_.c, s_.h, s_.w, s_.n_stride, s_.c_stride, s_.h_stride, s_.w_stride = n, c, h, w, ns, cs, hs, ws_
+        return s_
+    dense, transp = shp(1, 1, D, D, D * D, D * D, D, 1), shp(1, 1, D, D, D * D, D * D, 1, D)
+    one_row = shp(1, 1, D, D, 0, 0, 0, 1)
+    small = shp(1, 1, 64, 64, 4096, 4096, 64, 1)
+    vec = shp(1, 1, 1, D * D, D * D, D * D, D * D, 1)
+    cases = (
+        ("op_assign_add_dense", 3, lambda: lib.vx_op_assign(be._ctx, 0, A.data_ptr(), C.byref(dense), 0, B.data_ptr(), C.byref(dense), 0, 0, 0)),
+        ("op_assign_add_row_broadcast", 2, lambda: lib.vx_op_assign(be._ctx, 0, A.data_ptr(), C.byref(dense), 0, B.data_ptr(), C.byref(one_row), 0, 0, 0)),
+        ("op_assign_add_transposed_b", 3, lambda: lib.vx_op_assign(be._ctx, 0, A.data_ptr(), C.byref(dense), 0, B.data_ptr(), C.byref(transp), 0, 0, 0)),
+        ("contiguous_of_transposed", 2, lambda: lib.vx_contiguous(be._ctx, O.data_ptr(), 0, B.data_ptr(), C.byref(transp), 0, 0)),
+        ("repeat_64x64_tile", 1, lambda: lib.vx_repeat(be._ctx, O.data_ptr(), C.byref(dense), 0, B.data_ptr(), C.byref(small), 0)),
+        ("reduce_sum_wide", 1, lambda: lib.vx_reduce(be._ctx, 0, 0, 1, B.data_ptr(), C.byref(vec), 0, res.data_ptr())),
+        ("reduce_max_wide", 1, lambda: lib.vx_reduce(be._ctx, 3, 0, 1, B.data_ptr(), C.byref(vec), 0, res.data_ptr())),
+    )
+    ew = {}
+    for name, operands, call in cases:
+        def fn(call=call):
+            _lib.check(call())
+        us = time_graph(fn, 1, reps=10)
+        byts = operands * D * D * 4
+        ew[name] = {"us": us, "GB/s": byts / us / 1e3, "frac_of_measured_hbm": byts / us / 1e3 / peak}
+    out["elementwise_and_reduce_8192x8192_f32"] = ew
+    del A, B, O
     return out
 
 

@@ -118,3 +118,110 @@ def test_tensor_append_and_shift_remove(backend):
     assert t.shift_remove(backend, 2, 2) == 0
     with pytest.raises(IndexError):
         t.shift_remove(backend, 1, 9)
+
+
+# ---- the row, vector and tile forms of the kernels (layouts wide enough to take them) against the oracle and against
+# ---- the general kernels ("elementwise.fast" = 0), bit for bit
+
+def _shape(lib_mod, sizes, strides):
+    s = lib_mod.VxShape()
+    s.n, s.c, s.h, s.w = sizes
+    s.n_stride, s.c_stride, s.h_stride, s.w_stride = strides
+    return s
+
+
+def _dense(sizes):
+    n, c, h, w = sizes
+    return (c * h * w, h * w, w, 1)
+
+
+_FAST_CASES = [
+    # name, sizes of a, strides of a, strides of b, offset a, offset b
+    ("dense, float4 rows", (1, 1, 200, 520), None, None, 0, 0),
+    ("dense 4-D, float4 rows", (3, 2, 70, 132), None, None, 0, 0),
+    ("dense, width not a multiple of 4", (1, 1, 130, 1030), None, None, 0, 0),
+    ("dense, rows off 16-byte alignment", (1, 1, 64, 256), (0, 0, 260, 1), (0, 0, 260, 1), 3, 5),
+    ("b one row for every row", (1, 2, 90, 512), None, (0, 0, 0, 1), 0, 0),
+    ("b one value per row", (1, 2, 90, 512), None, (0, 90, 1, 0), 0, 8),
+    ("b one value per row, a off alignment", (1, 1, 90, 512), (0, 0, 513, 1), (0, 0, 1, 0), 1, 0),
+    ("b transposed", (1, 1, 100, 70), None, (0, 0, 1, 100), 0, 0),
+    ("b transposed, 4-D, ragged tiles", (2, 3, 65, 129), None, (3 * 65 * 129, 65 * 129, 1, 65), 0, 7),
+    ("a strided along w", (1, 1, 40, 300), (0, 0, 600, 2), None, 0, 0),
+]
+
+
+@pytest.mark.parametrize("op", [OV.Add, OV.Div, OV.Copy])
+@pytest.mark.parametrize("case", _FAST_CASES, ids=[c[0] for c in _FAST_CASES])
+def test_fast_forms_of_op_assign(backend, oracle, op, case):
+    import ctypes as C
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    _, sizes, stra, strb, off_a, off_b = case
+    stra = _dense(sizes) if stra is None else stra
+    strb = _dense(sizes) if strb is None else strb
+
+    def span(strides):
+        return 1 + sum((sz - 1) * st for sz, st in zip(sizes, strides))
+    A = synth.uniform_matrix(1, span(stra) + off_a + 4, seed=7).ravel()
+    B = (synth.uniform_matrix(1, span(strb) + off_b + 4, seed=8).ravel() + np.float32(1.25)).astype(np.float32)
+    want = A.copy()
+    oracle.op_assign(op, want, oracle.Shape.of(sizes, stra), B.copy(), oracle.Shape.of(sizes, strb), off_a, off_b)
+    sa, sb = _shape(_lib, sizes, stra), _shape(_lib, sizes, strb)
+    outs = []
+    for fast in (1, 0):
+        backend.set_option("elementwise.fast", fast)
+        a, b = backend.init_buffer(A), backend.init_buffer(B)
+        _lib.check(lib.vx_op_assign(backend._ctx, op, a.ptr, C.byref(sa), A.size, b.ptr, C.byref(sb), B.size, off_a, off_b))
+        got = np.empty_like(A)
+        backend.slow_read_buffer(a, got)
+        outs.append(got)
+    backend.set_option("elementwise.fast", 1)
+    assert np.array_equal(outs[0].view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(outs[1].view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.uint32])
+@pytest.mark.parametrize("sizes,strides,offset", [((1, 1, 100, 70), (0, 0, 1, 100), 0),          # a transposed matrix
+                                                  ((2, 3, 65, 129), (3 * 65 * 129, 65 * 129, 1, 65), 9),
+                                                  ((1, 4, 50, 256), (0, 256, 1024, 1), 0),        # rows of a permuted view
+                                                  ((1, 1, 300, 130), (0, 0, 131, 1), 2)])         # a narrowed view
+def test_fast_forms_of_contiguous(backend, oracle, dtype, sizes, strides, offset):
+    import ctypes as C
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    span = 1 + sum((sz - 1) * st for sz, st in zip(sizes, strides)) + offset
+    rng = np.random.Generator(np.random.Philox(11))
+    src = rng.integers(0, 2 ** 32, size=span, dtype=np.uint64).astype(np.uint32)        # every bit pattern, NaNs included
+    want = oracle.contiguous(src, oracle.Shape.of(sizes, strides), offset)
+    s = _shape(_lib, sizes, strides)
+    n = int(np.prod(sizes))
+    for fast in (1, 0):
+        backend.set_option("elementwise.fast", fast)
+        sb = backend.init_buffer(src.view(dtype))
+        db = backend.init_buffer(np.zeros(n, dtype))
+        _lib.check(lib.vx_contiguous(backend._ctx, db.ptr, n, sb.ptr, C.byref(s), span, offset))
+        got = np.empty(n, dtype)
+        backend.slow_read_buffer(db, got)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    backend.set_option("elementwise.fast", 1)
+
+
+@pytest.mark.parametrize("rsizes,ssizes", [((1, 1, 37, 300), (1, 1, 5, 7)), ((2, 3, 20, 256), (1, 2, 20, 64)),
+                                           ((1, 1, 10, 1000), (1, 1, 1, 1)), ((1, 1, 9, 130), (1, 1, 4, 300))])
+def test_fast_form_of_repeat(backend, oracle, rsizes, ssizes):
+    import ctypes as C
+    from vortx_b200 import _lib
+    lib = _lib.load()
+    S = synth.uniform_matrix(1, int(np.prod(ssizes)), seed=12).ravel()
+    want = np.zeros(int(np.prod(rsizes)), np.float32)
+    oracle.repeat(want, oracle.Shape.of(rsizes, _dense(rsizes)), S.copy(), oracle.Shape.of(ssizes, _dense(ssizes)))
+    sr, ss = _shape(_lib, rsizes, _dense(rsizes)), _shape(_lib, ssizes, _dense(ssizes))
+    for fast in (1, 0):
+        backend.set_option("elementwise.fast", fast)
+        rb = backend.init_buffer(np.zeros(want.size, np.float32))
+        sb = backend.init_buffer(S)
+        _lib.check(lib.vx_repeat(backend._ctx, rb.ptr, C.byref(sr), want.size, sb.ptr, C.byref(ss), S.size))
+        got = np.empty_like(want)
+        backend.slow_read_buffer(rb, got)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    backend.set_option("elementwise.fast", 1)

@@ -5,8 +5,16 @@
 // Index arithmetic follows the shaders exactly — a linear id is decomposed over the first
 // shape's sizes (shape.rs:76-86) and re-composed through each operand's strides (shape.rs:52-54),
 // all in wrapping u32 — so results are the very same bits wherever the reference is defined.
-// One grid-stride loop per kernel; adjacent threads take adjacent linear ids, which are adjacent
-// addresses whenever the innermost stride is 1.
+// The general kernels are one grid-stride loop each; adjacent threads take adjacent linear ids, which are
+// adjacent addresses whenever the innermost stride is 1.  They spend three integer divisions per element and
+// run at a third of the HBM rate, so the layouts that matter get forms that compute the same indices without
+// them (all bit-identical: the operations are exact per element, only the order of the elements changes):
+//   rows   a block walks whole rows (n, c, h) and its threads the w axis: one decomposition per row; float4
+//          accesses when both innermost strides are 1 (or b's is 0) and every row starts 16-byte aligned;
+//   tile   b is read across its unit-stride axis h (a transposed view): 64 x 64 tiles through shared memory.
+// They are taken when no index can wrap around 2^32 (the general kernels keep the wrapping arithmetic).
+#include <algorithm>
+
 #include "vx_internal.h"
 
 namespace {
@@ -39,6 +47,96 @@ __device__ __forceinline__ float apply(float a, float b) {
     if (OP == VX_OP_MUL) return __fmul_rn(a, b);
     if (OP == VX_OP_DIV) return __fdiv_rn(a, b);
     return b;
+}
+
+// (n, c, h) of row r, as decompose() finds them for the row's elements
+__device__ __forceinline__ Idx4 row_of(const vx_shape& s, uint32_t r) {
+    const uint32_t t = r / s.h;
+    return Idx4{t / s.c, t % s.c, r % s.h, 0};
+}
+
+// rows form.  VEC: float4 along w (b's innermost stride 1, or 0 with BCAST: one b value per row).
+template <int OP, bool VEC, bool BCAST>
+__global__ void __launch_bounds__(256)
+op_assign_rows_kernel(float* __restrict__ a, const float* __restrict__ b, const vx_shape sa, const vx_shape sb,
+                      uint32_t off_a, uint32_t off_b) {
+    const uint32_t rows = sa.n * sa.c * sa.h;
+    for (uint32_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        Idx4 id = row_of(sa, r);
+        const uint32_t base_a = off_a + compose(sa, id), base_b = off_b + compose(sb, id);
+        if (VEC) {
+            float4* pa = reinterpret_cast<float4*>(a + base_a);
+            const float4* pb = reinterpret_cast<const float4*>(b + base_b);
+            const float bv = BCAST ? b[base_b] : 0.0f;
+            for (uint32_t w = threadIdx.x; w < sa.w / 4; w += blockDim.x) {
+                float4 va = pa[w];
+                const float4 vb = BCAST ? make_float4(bv, bv, bv, bv) : pb[w];
+                va.x = apply<OP>(va.x, vb.x);
+                va.y = apply<OP>(va.y, vb.y);
+                va.z = apply<OP>(va.z, vb.z);
+                va.w = apply<OP>(va.w, vb.w);
+                pa[w] = va;
+            }
+        } else {
+            for (uint32_t w = threadIdx.x; w < sa.w; w += blockDim.x) {
+                const uint32_t ia = base_a + w * sa.w_stride;
+                a[ia] = apply<OP>(a[ia], b[base_b + w * sb.w_stride]);
+            }
+        }
+    }
+}
+
+// tile form: a's innermost stride is 1, b's unit stride is along h.  Tile (th, tw) of plane (n, c): b is read
+// with h fastest, a is updated with w fastest; the 64 x 65 shared tile turns one into the other (runs of 256
+// bytes on both sides; 32 x 32 tiles measured 15 % slower).
+constexpr int kTile = 64;
+template <int OP>
+__global__ void __launch_bounds__(256)
+op_assign_tile_kernel(float* __restrict__ a, const float* __restrict__ b, const vx_shape sa, const vx_shape sb,
+                      uint32_t off_a, uint32_t off_b) {
+    __shared__ float tile[kTile][kTile + 1];
+    const uint32_t tiles_w = (sa.w + kTile - 1) / kTile, tiles_h = (sa.h + kTile - 1) / kTile;
+    const uint32_t per_plane = tiles_w * tiles_h, total = per_plane * sa.n * sa.c;
+    const uint32_t x = threadIdx.x & (kTile - 1), y = threadIdx.x / kTile;     // 64 x 4 threads
+    for (uint32_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const uint32_t plane = t / per_plane, in_plane = t - plane * per_plane;
+        const uint32_t th = in_plane / tiles_w, tw = in_plane - th * tiles_w;
+        const Idx4 pl = Idx4{plane / sa.c, plane % sa.c, 0, 0};
+        const uint32_t base_a = off_a + compose(sa, pl), base_b = off_b + compose(sb, pl);
+        __syncthreads();                                            // the tile of the round before has been used
+#pragma unroll
+        for (int k = 0; k < kTile / 4; ++k) {
+            const uint32_t h = th * kTile + x, w = tw * kTile + y + 4 * k;
+            if (h < sa.h && w < sa.w) tile[y + 4 * k][x] = b[base_b + h * sb.h_stride + w * sb.w_stride];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kTile / 4; ++k) {
+            const uint32_t h = th * kTile + y + 4 * k, w = tw * kTile + x;
+            if (h < sa.h && w < sa.w) {
+                const uint32_t ia = base_a + h * sa.h_stride + w * sa.w_stride;
+                a[ia] = apply<OP>(a[ia], tile[x][y + 4 * k]);
+            }
+        }
+    }
+}
+
+// rows form of the tiling copy: the source's (n, c, h) wrap once per row, its w index by increments.
+__global__ void __launch_bounds__(256)
+repeat_rows_kernel(float* __restrict__ result, const float* __restrict__ source, const vx_shape sr, const vx_shape ss) {
+    const uint32_t rows = sr.n * sr.c * sr.h;
+    const uint32_t step = blockDim.x % ss.w;
+    for (uint32_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const Idx4 id = row_of(sr, r);
+        const Idx4 wr = Idx4{id.n % ss.n, id.c % ss.c, id.h % ss.h, 0};
+        const uint32_t base_r = compose(sr, id), base_s = compose(ss, wr);
+        uint32_t ws = threadIdx.x % ss.w;
+        for (uint32_t w = threadIdx.x; w < sr.w; w += blockDim.x) {
+            result[base_r + w * sr.w_stride] = source[base_s + ws * ss.w_stride];
+            ws += step;
+            if (ws >= ss.w) ws -= ss.w;
+        }
+    }
 }
 
 template <int OP>
@@ -84,6 +182,43 @@ unsigned grid_for(const vx_context* ctx, uint32_t len) {
     return std::max(1u, std::min(want, (unsigned)ctx->sm_count * 16));
 }
 
+// No index of `s` walked over `sizes` (plus offset) reaches 2^32: the fast forms may then compute indices
+// in any order.
+bool no_wrap(const vx_shape& sizes, const vx_shape& s, uint64_t offset) {
+    if (sizes.n == 0 || sizes.c == 0 || sizes.h == 0 || sizes.w == 0) return true;
+    const uint64_t last = offset + (uint64_t)(sizes.n - 1) * s.n_stride + (uint64_t)(sizes.c - 1) * s.c_stride +
+                          (uint64_t)(sizes.h - 1) * s.h_stride + (uint64_t)(sizes.w - 1) * s.w_stride;
+    return last < (1ull << 32);
+}
+bool rows_aligned(const void* base, const vx_shape& s, uint64_t offset) {
+    return (reinterpret_cast<uintptr_t>(base) & 15u) == 0 && offset % 4 == 0 && s.n_stride % 4 == 0 && s.c_stride % 4 == 0 &&
+           s.h_stride % 4 == 0;
+}
+
+// Picks the form for a op= b (see the head of this file) and launches it.
+template <int OP>
+void launch_op_assign(vx_context* ctx, float* a, const float* b, const vx_shape& sa, const vx_shape& sb, uint32_t off_a,
+                      uint32_t off_b) {
+    const uint32_t len = shape_len(sa);
+    const bool fast = vx::option(ctx, "elementwise.fast", 1) != 0 && no_wrap(sa, sa, off_a) && no_wrap(sa, sb, off_b);
+    const uint32_t rows = sa.n * sa.c * sa.h;
+    const unsigned row_grid = std::max(1u, std::min(rows, (unsigned)ctx->sm_count * 8));
+    if (fast && sa.w >= 32 && sa.h >= 32 && sa.w_stride == 1 && sb.h_stride == 1 && sb.w_stride != 1 && sb.w_stride != 0) {
+        const uint32_t tiles = ((sa.w + kTile - 1) / kTile) * ((sa.h + kTile - 1) / kTile) * sa.n * sa.c;
+        op_assign_tile_kernel<OP><<<std::min(tiles, (uint32_t)ctx->sm_count * 16), 256, 0, ctx->stream>>>(a, b, sa, sb, off_a, off_b);
+    } else if (fast && sa.w >= 128) {
+        const bool vec = sa.w % 4 == 0 && sa.w_stride == 1 && rows_aligned(a, sa, off_a) && rows_aligned(b, sb, off_b);
+        if (vec && sb.w_stride == 1)
+            op_assign_rows_kernel<OP, true, false><<<row_grid, 256, 0, ctx->stream>>>(a, b, sa, sb, off_a, off_b);
+        else if (sa.w % 4 == 0 && sa.w_stride == 1 && sb.w_stride == 0 && rows_aligned(a, sa, off_a))
+            op_assign_rows_kernel<OP, true, true><<<row_grid, 256, 0, ctx->stream>>>(a, b, sa, sb, off_a, off_b);
+        else
+            op_assign_rows_kernel<OP, false, false><<<row_grid, 256, 0, ctx->stream>>>(a, b, sa, sb, off_a, off_b);
+    } else {
+        op_assign_kernel<OP><<<grid_for(ctx, len), 256, 0, ctx->stream>>>(a, b, sa, sb, off_a, off_b);
+    }
+}
+
 vx_status cap_check(const vx_context* ctx, const char* what, const vx_shape& s, uint64_t offset, uint64_t cap) {
     if (cap == 0 || vx::option(ctx, "bounds_check", 1) == 0) return VX_OK;
     const uint64_t sp = span(s);
@@ -111,13 +246,12 @@ vx_status vx_op_assign(vx_context* ctx, vx_op op, float* a, const vx_shape* shap
     if ((st = cap_check(ctx, "a", *shape_a, offset_a, cap_a)) != VX_OK) return st;
     if ((st = cap_check(ctx, "b", touched_b, offset_b, cap_b)) != VX_OK) return st;
     vx::DeviceGuard guard(ctx->device);
-    const unsigned grid = grid_for(ctx, len);
     switch (op) {
-        case VX_OP_ADD: op_assign_kernel<VX_OP_ADD><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
-        case VX_OP_SUB: op_assign_kernel<VX_OP_SUB><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
-        case VX_OP_MUL: op_assign_kernel<VX_OP_MUL><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
-        case VX_OP_DIV: op_assign_kernel<VX_OP_DIV><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
-        default: op_assign_kernel<VX_OP_COPY><<<grid, 256, 0, ctx->stream>>>(a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        case VX_OP_ADD: launch_op_assign<VX_OP_ADD>(ctx, a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        case VX_OP_SUB: launch_op_assign<VX_OP_SUB>(ctx, a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        case VX_OP_MUL: launch_op_assign<VX_OP_MUL>(ctx, a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        case VX_OP_DIV: launch_op_assign<VX_OP_DIV>(ctx, a, b, *shape_a, *shape_b, offset_a, offset_b); break;
+        default: launch_op_assign<VX_OP_COPY>(ctx, a, b, *shape_a, *shape_b, offset_a, offset_b); break;
     }
     VX_CUDA(cudaGetLastError());
     ctx->launches++;
@@ -135,8 +269,18 @@ vx_status vx_contiguous(vx_context* ctx, void* dest, uint64_t cap_dest, const vo
     vx_status st = cap_check(ctx, "source", *shape_src, offset, cap_src);
     if (st != VX_OK) return st;
     vx::DeviceGuard guard(ctx->device);
-    contiguous_kernel<<<grid_for(ctx, len), 256, 0, ctx->stream>>>(static_cast<uint32_t*>(dest),
-                                                                   static_cast<const uint32_t*>(src), *shape_src, offset);
+    // dest[i] = src[..] is "a = b" with a the row-major tensor of src's sizes: the copy forms of op_assign move
+    // the 4-byte elements as they are (no arithmetic touches them)
+    vx_shape sd = *shape_src;
+    sd.w_stride = 1;
+    sd.h_stride = sd.w;
+    sd.c_stride = sd.h * sd.w;
+    sd.n_stride = sd.c * sd.h * sd.w;
+    if (vx::option(ctx, "elementwise.fast", 1) != 0 && (uint64_t)shape_src->n * shape_src->c * shape_src->h * shape_src->w < (1ull << 32))
+        launch_op_assign<VX_OP_COPY>(ctx, static_cast<float*>(dest), static_cast<const float*>(src), sd, *shape_src, 0, offset);
+    else
+        contiguous_kernel<<<grid_for(ctx, len), 256, 0, ctx->stream>>>(static_cast<uint32_t*>(dest),
+                                                                       static_cast<const uint32_t*>(src), *shape_src, offset);
     VX_CUDA(cudaGetLastError());
     ctx->launches++;
     return VX_OK;
@@ -153,7 +297,14 @@ vx_status vx_repeat(vx_context* ctx, float* result, const vx_shape* shape_result
     if ((st = cap_check(ctx, "result", *shape_result, 0, cap_result)) != VX_OK) return st;
     if ((st = cap_check(ctx, "source", *shape_source, 0, cap_source)) != VX_OK) return st;
     vx::DeviceGuard guard(ctx->device);
-    repeat_kernel<<<grid_for(ctx, len), 256, 0, ctx->stream>>>(result, source, *shape_result, *shape_source);
+    if (vx::option(ctx, "elementwise.fast", 1) != 0 && shape_result->w >= 128 && no_wrap(*shape_result, *shape_result, 0) &&
+        no_wrap(*shape_source, *shape_source, 0)) {
+        const uint32_t rows = shape_result->n * shape_result->c * shape_result->h;
+        repeat_rows_kernel<<<std::max(1u, std::min(rows, (unsigned)ctx->sm_count * 8)), 256, 0, ctx->stream>>>(
+            result, source, *shape_result, *shape_source);
+    } else {
+        repeat_kernel<<<grid_for(ctx, len), 256, 0, ctx->stream>>>(result, source, *shape_result, *shape_source);
+    }
     VX_CUDA(cudaGetLastError());
     ctx->launches++;
     return VX_OK;

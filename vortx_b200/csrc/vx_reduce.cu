@@ -92,6 +92,15 @@ reduce_ordered_kernel(const T* __restrict__ in, uint32_t n, uint32_t stride, T* 
 // ---- WIDE: grid of partials + fold ------------------------------------------------------------
 constexpr int kWideThreads = 256;
 
+template <class T>
+__device__ __forceinline__ T bits_to(uint32_t w);
+template <>
+__device__ __forceinline__ float bits_to<float>(uint32_t w) { return __uint_as_float(w); }
+template <>
+__device__ __forceinline__ uint32_t bits_to<uint32_t>(uint32_t w) { return w; }
+template <>
+__device__ __forceinline__ int32_t bits_to<int32_t>(uint32_t w) { return (int32_t)w; }
+
 template <class T, int OP>
 __device__ __forceinline__ T block_fold(T a, T* ws) {
     constexpr int TREE = OP == SQNORM ? SUM : OP;
@@ -109,11 +118,39 @@ template <class T, int OP>
 __global__ void __launch_bounds__(kWideThreads)
 reduce_wide_partials_kernel(const T* __restrict__ in, uint32_t n, uint32_t stride, T* __restrict__ partials) {
     __shared__ T ws[kWideThreads];
-    // contiguous slice per block, so that the partials' order is the index order
-    const uint32_t per = (n + gridDim.x - 1) / gridDim.x;
-    const uint32_t lo = blockIdx.x * per, hi = min(n, lo + per);
+    // contiguous slice per block (a multiple of 4 elements), so that the partials' order is the index order
+    const uint32_t per = ((n + gridDim.x - 1) / gridDim.x + 3) & ~3u;
+    const uint32_t lo = min(n, blockIdx.x * per), hi = min(n, lo + per);
     T a = identity<T, OP>();
-    for (uint32_t i = lo + threadIdx.x; i < hi; i += kWideThreads) a = fold<T, OP>(a, prepare<T, OP>(in[(size_t)i * stride]));
+    if (stride == 1 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0) {
+        // unit stride: 16-byte loads, four running results per thread (element 4 k + j goes to result j), two
+        // loads in flight; the thread's four results are folded as (0 with 1) with (2 with 3)
+        constexpr int TREE = OP == SQNORM ? SUM : OP;
+        T acc[4] = {a, a, a, a};
+        const uint4* v = reinterpret_cast<const uint4*>(in + lo);
+        const uint32_t nv = (hi - lo) / 4;
+        uint32_t i = threadIdx.x;
+        for (; i + kWideThreads < nv; i += 2 * kWideThreads) {
+            const uint4 p = v[i], q = v[i + kWideThreads];
+            const uint32_t pw[4] = {p.x, p.y, p.z, p.w}, qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = fold<T, OP>(acc[j], prepare<T, OP>(bits_to<T>(pw[j])));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = fold<T, OP>(acc[j], prepare<T, OP>(bits_to<T>(qw[j])));
+        }
+        for (; i < nv; i += kWideThreads) {
+            const uint4 p = v[i];
+            const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = fold<T, OP>(acc[j], prepare<T, OP>(bits_to<T>(pw[j])));
+        }
+        a = fold<T, TREE>(fold<T, TREE>(acc[0], acc[1]), fold<T, TREE>(acc[2], acc[3]));
+        // the slice's last 1..3 elements (only the last block has any)
+        const uint32_t rest = lo + nv * 4 + threadIdx.x;
+        if (rest < hi) a = fold<T, TREE>(a, prepare<T, OP>(in[rest]));
+    } else {
+        for (uint32_t i = lo + threadIdx.x; i < hi; i += kWideThreads) a = fold<T, OP>(a, prepare<T, OP>(in[(size_t)i * stride]));
+    }
     const T r = block_fold<T, OP>(a, ws);
     if (threadIdx.x == 0) partials[blockIdx.x] = r;
 }
