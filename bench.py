@@ -675,6 +675,20 @@ def cpu_side_baselines(o, threads):
             o.gemv(qt, blocks, dim, dim, x, nthreads=threads)
         dt = (time.perf_counter() - t0) / 10
         out[name] = {"ms": dt * 1e3, "GB/s": gemv_bytes(dim, dim, 1, 1, bb) / dt / 1e9, "sample": "10 calls after one warm-up"}
+    # the kernels around the path: a += b and the sum of 4096 x 4096 f32 (the restatements are single-threaded, as
+    # the shaders' one-element-per-invocation form is)
+    dim = 4096
+    a = synth.uniform_matrix(dim, dim, 2).ravel().copy()
+    b = synth.uniform_matrix(dim, dim, 3).ravel().copy()
+    sh = o.shape_contiguous(1, 1, dim, dim)
+    t0 = time.perf_counter()
+    o.op_assign(0, a, sh, b, sh)
+    dt = time.perf_counter() - t0
+    out["op_assign_add_4096x4096"] = {"ms": dt * 1e3, "GB/s": 3 * dim * dim * 4 / dt / 1e9, "cores": 1, "sample": "1 call"}
+    t0 = time.perf_counter()
+    o.reduce(b, "sum")
+    dt = time.perf_counter() - t0
+    out["reduce_sum_16Mi"] = {"ms": dt * 1e3, "GB/s": dim * dim * 4 / dt / 1e9, "cores": 1, "sample": "1 call"}
     return out
 
 
