@@ -195,3 +195,55 @@ def test_gemv_nan_inf_and_tiny_x(backend, oracle, qt, variant):
     finally:
         backend.set_option("gemv.variant", 2)
         qm.free()
+
+
+@pytest.mark.parametrize("batch", [2, 4, 8])
+def test_q4_0_batches_at_full_size_on_the_tensor_cores(backend, oracle, up_projection, batch):
+    """Batches of 2 / 4 / 8 vectors over the 28672 x 8192 matrix through the tensor-core batch kernel, every vector
+    against the f64 oracle and not worse than a few times the f32 oracle's own error; linearity as a size-independent
+    property: the product of x0 + x1 (formed in f32) equals the sum of the two products to within the bars."""
+    rows, cols, blocks, qm, xs = up_projection
+    x = xs[:batch].copy()
+    x[batch - 1] = (xs[0] + xs[1]).astype(np.float32)
+    xd = backend.init_buffer(x.ravel())
+    yd = backend.init_buffer(np.full(batch * rows, np.nan, np.float32))
+    before = backend.launch_count()
+    vb.Gemv().dispatch(backend, None, yd, qm, xd, batch=batch)
+    assert backend.launch_count() - before == 2                # pre-pass + one pass over the weights
+    got = np.empty(batch * rows, np.float32)
+    backend.slow_read_buffer(yd, got)
+    got = got.reshape(batch, rows)
+    y64, absdot = oracle.gemv_f64(vb.Q4_0, blocks, rows, cols, x)
+    y32 = oracle.gemv(vb.Q4_0, blocks, rows, cols, x, nthreads=oracle.hardware_threads())
+    for v in range(batch):
+        _check(got[v], y64[v], absdot[v], y32[v])
+    if batch > 2:
+        lin = got[0].astype(np.float64) + got[1].astype(np.float64)
+        assert np.abs(got[batch - 1] - lin).max() / np.abs(lin).max() <= 2 * REL_TOL
+
+
+def test_q4_0_8192x8192_batch_of_8_and_three_matrices_sharing_it(backend, oracle):
+    """BASELINE.json's 8192 x 8192 shape with 8 vectors: one matrix, and three matrices sharing the vectors in one
+    call (vx_gemv_q_multi); both against the f64 oracle, and bit-identical to each other."""
+    rows = cols = 8192
+    x = synth.normal_vectors(8, cols, seed=1)
+    qms, refs = [], []
+    for i in range(3):
+        blocks = vb.quantize(vb.Q4_0, synth.normal_matrix(rows, cols, seed=i))
+        qms.append(vb.QuantizedMatrix(backend, vb.Q4_0, blocks, rows, cols))
+        refs.append(oracle.gemv_f64(vb.Q4_0, blocks, rows, cols, x))
+    xd = backend.init_buffer(x.ravel())
+    yds = [backend.init_buffer(np.full(8 * rows, np.nan, np.float32)) for _ in qms]
+    vb.Gemv().dispatch_multi(backend, None, yds, qms, xd, batch=8)
+    one = backend.init_buffer(np.full(8 * rows, np.nan, np.float32))
+    for qm, yd, (y64, absdot) in zip(qms, yds, refs):
+        got = np.empty(8 * rows, np.float32)
+        backend.slow_read_buffer(yd, got)
+        for v in range(8):
+            _check(got.reshape(8, rows)[v], y64[v], absdot[v])
+        vb.Gemv().dispatch(backend, None, one, qm, xd, batch=8)
+        alone = np.empty(8 * rows, np.float32)
+        backend.slow_read_buffer(one, alone)
+        assert np.array_equal(alone.view(np.uint32), got.view(np.uint32))
+    for qm in qms:
+        qm.free()
