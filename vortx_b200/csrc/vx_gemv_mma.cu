@@ -24,11 +24,13 @@
 //   * The main kernel is persistent, one CTA per SM: producer thread (one tiled TMA load per 16-row tile,
 //     128-byte swizzle so that fragment loads hit 32 different banks) and 8 consumer warps.
 //     A CTA owns whole rows.  The planes (25 bytes per column, 9 in the SINGLE form) must sit in its shared
-//     memory, so wide matrices are walked in PHASES: the planes of one column part are loaded, the part is
-//     streamed for all the CTA's row tiles (at most `sg_units` of them at a time), their sums wait in shared
-//     memory, the next part's planes replace the first's, and so on; the last phase writes y.  No sums
-//     cross CTAs.  The 8 warps of a CTA split a tile's columns further and keep their B fragments in
-//     registers while they walk up to 4 row tiles.
+//     memory, so the columns are walked in PHASES of one column tile (32 NBW x 8 warps columns): the tile's
+//     planes sit in one of two slots (the next phase's arrive meanwhile), the tile is streamed for all the
+//     CTA's row tiles (at most `sg_units` of them at a time: a pass), their sums wait in shared memory, and
+//     so on; the last phase writes y.  No sums cross CTAs.  The 8 warps of a CTA split a tile's columns
+//     further and keep their B fragments in registers for the whole pass.
+//   * One launch walks up to 8 matrices of one type and column count that share the vectors (their row tiles
+//     are numbered through and dealt out evenly); the planes are made once for all of them.
 //   * Partial sums meet in shared memory: every consumer thread leaves its four sums of a row tile there (its
 //     own 16 bytes, no synchronisation per tile); at the end of a pass over the set's row tiles the warps add
 //     them up, the 8 warps of a CTA and then the phases, both in a fixed order.  (A hand-off of every tile to an
