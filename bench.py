@@ -1112,14 +1112,14 @@ def run_single_timeline(rows: int, cols: int, what: str, copies: int):
         for l in range(3, copies - 1):
             end = d[l - 1][:, 5].max()
             t = d[l]
-            table.append([np.median(t[:, 7]) - end, np.median(t[:, 0]) - end, np.median(t[:, 2]) - end,
+            table.append([np.median(t[:, 7]) - end, np.median(t[:, 0]) - end, np.median(t[:, 1]) - end, np.median(t[:, 2]) - end,
                           np.median(t[:, 3]) - end, np.median(t[:, 4]) - end, t[:, 5].min() - end, t[:, 5].max() - end])
         m = np.median(np.array(table), axis=0) / 1e3
         print(f"{what} {rows} x {cols}, programmatic dependent launch {'on' if pdl else 'off'}: {per:.2f} us per launch, "
               f"{d[4].shape[0]} thread blocks; microseconds after the last store of the launch before (median block, "
-              f"median launch): block starts {m[0]:.2f}, past griddepcontrol.wait {m[1]:.2f}, x converted {m[2]:.2f}, "
-              f"first tile present {m[3]:.2f}, last tile computed {m[4]:.2f}, first block's last store {m[5]:.2f}, "
-              f"last block's last store {m[6]:.2f}", flush=True)
+              f"median launch): block starts {m[0]:.2f}, past griddepcontrol.wait {m[1]:.2f}, first of x here {m[2]:.2f}, "
+              f"x converted {m[3]:.2f}, first tile present {m[4]:.2f}, last tile computed {m[5]:.2f}, "
+              f"first block's last store {m[6]:.2f}, last block's last store {m[7]:.2f}", flush=True)
     g = None
     for w in ws:
         w.free()

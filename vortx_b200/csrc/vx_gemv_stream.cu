@@ -436,6 +436,14 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
                     for (int i = 0; i < W; ++i) xv[i] = 0.0f;
                 }
+#ifdef VX_TIMELINE
+                // plain x: [1] = the first and the last 16 bytes of the thread's first chunk have arrived
+                if (tl && j == 0 && !x_pairs) {
+                    float probe = xv[0] + xv[W - 1];
+                    asm volatile("" ::"f"(probe));
+                    tl[1] = gtime();
+                }
+#endif
                 float amax = 0.0f, poison = 0.0f;
 #pragma unroll
                 for (int i = 0; i < W; ++i) {
