@@ -462,6 +462,7 @@ public:
         if (batch_) vx_gemv_batch_free(ctx_, batch_);
     }
     void launch() const { check(vx_gemv_batch_launch(ctx_, batch_)); }
+    const vx_gemv_batch* handle() const { return batch_; }
 
 private:
     vx_context* ctx_;

@@ -204,6 +204,73 @@ static void gpu_tests() {
             const auto a = single[i].read(), b = listed[i].read();
             EXPECT(std::memcmp(a.data(), b.data(), rows * sizeof(float)) == 0);
         }
+        // the same three matrices times the same vector in one call (vx_gemv_q_multi), and with two vectors; then the
+        // list with host buffers, recorded once and replayed (vx_host_pipeline): pinned x up, the list, y down
+        {
+            const vx_qweights* wp[3] = {ws[0]->handle(), ws[1]->handle(), ws[2]->handle()};
+            std::vector<Tensor<float>> multi;
+            float* yp[3];
+            for (int i = 0; i < 3; ++i) {
+                multi.push_back(Tensor<float>::vector_uninit(backend, 2 * rows));
+                yp[i] = multi.back().buffer().ptr();
+            }
+            std::vector<float> x2(2 * cols);
+            for (size_t c = 0; c < cols; ++c) {
+                x2[c] = x[c];
+                x2[cols + c] = 0.5f * x[cols - 1 - c];
+            }
+            auto gx2 = Tensor<float>::vector(backend, x2);
+            check(vx_gemv_q_multi(backend.ctx(), wp, 3, gx2.buffer().ptr(), cols, yp, rows, 2));
+            backend.synchronize();
+            for (int i = 0; i < 3; ++i) {
+                const auto a = single[i].read(), b = multi[i].read();
+                double worst = 0, largest = 0;
+                for (size_t r = 0; r < rows; ++r) {
+                    worst = std::fmax(worst, std::fabs((double)a[r] - b[r]));
+                    largest = std::fmax(largest, std::fabs((double)a[r]));
+                }
+                EXPECT(worst / largest <= 1e-5);          // the tensor-core kernel against the streaming kernel
+            }
+            void *hx = nullptr, *hy = nullptr;
+            check(vx_host_alloc(cols * sizeof(float), &hx));
+            check(vx_host_alloc(3 * rows * sizeof(float), &hy));
+            std::memcpy(hx, x.data(), cols * sizeof(float));
+            auto gxh = Tensor<float>::vector_uninit(backend, cols);
+            auto gyh = Tensor<float>::vector_uninit(backend, 3 * rows);
+            std::vector<vx_gemv_op> hops(3);
+            for (int i = 0; i < 3; ++i) {
+                std::memset(&hops[i], 0, sizeof(vx_gemv_op));
+                hops[i].w = ws[i]->handle();
+                hops[i].nrows = rows;
+                hops[i].x = gxh.buffer().ptr();
+                hops[i].y = gyh.buffer().ptr() + i * rows;
+                hops[i].y_stride = 1;
+            }
+            GemvBatch hbatch(backend, hops);
+            vx_host_stage stage;
+            std::memset(&stage, 0, sizeof(stage));
+            stage.batch = hbatch.handle();
+            stage.up_device = gxh.buffer().ptr();
+            stage.up_host = hx;
+            stage.up_bytes = cols * sizeof(float);
+            stage.down_host = hy;
+            stage.down_host_pitch = stage.down_device_pitch = stage.down_width_bytes = 3 * rows * sizeof(float);
+            stage.down_device = gyh.buffer().ptr();
+            stage.down_rows = 1;
+            vx_host_pipeline* pipe = nullptr;
+            check(vx_host_pipeline_create(backend.ctx(), &stage, 1, &pipe));
+            for (int rep = 0; rep < 2; ++rep) {
+                std::memset(hy, 0xFF, 3 * rows * sizeof(float));
+                check(vx_host_pipeline_run(pipe));
+                for (int i = 0; i < 3; ++i) {
+                    const auto a = single[i].read();
+                    EXPECT(std::memcmp(a.data(), static_cast<float*>(hy) + i * rows, rows * sizeof(float)) == 0);
+                }
+            }
+            check(vx_host_pipeline_free(pipe));
+            check(vx_host_free(hx));
+            check(vx_host_free(hy));
+        }
         // both block formats against a host product over the dequantised weights: 1e-4 of the largest output
         for (vx_qtype qt : {VX_Q8_0, VX_Q4_0}) {
             const auto w = random_vec(rows * cols, 20 + (int)qt, -0.05f, 0.05f);
