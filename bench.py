@@ -923,6 +923,25 @@ def side_configs(be, lib, torch, stream):
     # (268 MB each, beyond L2), against the HBM copy peak; algorithmic bytes = every operand element read or
     # written once.
     D = 8192
+    cases, keep = elementwise_cases(be, lib, D)
+    ew = {}
+    for name, operands, call in cases:
+        def fn(call=call):
+            _lib.check(call())
+        us = time_graph(fn, 1, reps=10)
+        byts = operands * D * D * 4
+        ew[name] = {"us": us, "GB/s": byts / us / 1e3, "frac_of_measured_hbm": byts / us / 1e3 / peak}
+    out["elementwise_and_reduce_8192x8192_f32"] = ew
+    del cases, keep
+    return out
+
+
+def elementwise_cases(be, lib, D):
+    """The element-wise and reduction calls timed under `extra` (and launched by the `elementwise_8192` profile
+    case): (name, operands moved, call) on D x D f32 operands, and the tensors that must outlive the calls."""
+    import ctypes as C
+    import torch
+    from vortx_b200 import _lib
     A = torch.rand(D * D, device="cuda")
     B = torch.rand(D * D, device="cuda") + 1.0
     O = torch.empty(D * D, device="cuda")
@@ -945,16 +964,7 @@ def side_configs(be, lib, torch, stream):
         ("reduce_sum_wide", 1, lambda: lib.vx_reduce(be._ctx, 0, 0, 1, B.data_ptr(), C.byref(vec), 0, res.data_ptr())),
         ("reduce_max_wide", 1, lambda: lib.vx_reduce(be._ctx, 3, 0, 1, B.data_ptr(), C.byref(vec), 0, res.data_ptr())),
     )
-    ew = {}
-    for name, operands, call in cases:
-        def fn(call=call):
-            _lib.check(call())
-        us = time_graph(fn, 1, reps=10)
-        byts = operands * D * D * 4
-        ew[name] = {"us": us, "GB/s": byts / us / 1e3, "frac_of_measured_hbm": byts / us / 1e3 / peak}
-    out["elementwise_and_reduce_8192x8192_f32"] = ew
-    del A, B, O
-    return out
+    return cases, (A, B, O, res, dense, transp, one_row, small, vec)
 
 
 PROFILE_CASES = {
@@ -971,6 +981,8 @@ PROFILE_CASES = {
     "gemm_simt_exact_1024": ("gemm", 1024, 1024, "SIMT", 0),
     "gemm_tf32_4096": ("gemm", 4096, 4096, "TF32", 0),
     "gemm_tf32_8192": ("gemm", 8192, 8192, "TF32", 0),
+    # OpAssign / Contiguous / Repeat / WIDE reductions, the calls `extra` times, twice each on 8192 x 8192 f32
+    "elementwise_8192": ("elementwise", 8192, 8192, "f32", 2),
     # not for ncu: the chained list with the kernel's own %globaltimer stamps (a library built with
     # `python -m vortx_b200.build --timeline`); runs on 1 GPU or, under torchrun, on N
     "gemv_chain_timeline": ("chain_timeline", ROWS, COLS, "Q4_0", LAYERS),
@@ -1146,6 +1158,16 @@ def run_profile_case(name: str):
     be = vb.Backend(0)
     lib = _lib.load()
     rng = np.random.Generator(np.random.Philox(1))
+    if kind == "elementwise":
+        cases, keep = elementwise_cases(be, lib, rows)
+        for _ in range(copies):
+            for _name, _operands, call in cases:
+                _lib.check(call())
+        be.synchronize()
+        emit({"profile_case": name, "kernels_launched": be.launch_count(), "order": [c[0] for c in cases]})
+        del cases, keep
+        be.close()
+        return
     if kind == "gemv_batch":
         # `copies` is the batch here; four copies of the weights so that they come from HBM
         batch, copies = copies, 4

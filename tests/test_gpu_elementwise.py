@@ -147,6 +147,11 @@ _FAST_CASES = [
     ("b transposed", (1, 1, 100, 70), None, (0, 0, 1, 100), 0, 0),
     ("b transposed, 4-D, ragged tiles", (2, 3, 65, 129), None, (3 * 65 * 129, 65 * 129, 1, 65), 0, 7),
     ("a strided along w", (1, 1, 40, 300), (0, 0, 600, 2), None, 0, 0),
+    ("padded rows, float4 rows", (1, 2, 64, 256), (0, 64 * 260, 260, 1), (0, 64 * 264, 264, 1), 4, 8),
+    ("padded rows longer than one batch", (1, 1, 5, 4400), (0, 0, 4404, 1), (0, 0, 4408, 1), 0, 0),
+    ("dense, rows longer than one batch of float4 per thread", (1, 1, 6, 5000), None, None, 0, 0),
+    ("b one row, rows longer than one batch", (1, 1, 5, 4400), None, (0, 0, 0, 1), 0, 0),
+    ("b transposed, several tiles each way", (1, 1, 200, 333), None, (0, 0, 1, 200), 0, 0),
 ]
 
 
@@ -207,7 +212,10 @@ def test_fast_forms_of_contiguous(backend, oracle, dtype, sizes, strides, offset
 
 
 @pytest.mark.parametrize("rsizes,ssizes", [((1, 1, 37, 300), (1, 1, 5, 7)), ((2, 3, 20, 256), (1, 2, 20, 64)),
-                                           ((1, 1, 10, 1000), (1, 1, 1, 1)), ((1, 1, 9, 130), (1, 1, 4, 300))])
+                                           ((1, 1, 10, 1000), (1, 1, 1, 1)), ((1, 1, 9, 130), (1, 1, 4, 300)),
+                                           ((1, 1, 6, 2048), (1, 1, 3, 12)),      # float4 moves, the source wraps often
+                                           ((1, 1, 7, 1000), (1, 1, 2, 8)),       # float4 moves, 256 threads a multiple of the source
+                                           ((1, 1, 9, 132), (1, 1, 4, 300))])     # float4 moves, the source is wider
 def test_fast_form_of_repeat(backend, oracle, rsizes, ssizes):
     import ctypes as C
     from vortx_b200 import _lib

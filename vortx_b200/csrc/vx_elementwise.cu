@@ -68,14 +68,30 @@ op_assign_rows_kernel(float* __restrict__ a, const float* __restrict__ b, const 
             float4* pa = reinterpret_cast<float4*>(a + base_a);
             const float4* pb = reinterpret_cast<const float4*>(b + base_b);
             const float bv = BCAST ? b[base_b] : 0.0f;
-            for (uint32_t w = threadIdx.x; w < sa.w / 4; w += blockDim.x) {
-                float4 va = pa[w];
-                const float4 vb = BCAST ? make_float4(bv, bv, bv, bv) : pb[w];
-                va.x = apply<OP>(va.x, vb.x);
-                va.y = apply<OP>(va.y, vb.y);
-                va.z = apply<OP>(va.z, vb.z);
-                va.w = apply<OP>(va.w, vb.w);
-                pa[w] = va;
+            // four float4 of a (and of b) in flight per thread: a load after a store to the same array would wait
+            const uint32_t w4 = sa.w / 4;
+            for (uint32_t w0 = threadIdx.x; w0 < w4; w0 += 4 * blockDim.x) {
+                float4 va[4], vb[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t w = w0 + k * blockDim.x;
+                    if (w < w4) {
+                        if (OP != VX_OP_COPY) va[k] = pa[w];
+                        vb[k] = BCAST ? make_float4(bv, bv, bv, bv) : pb[w];
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t w = w0 + k * blockDim.x;
+                    if (w < w4) {
+                        float4 r;
+                        r.x = apply<OP>(OP != VX_OP_COPY ? va[k].x : 0.0f, vb[k].x);
+                        r.y = apply<OP>(OP != VX_OP_COPY ? va[k].y : 0.0f, vb[k].y);
+                        r.z = apply<OP>(OP != VX_OP_COPY ? va[k].z : 0.0f, vb[k].z);
+                        r.w = apply<OP>(OP != VX_OP_COPY ? va[k].w : 0.0f, vb[k].w);
+                        pa[w] = r;
+                    }
+                }
             }
         } else {
             for (uint32_t w = threadIdx.x; w < sa.w; w += blockDim.x) {
@@ -86,55 +102,116 @@ op_assign_rows_kernel(float* __restrict__ a, const float* __restrict__ b, const 
     }
 }
 
-// tile form: a's innermost stride is 1, b's unit stride is along h.  Tile (th, tw) of plane (n, c): b is read
-// with h fastest, a is updated with w fastest; the 64 x 65 shared tile turns one into the other (runs of 256
-// bytes on both sides; 32 x 32 tiles measured 15 % slower).
-constexpr int kTile = 64;
+// flat form: both operands are the same dense row-major block (16-byte aligned, length a multiple of 4): one
+// 1-D pass, every thread block takes 1024 consecutive float4 and every thread four of them, loads before stores.
 template <int OP>
+__global__ void __launch_bounds__(256)
+op_assign_flat_kernel(float4* __restrict__ a, const float4* __restrict__ b, uint32_t len4) {
+    const uint32_t base = blockIdx.x * 1024u + threadIdx.x;
+    float4 va[4], vb[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t i = base + 256u * k;
+        if (i < len4) {
+            if (OP != VX_OP_COPY) va[k] = a[i];
+            vb[k] = b[i];
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t i = base + 256u * k;
+        if (i < len4) {
+            float4 r;
+            r.x = apply<OP>(OP != VX_OP_COPY ? va[k].x : 0.0f, vb[k].x);
+            r.y = apply<OP>(OP != VX_OP_COPY ? va[k].y : 0.0f, vb[k].y);
+            r.z = apply<OP>(OP != VX_OP_COPY ? va[k].z : 0.0f, vb[k].z);
+            r.w = apply<OP>(OP != VX_OP_COPY ? va[k].w : 0.0f, vb[k].w);
+            a[i] = r;
+        }
+    }
+}
+
+// tile form: a's innermost stride is 1, b's unit stride is along h.  Tile (th, tw) of plane (n, c): b is read
+// with h fastest (runs of TH floats), a is updated with w fastest (runs of TW floats); the TW x (TH + 1) shared
+// tile turns one into the other.
+template <int OP, int TH, int TW>
 __global__ void __launch_bounds__(256)
 op_assign_tile_kernel(float* __restrict__ a, const float* __restrict__ b, const vx_shape sa, const vx_shape sb,
                       uint32_t off_a, uint32_t off_b) {
-    __shared__ float tile[kTile][kTile + 1];
-    const uint32_t tiles_w = (sa.w + kTile - 1) / kTile, tiles_h = (sa.h + kTile - 1) / kTile;
+    extern __shared__ float tile_mem[];
+    float (*tile)[TH + 1] = reinterpret_cast<float (*)[TH + 1]>(tile_mem);      // [w][h]
+    const uint32_t tiles_w = (sa.w + TW - 1) / TW, tiles_h = (sa.h + TH - 1) / TH;
     const uint32_t per_plane = tiles_w * tiles_h, total = per_plane * sa.n * sa.c;
-    const uint32_t x = threadIdx.x & (kTile - 1), y = threadIdx.x / kTile;     // 64 x 4 threads
+    const uint32_t xh = threadIdx.x % TH, yh = threadIdx.x / TH;     // loading: TH x (256 / TH) threads
+    const uint32_t xw = threadIdx.x % TW, yw = threadIdx.x / TW;     // storing: TW x (256 / TW) threads
+    constexpr int kRowsH = 256 / TH, kRowsW = 256 / TW;
     for (uint32_t t = blockIdx.x; t < total; t += gridDim.x) {
         const uint32_t plane = t / per_plane, in_plane = t - plane * per_plane;
         const uint32_t th = in_plane / tiles_w, tw = in_plane - th * tiles_w;
         const Idx4 pl = Idx4{plane / sa.c, plane % sa.c, 0, 0};
         const uint32_t base_a = off_a + compose(sa, pl), base_b = off_b + compose(sb, pl);
         __syncthreads();                                            // the tile of the round before has been used
-#pragma unroll
-        for (int k = 0; k < kTile / 4; ++k) {
-            const uint32_t h = th * kTile + x, w = tw * kTile + y + 4 * k;
-            if (h < sa.h && w < sa.w) tile[y + 4 * k][x] = b[base_b + h * sb.h_stride + w * sb.w_stride];
+#pragma unroll 16
+        for (int k = 0; k < TW / kRowsH; ++k) {
+            const uint32_t h = th * TH + xh, w = tw * TW + yh + kRowsH * k;
+            if (h < sa.h && w < sa.w) tile[yh + kRowsH * k][xh] = b[base_b + h * sb.h_stride + w * sb.w_stride];
         }
         __syncthreads();
+        // all of a's elements first, then the stores: a load after a store to the same array would wait for it
+        constexpr int kPer = TH / kRowsW;
+        float va[kPer];
+        if (OP != VX_OP_COPY) {
 #pragma unroll
-        for (int k = 0; k < kTile / 4; ++k) {
-            const uint32_t h = th * kTile + y + 4 * k, w = tw * kTile + x;
-            if (h < sa.h && w < sa.w) {
-                const uint32_t ia = base_a + h * sa.h_stride + w * sa.w_stride;
-                a[ia] = apply<OP>(a[ia], tile[x][y + 4 * k]);
+            for (int k = 0; k < kPer; ++k) {
+                const uint32_t h = th * TH + yw + kRowsW * k, w = tw * TW + xw;
+                va[k] = (h < sa.h && w < sa.w) ? a[base_a + h * sa.h_stride + w * sa.w_stride] : 0.0f;
             }
+        }
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const uint32_t h = th * TH + yw + kRowsW * k, w = tw * TW + xw;
+            if (h < sa.h && w < sa.w)
+                a[base_a + h * sa.h_stride + w * sa.w_stride] = apply<OP>(OP != VX_OP_COPY ? va[k] : 0.0f, tile[xw][yw + kRowsW * k]);
         }
     }
 }
 
+template <int OP, int TH, int TW>
+void launch_tile(vx_context* ctx, float* a, const float* b, const vx_shape& sa, const vx_shape& sb, uint32_t off_a,
+                 uint32_t off_b) {
+    constexpr int kBytes = TW * (TH + 1) * 4;
+    static bool raised = false;     // per instantiation; the attribute belongs to the function, any device
+    if (kBytes > 48 * 1024 && !raised) {
+        cudaFuncSetAttribute(op_assign_tile_kernel<OP, TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+        raised = true;
+    }
+    const uint32_t tiles = ((sa.w + TW - 1) / TW) * ((sa.h + TH - 1) / TH) * sa.n * sa.c;
+    const uint32_t per_sm = std::max(1, std::min(8, (200 * 1024) / kBytes));
+    op_assign_tile_kernel<OP, TH, TW><<<std::min(tiles, (uint32_t)ctx->sm_count * per_sm * 2), 256, kBytes, ctx->stream>>>(
+        a, b, sa, sb, off_a, off_b);
+}
+
 // rows form of the tiling copy: the source's (n, c, h) wrap once per row, its w index by increments.
+// VEC: both innermost strides are 1, both widths multiples of 4 and every row 16-byte aligned: float4 moves
+// (a float4 of the result never straddles the source's wrap).
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 repeat_rows_kernel(float* __restrict__ result, const float* __restrict__ source, const vx_shape sr, const vx_shape ss) {
     const uint32_t rows = sr.n * sr.c * sr.h;
-    const uint32_t step = blockDim.x % ss.w;
+    const uint32_t src_w = VEC ? ss.w / 4 : ss.w, res_w = VEC ? sr.w / 4 : sr.w;
+    const uint32_t step = blockDim.x % src_w;
     for (uint32_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const Idx4 id = row_of(sr, r);
         const Idx4 wr = Idx4{id.n % ss.n, id.c % ss.c, id.h % ss.h, 0};
         const uint32_t base_r = compose(sr, id), base_s = compose(ss, wr);
-        uint32_t ws = threadIdx.x % ss.w;
-        for (uint32_t w = threadIdx.x; w < sr.w; w += blockDim.x) {
-            result[base_r + w * sr.w_stride] = source[base_s + ws * ss.w_stride];
+        uint32_t ws = threadIdx.x % src_w;
+        for (uint32_t w = threadIdx.x; w < res_w; w += blockDim.x) {
+            if (VEC)
+                reinterpret_cast<float4*>(result + base_r)[w] = reinterpret_cast<const float4*>(source + base_s)[ws];
+            else
+                result[base_r + w * sr.w_stride] = source[base_s + ws * ss.w_stride];
             ws += step;
-            if (ws >= ss.w) ws -= ss.w;
+            if (ws >= src_w) ws -= src_w;
         }
     }
 }
@@ -195,6 +272,13 @@ bool rows_aligned(const void* base, const vx_shape& s, uint64_t offset) {
            s.h_stride % 4 == 0;
 }
 
+// The strides of `s`, walked over the extents of `sizes`, are row-major without gaps (a dimension of extent 1
+// may carry any stride).  b is indexed with a's ids, so its strides are judged over a's extents.
+bool is_dense(const vx_shape& sizes, const vx_shape& s) {
+    return (sizes.w == 1 || s.w_stride == 1) && (sizes.h == 1 || s.h_stride == sizes.w) &&
+           (sizes.c == 1 || s.c_stride == sizes.h * sizes.w) && (sizes.n == 1 || s.n_stride == sizes.c * sizes.h * sizes.w);
+}
+
 // Picks the form for a op= b (see the head of this file) and launches it.
 template <int OP>
 void launch_op_assign(vx_context* ctx, float* a, const float* b, const vx_shape& sa, const vx_shape& sb, uint32_t off_a,
@@ -202,10 +286,20 @@ void launch_op_assign(vx_context* ctx, float* a, const float* b, const vx_shape&
     const uint32_t len = shape_len(sa);
     const bool fast = vx::option(ctx, "elementwise.fast", 1) != 0 && no_wrap(sa, sa, off_a) && no_wrap(sa, sb, off_b);
     const uint32_t rows = sa.n * sa.c * sa.h;
-    const unsigned row_grid = std::max(1u, std::min(rows, (unsigned)ctx->sm_count * 8));
-    if (fast && sa.w >= 32 && sa.h >= 32 && sa.w_stride == 1 && sb.h_stride == 1 && sb.w_stride != 1 && sb.w_stride != 0) {
-        const uint32_t tiles = ((sa.w + kTile - 1) / kTile) * ((sa.h + kTile - 1) / kTile) * sa.n * sa.c;
-        op_assign_tile_kernel<OP><<<std::min(tiles, (uint32_t)ctx->sm_count * 16), 256, 0, ctx->stream>>>(a, b, sa, sb, off_a, off_b);
+    // long rows: a thread block per row (blocks that come and go keep the memory system fuller than resident
+    // ones walking rows, measured); short rows: resident blocks that walk rows
+    const unsigned row_grid = sa.w >= 4096 ? std::max(1u, rows) : std::max(1u, std::min(rows, (unsigned)ctx->sm_count * 8));
+    if (fast && vx::option(ctx, "elementwise.flat", 1) != 0 && len % 4 == 0 && is_dense(sa, sa) && is_dense(sa, sb) &&
+        (reinterpret_cast<uintptr_t>(a + off_a) & 15u) == 0 && (reinterpret_cast<uintptr_t>(b + off_b) & 15u) == 0) {
+        op_assign_flat_kernel<OP><<<(len / 4 + 1023) / 1024, 256, 0, ctx->stream>>>(
+            reinterpret_cast<float4*>(a + off_a), reinterpret_cast<const float4*>(b + off_b), len / 4);
+    } else if (fast && sa.w >= 32 && sa.h >= 32 && sa.w_stride == 1 && sb.h_stride == 1 && sb.w_stride != 1 && sb.w_stride != 0) {
+        const int th = (int)vx::option(ctx, "elementwise.tile_h", 64), tw = (int)vx::option(ctx, "elementwise.tile_w", 64);
+        if (th == 128 && tw == 128) launch_tile<OP, 128, 128>(ctx, a, b, sa, sb, off_a, off_b);
+        else if (th == 128) launch_tile<OP, 128, 64>(ctx, a, b, sa, sb, off_a, off_b);
+        else if (tw == 128) launch_tile<OP, 64, 128>(ctx, a, b, sa, sb, off_a, off_b);
+        else if (th == 256) launch_tile<OP, 256, 32>(ctx, a, b, sa, sb, off_a, off_b);
+        else launch_tile<OP, 64, 64>(ctx, a, b, sa, sb, off_a, off_b);
     } else if (fast && sa.w >= 128) {
         const bool vec = sa.w % 4 == 0 && sa.w_stride == 1 && rows_aligned(a, sa, off_a) && rows_aligned(b, sb, off_b);
         if (vec && sb.w_stride == 1)
@@ -300,8 +394,13 @@ vx_status vx_repeat(vx_context* ctx, float* result, const vx_shape* shape_result
     if (vx::option(ctx, "elementwise.fast", 1) != 0 && shape_result->w >= 128 && no_wrap(*shape_result, *shape_result, 0) &&
         no_wrap(*shape_source, *shape_source, 0)) {
         const uint32_t rows = shape_result->n * shape_result->c * shape_result->h;
-        repeat_rows_kernel<<<std::max(1u, std::min(rows, (unsigned)ctx->sm_count * 8)), 256, 0, ctx->stream>>>(
-            result, source, *shape_result, *shape_source);
+        const unsigned grid = shape_result->w >= 4096 ? std::max(1u, rows) : std::max(1u, std::min(rows, (unsigned)ctx->sm_count * 8));
+        const bool vec = shape_result->w_stride == 1 && shape_source->w_stride == 1 && shape_result->w % 4 == 0 &&
+                         shape_source->w % 4 == 0 && rows_aligned(result, *shape_result, 0) && rows_aligned(source, *shape_source, 0);
+        if (vec)
+            repeat_rows_kernel<true><<<grid, 256, 0, ctx->stream>>>(result, source, *shape_result, *shape_source);
+        else
+            repeat_rows_kernel<false><<<grid, 256, 0, ctx->stream>>>(result, source, *shape_result, *shape_source);
     } else {
         repeat_kernel<<<grid_for(ctx, len), 256, 0, ctx->stream>>>(result, source, *shape_result, *shape_source);
     }
