@@ -923,22 +923,23 @@ def side_configs(be, lib, torch, stream):
     # (268 MB each, beyond L2), against the HBM copy peak; algorithmic bytes = every operand element read or
     # written once.
     D = 8192
-    cases, keep = elementwise_cases(be, lib, D)
+    cases, keep = elementwise_cases(be, lib, D, big=True)
     ew = {}
     for name, operands, call in cases:
         def fn(call=call):
             _lib.check(call())
         us = time_graph(fn, 1, reps=10)
-        byts = operands * D * D * 4
+        byts = int(operands * D * D * 4)
         ew[name] = {"us": us, "GB/s": byts / us / 1e3, "frac_of_measured_hbm": byts / us / 1e3 / peak}
     out["elementwise_and_reduce_8192x8192_f32"] = ew
     del cases, keep
     return out
 
 
-def elementwise_cases(be, lib, D):
+def elementwise_cases(be, lib, D, big=False):
     """The element-wise and reduction calls timed under `extra` (and launched by the `elementwise_8192` profile
-    case): (name, operands moved, call) on D x D f32 operands, and the tensors that must outlive the calls."""
+    case): (name, operands of D x D f32 moved, call), and the tensors that must outlive the calls.  `big` adds
+    the reductions over 2^30 elements (4 GiB), where launch and tail no longer count."""
     import ctypes as C
     import torch
     from vortx_b200 import _lib
@@ -964,7 +965,17 @@ def elementwise_cases(be, lib, D):
         ("reduce_sum_wide", 1, lambda: lib.vx_reduce(be._ctx, 0, 0, 1, B.data_ptr(), C.byref(vec), 0, res.data_ptr())),
         ("reduce_max_wide", 1, lambda: lib.vx_reduce(be._ctx, 3, 0, 1, B.data_ptr(), C.byref(vec), 0, res.data_ptr())),
     )
-    return cases, (A, B, O, res, dense, transp, one_row, small, vec)
+    keep = [A, B, O, res, dense, transp, one_row, small, vec]
+    if big:
+        n_big = 1 << 30
+        G = torch.rand(n_big, device="cuda")
+        vbig = shp(1, 1, 1, n_big, n_big, n_big, n_big, 1)
+        keep += [G, vbig]
+        cases = cases + (
+            ("reduce_sum_wide_1Gi", n_big / (D * D), lambda: lib.vx_reduce(be._ctx, 0, 0, 1, G.data_ptr(), C.byref(vbig), 0, res.data_ptr())),
+            ("reduce_max_wide_1Gi", n_big / (D * D), lambda: lib.vx_reduce(be._ctx, 3, 0, 1, G.data_ptr(), C.byref(vbig), 0, res.data_ptr())),
+        )
+    return cases, keep
 
 
 PROFILE_CASES = {

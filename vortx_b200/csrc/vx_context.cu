@@ -55,9 +55,8 @@ static const char* const kKnownOptions[] = {
     "gemm.tf32.round_nearest",  // 1 (default): TMA rounds A and B to TF32 to nearest on load; 0: the tensor core truncates
     "gemm.tf32.tile_m",   // 128 or 256 forces the tile height of the TF32 kernel (0 = by problem size)
     "elementwise.fast",   // 1 (default): op_assign / contiguous / repeat take their row and tile forms where the layout allows; 0: the general kernels
+    "reduce.blocks_per_sm",  // WIDE reductions: thread blocks per SM (1..8, default 8)
     "elementwise.flat",   // 1 (default): dense operands of op_assign / contiguous take the one-dimensional form
-    "elementwise.tile_h",  // transposing tile of op_assign / contiguous: extent along b's unit-stride axis (64, 128 or 256)
-    "elementwise.tile_w",  // the same along a's unit-stride axis (64 or 128; 32 with tile_h 256)
     "bounds_check",       // 1 (default): refuse layouts that reach beyond the stated capacity
     "wait_cycles",        // budget, in SM clocks, of the device-side waits on exchange vectors and peer barriers (0 = about 0.2 s)
     "debug.fail_alloc_after",  // n > 0: the n-th device allocation from now fails as if the device were full (tests)

@@ -9,9 +9,13 @@
 // adjacent addresses whenever the innermost stride is 1.  They spend three integer divisions per element and
 // run at a third of the HBM rate, so the layouts that matter get forms that compute the same indices without
 // them (all bit-identical: the operations are exact per element, only the order of the elements changes):
+//   flat   both operands are one dense row-major block: a one-dimensional float4 pass, 16 KB per thread block;
 //   rows   a block walks whole rows (n, c, h) and its threads the w axis: one decomposition per row; float4
 //          accesses when both innermost strides are 1 (or b's is 0) and every row starts 16-byte aligned;
+//          rows of 4096 elements or more get a thread block each, shorter ones resident blocks;
 //   tile   b is read across its unit-stride axis h (a transposed view): 64 x 64 tiles through shared memory.
+// Every form issues a batch of loads before the stores that depend on them: a and the result are the same
+// array, so the compiler cannot move a later load above an earlier store by itself.
 // They are taken when no index can wrap around 2^32 (the general kernels keep the wrapping arithmetic).
 #include <algorithm>
 
@@ -132,63 +136,49 @@ op_assign_flat_kernel(float4* __restrict__ a, const float4* __restrict__ b, uint
 }
 
 // tile form: a's innermost stride is 1, b's unit stride is along h.  Tile (th, tw) of plane (n, c): b is read
-// with h fastest (runs of TH floats), a is updated with w fastest (runs of TW floats); the TW x (TH + 1) shared
-// tile turns one into the other.
-template <int OP, int TH, int TW>
+// with h fastest, a is updated with w fastest; the 64 x 65 shared tile turns one into the other (runs of 256
+// bytes on both sides).  Measured alternatives, none faster: 32 x 32 tiles (15 % slower), 128 x 64, 64 x 128,
+// 256 x 32 and 128 x 128 tiles (3 to 60 % slower), one thread block per tile instead of resident blocks, and a
+// diagonal order of the tiles (no change: the power-of-two pitch does not camp on memory channels).
+constexpr int kTile = 64;
+template <int OP>
 __global__ void __launch_bounds__(256)
 op_assign_tile_kernel(float* __restrict__ a, const float* __restrict__ b, const vx_shape sa, const vx_shape sb,
                       uint32_t off_a, uint32_t off_b) {
-    extern __shared__ float tile_mem[];
-    float (*tile)[TH + 1] = reinterpret_cast<float (*)[TH + 1]>(tile_mem);      // [w][h]
-    const uint32_t tiles_w = (sa.w + TW - 1) / TW, tiles_h = (sa.h + TH - 1) / TH;
+    __shared__ float tile[kTile][kTile + 1];
+    const uint32_t tiles_w = (sa.w + kTile - 1) / kTile, tiles_h = (sa.h + kTile - 1) / kTile;
     const uint32_t per_plane = tiles_w * tiles_h, total = per_plane * sa.n * sa.c;
-    const uint32_t xh = threadIdx.x % TH, yh = threadIdx.x / TH;     // loading: TH x (256 / TH) threads
-    const uint32_t xw = threadIdx.x % TW, yw = threadIdx.x / TW;     // storing: TW x (256 / TW) threads
-    constexpr int kRowsH = 256 / TH, kRowsW = 256 / TW;
+    const uint32_t x = threadIdx.x & (kTile - 1), y = threadIdx.x / kTile;     // 64 x 4 threads
+    constexpr int kPer = kTile / 4;
     for (uint32_t t = blockIdx.x; t < total; t += gridDim.x) {
         const uint32_t plane = t / per_plane, in_plane = t - plane * per_plane;
         const uint32_t th = in_plane / tiles_w, tw = in_plane - th * tiles_w;
         const Idx4 pl = Idx4{plane / sa.c, plane % sa.c, 0, 0};
         const uint32_t base_a = off_a + compose(sa, pl), base_b = off_b + compose(sb, pl);
         __syncthreads();                                            // the tile of the round before has been used
-#pragma unroll 16
-        for (int k = 0; k < TW / kRowsH; ++k) {
-            const uint32_t h = th * TH + xh, w = tw * TW + yh + kRowsH * k;
-            if (h < sa.h && w < sa.w) tile[yh + kRowsH * k][xh] = b[base_b + h * sb.h_stride + w * sb.w_stride];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const uint32_t h = th * kTile + x, w = tw * kTile + y + 4 * k;
+            if (h < sa.h && w < sa.w) tile[y + 4 * k][x] = b[base_b + h * sb.h_stride + w * sb.w_stride];
         }
         __syncthreads();
         // all of a's elements first, then the stores: a load after a store to the same array would wait for it
-        constexpr int kPer = TH / kRowsW;
+        // (a quarter of the time of the whole pass, measured)
         float va[kPer];
         if (OP != VX_OP_COPY) {
 #pragma unroll
             for (int k = 0; k < kPer; ++k) {
-                const uint32_t h = th * TH + yw + kRowsW * k, w = tw * TW + xw;
+                const uint32_t h = th * kTile + y + 4 * k, w = tw * kTile + x;
                 va[k] = (h < sa.h && w < sa.w) ? a[base_a + h * sa.h_stride + w * sa.w_stride] : 0.0f;
             }
         }
 #pragma unroll
         for (int k = 0; k < kPer; ++k) {
-            const uint32_t h = th * TH + yw + kRowsW * k, w = tw * TW + xw;
+            const uint32_t h = th * kTile + y + 4 * k, w = tw * kTile + x;
             if (h < sa.h && w < sa.w)
-                a[base_a + h * sa.h_stride + w * sa.w_stride] = apply<OP>(OP != VX_OP_COPY ? va[k] : 0.0f, tile[xw][yw + kRowsW * k]);
+                a[base_a + h * sa.h_stride + w * sa.w_stride] = apply<OP>(OP != VX_OP_COPY ? va[k] : 0.0f, tile[x][y + 4 * k]);
         }
     }
-}
-
-template <int OP, int TH, int TW>
-void launch_tile(vx_context* ctx, float* a, const float* b, const vx_shape& sa, const vx_shape& sb, uint32_t off_a,
-                 uint32_t off_b) {
-    constexpr int kBytes = TW * (TH + 1) * 4;
-    static bool raised = false;     // per instantiation; the attribute belongs to the function, any device
-    if (kBytes > 48 * 1024 && !raised) {
-        cudaFuncSetAttribute(op_assign_tile_kernel<OP, TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
-        raised = true;
-    }
-    const uint32_t tiles = ((sa.w + TW - 1) / TW) * ((sa.h + TH - 1) / TH) * sa.n * sa.c;
-    const uint32_t per_sm = std::max(1, std::min(8, (200 * 1024) / kBytes));
-    op_assign_tile_kernel<OP, TH, TW><<<std::min(tiles, (uint32_t)ctx->sm_count * per_sm * 2), 256, kBytes, ctx->stream>>>(
-        a, b, sa, sb, off_a, off_b);
 }
 
 // rows form of the tiling copy: the source's (n, c, h) wrap once per row, its w index by increments.
@@ -294,12 +284,8 @@ void launch_op_assign(vx_context* ctx, float* a, const float* b, const vx_shape&
         op_assign_flat_kernel<OP><<<(len / 4 + 1023) / 1024, 256, 0, ctx->stream>>>(
             reinterpret_cast<float4*>(a + off_a), reinterpret_cast<const float4*>(b + off_b), len / 4);
     } else if (fast && sa.w >= 32 && sa.h >= 32 && sa.w_stride == 1 && sb.h_stride == 1 && sb.w_stride != 1 && sb.w_stride != 0) {
-        const int th = (int)vx::option(ctx, "elementwise.tile_h", 64), tw = (int)vx::option(ctx, "elementwise.tile_w", 64);
-        if (th == 128 && tw == 128) launch_tile<OP, 128, 128>(ctx, a, b, sa, sb, off_a, off_b);
-        else if (th == 128) launch_tile<OP, 128, 64>(ctx, a, b, sa, sb, off_a, off_b);
-        else if (tw == 128) launch_tile<OP, 64, 128>(ctx, a, b, sa, sb, off_a, off_b);
-        else if (th == 256) launch_tile<OP, 256, 32>(ctx, a, b, sa, sb, off_a, off_b);
-        else launch_tile<OP, 64, 64>(ctx, a, b, sa, sb, off_a, off_b);
+        const uint32_t tiles = ((sa.w + kTile - 1) / kTile) * ((sa.h + kTile - 1) / kTile) * sa.n * sa.c;
+        op_assign_tile_kernel<OP><<<std::min(tiles, (uint32_t)ctx->sm_count * 16), 256, 0, ctx->stream>>>(a, b, sa, sb, off_a, off_b);
     } else if (fast && sa.w >= 128) {
         const bool vec = sa.w % 4 == 0 && sa.w_stride == 1 && rows_aligned(a, sa, off_a) && rows_aligned(b, sb, off_b);
         if (vec && sb.w_stride == 1)

@@ -116,30 +116,35 @@ __device__ __forceinline__ T block_fold(T a, T* ws) {
 
 template <class T, int OP>
 __global__ void __launch_bounds__(kWideThreads)
-reduce_wide_partials_kernel(const T* __restrict__ in, uint32_t n, uint32_t stride, T* __restrict__ partials) {
+reduce_wide_partials_kernel(const T* __restrict__ in, uint32_t n, uint32_t stride, T* partials, uint32_t* done, T* out) {
     __shared__ T ws[kWideThreads];
+    __shared__ bool is_last;
     // contiguous slice per block (a multiple of 4 elements), so that the partials' order is the index order
     const uint32_t per = ((n + gridDim.x - 1) / gridDim.x + 3) & ~3u;
     const uint32_t lo = min(n, blockIdx.x * per), hi = min(n, lo + per);
     T a = identity<T, OP>();
     if (stride == 1 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0) {
-        // unit stride: 16-byte loads, four running results per thread (element 4 k + j goes to result j), two
-        // loads in flight; the thread's four results are folded as (0 with 1) with (2 with 3)
+        // unit stride: 16-byte streaming loads, four running results per thread (element 4 k + j goes to result j),
+        // four loads in flight; the thread's four results are folded as (0 with 1) with (2 with 3)
         constexpr int TREE = OP == SQNORM ? SUM : OP;
+        constexpr int kInFlight = 4;
         T acc[4] = {a, a, a, a};
         const uint4* v = reinterpret_cast<const uint4*>(in + lo);
         const uint32_t nv = (hi - lo) / 4;
         uint32_t i = threadIdx.x;
-        for (; i + kWideThreads < nv; i += 2 * kWideThreads) {
-            const uint4 p = v[i], q = v[i + kWideThreads];
-            const uint32_t pw[4] = {p.x, p.y, p.z, p.w}, qw[4] = {q.x, q.y, q.z, q.w};
+        for (; i + (kInFlight - 1) * kWideThreads < nv; i += kInFlight * kWideThreads) {
+            uint4 p[kInFlight];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] = fold<T, OP>(acc[j], prepare<T, OP>(bits_to<T>(pw[j])));
+            for (int u = 0; u < kInFlight; ++u) p[u] = __ldcs(v + i + u * kWideThreads);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] = fold<T, OP>(acc[j], prepare<T, OP>(bits_to<T>(qw[j])));
+            for (int u = 0; u < kInFlight; ++u) {
+                const uint32_t pw[4] = {p[u].x, p[u].y, p[u].z, p[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j] = fold<T, OP>(acc[j], prepare<T, OP>(bits_to<T>(pw[j])));
+            }
         }
         for (; i < nv; i += kWideThreads) {
-            const uint4 p = v[i];
+            const uint4 p = __ldcs(v + i);
             const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[j] = fold<T, OP>(acc[j], prepare<T, OP>(bits_to<T>(pw[j])));
@@ -152,7 +157,26 @@ reduce_wide_partials_kernel(const T* __restrict__ in, uint32_t n, uint32_t strid
         for (uint32_t i = lo + threadIdx.x; i < hi; i += kWideThreads) a = fold<T, OP>(a, prepare<T, OP>(in[(size_t)i * stride]));
     }
     const T r = block_fold<T, OP>(a, ws);
-    if (threadIdx.x == 0) partials[blockIdx.x] = r;
+    if (done == nullptr) {          // the partials are folded by reduce_wide_final_kernel
+        if (threadIdx.x == 0) partials[blockIdx.x] = r;
+        return;
+    }
+    // With a counter, the block that finishes last folds the partials itself, in the same order as
+    // reduce_wide_final_kernel: which block that is does not change the result.  atomicInc wraps to 0 at the
+    // last arrival, so the counter is ready for the next call.
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = r;
+        __threadfence();
+        is_last = atomicInc(done, gridDim.x - 1) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    constexpr int TREE = OP == SQNORM ? SUM : OP;
+    T f = identity<T, OP>();
+    for (uint32_t i = threadIdx.x; i < gridDim.x; i += kWideThreads) f = fold<T, TREE>(f, __ldcg(partials + i));
+    const T total = block_fold<T, TREE>(f, ws);
+    if (threadIdx.x == 0) out[0] = total;
 }
 
 template <class T, int OP>
@@ -176,12 +200,12 @@ vx_status run(vx_context* ctx, bool wide, const T* in, uint32_t n, uint32_t stri
         return VX_OK;
     }
     uint32_t blocks = (n + kWideThreads * 8 - 1) / (kWideThreads * 8);
-    blocks = std::max(1u, std::min(blocks, std::min<uint32_t>(max_partials, (uint32_t)ctx->sm_count * 4)));
-    reduce_wide_partials_kernel<T, OP><<<blocks, kWideThreads, 0, ctx->stream>>>(in, n, stride, partials);
+    blocks = std::max(1u, std::min(blocks, std::min<uint32_t>(max_partials, (uint32_t)ctx->sm_count * (uint32_t)std::clamp<long long>(vx::option(ctx, "reduce.blocks_per_sm", 8), 1, 8))));
+    // one launch: the counter behind the partials lets the last block finish the fold
+    uint32_t* done = reinterpret_cast<uint32_t*>(partials + max_partials);
+    reduce_wide_partials_kernel<T, OP><<<blocks, kWideThreads, 0, ctx->stream>>>(in, n, stride, partials, done, out);
     VX_CUDA(cudaGetLastError());
-    reduce_wide_final_kernel<T, OP><<<1, kWideThreads, 0, ctx->stream>>>(partials, blocks, out);
-    VX_CUDA(cudaGetLastError());
-    ctx->launches += 2;
+    ctx->launches += 1;
     return VX_OK;
 }
 
@@ -228,10 +252,14 @@ vx_status vx_reduce(vx_context* ctx, vx_reduce_op op, vx_dtype dtype, vx_reduce_
     vx::DeviceGuard guard(ctx->device);
     const bool wide = mode == VX_REDUCE_WIDE;
     void* partials = nullptr;
-    const uint32_t max_partials = (uint32_t)ctx->sm_count * 4;
+    const uint32_t max_partials = (uint32_t)ctx->sm_count * 8;
     if (wide) {
         // Scratch for the partials: owned by the context, allocated on first use.
-        if (!ctx->reduce_scratch) VX_CUDA(vx::device_malloc(ctx, &ctx->reduce_scratch, (size_t)max_partials * 4));
+        // (max_partials values, then the arrival counter of the last-block fold, zero between calls)
+        if (!ctx->reduce_scratch) {
+            VX_CUDA(vx::device_malloc(ctx, &ctx->reduce_scratch, (size_t)max_partials * 4 + 16));
+            VX_CUDA(cudaMemsetAsync(static_cast<char*>(ctx->reduce_scratch) + (size_t)max_partials * 4, 0, 16, ctx->stream));
+        }
         partials = ctx->reduce_scratch;
     }
     switch (dtype) {
@@ -306,7 +334,7 @@ vx_status run_static(cudaStream_t stream, const T* in, uint32_t n, uint32_t stri
     blocks = std::max(1u, std::min(blocks, kStaticPartials));
     // Every partial the second kernel reads is written by the first one of the same call, so
     // nothing in the shared array has to be cleared between calls.
-    reduce_wide_partials_kernel<T, OP><<<blocks, kWideThreads, 0, stream>>>(in, n, stride, partials);
+    reduce_wide_partials_kernel<T, OP><<<blocks, kWideThreads, 0, stream>>>(in, n, stride, partials, nullptr, nullptr);
     VX_CUDA(cudaGetLastError());
     reduce_wide_final_kernel<T, OP><<<1, kWideThreads, 0, stream>>>(partials, blocks, out);
     VX_CUDA(cudaGetLastError());
