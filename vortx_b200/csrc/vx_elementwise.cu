@@ -139,7 +139,9 @@ op_assign_flat_kernel(float4* __restrict__ a, const float4* __restrict__ b, uint
 // with h fastest, a is updated with w fastest; the 64 x 65 shared tile turns one into the other (runs of 256
 // bytes on both sides).  Measured alternatives, none faster: 32 x 32 tiles (15 % slower), 128 x 64, 64 x 128,
 // 256 x 32 and 128 x 128 tiles (3 to 60 % slower), one thread block per tile instead of resident blocks, and a
-// diagonal order of the tiles (no change: the power-of-two pitch does not camp on memory channels).
+// diagonal order of the tiles (no change: the power-of-two pitch does not camp on memory channels), and rings of
+// 4, 6 and 13 tiles per block filled by 4-byte asynchronous copies (8 to 15 % slower: more bytes in flight do
+// not help, the 256-byte runs themselves are what the memory system serves at 0.8 of its dense rate).
 constexpr int kTile = 64;
 template <int OP>
 __global__ void __launch_bounds__(256)
