@@ -584,7 +584,7 @@ def run_ours(args):
     if rank == 0 and n == 1:
         try:
             extra.update(side_configs(be, lib, torch, stream))
-        except _lib.VortxError as e:
+        except (_lib.VortxError, RuntimeError) as e:      # a side configuration must not take the headline line with it
             extra["side_configs_failed"] = str(e)
         try:
             gbs, dt, threads = cpu_gemv_rate(blocks, ROWS, steps=5, warmup=1)
